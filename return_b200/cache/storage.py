@@ -1,0 +1,96 @@
+"""The device side of the cache: pools of pages per group of layers, and state slots.
+
+Layers (runs of the schedule that own a cache) are grouped by what their mixers ask for:
+paged keys and values with the same window, number of KV heads and head size share a group,
+hence a page pool, a free list and block tables (``return_b200/cache/manager.py``).  The pool of
+a group is one tensor ``[layers, 2, num_pages, Hkv, page_size, D]`` in the activation dtype
+(index 0 of the second axis: keys, 1: values), so one page id addresses a slab in every layer of
+the group, as in the reference (rollout/cache.py:19-24), and one (page, kv head) tile is
+contiguous.  A mixer that asks for state of fixed size gets ``[max_reside, *shape]``, one row per
+request slot (after rollout/cache.py:340-360).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..parts.base import BuildEnv, KVCacheNeed, KVView, LayerContext, StateNeed
+from .manager import CacheManager, GroupSpec
+
+
+class CacheStorage:
+    def __init__(self, needs: List[object], page_size: int, num_pages: int, max_reside: int, env: BuildEnv):
+        self.env = env
+        self.page_size = page_size
+        self.max_reside = max_reside
+        signature_to_group: Dict[Tuple, int] = {}
+        self.group_specs: List[GroupSpec] = []
+        self._group_layers: List[int] = []
+        self._group_shape: List[Tuple[int, int]] = []
+        self.entry_place: Dict[int, Tuple[int, int]] = {}      # schedule index -> (group, layer in group)
+        self._state_needs: Dict[int, StateNeed] = {}
+        for index, need in enumerate(needs):
+            if need is None:
+                continue
+            if isinstance(need, KVCacheNeed):
+                sig = (need.window, need.num_kv_heads, need.head_dim)
+                if sig not in signature_to_group:
+                    signature_to_group[sig] = len(self.group_specs)
+                    name = "full" if need.window is None else f"window{need.window}"
+                    self.group_specs.append(GroupSpec(f"{name}_h{need.num_kv_heads}_d{need.head_dim}",
+                                                      page_size, num_pages, need.window))
+                    self._group_layers.append(0)
+                    self._group_shape.append((need.num_kv_heads, need.head_dim))
+                g = signature_to_group[sig]
+                self.entry_place[index] = (g, self._group_layers[g])
+                self._group_layers[g] += 1
+            elif isinstance(need, StateNeed):
+                self._state_needs[index] = need
+            else:
+                raise TypeError(f"schedule entry {index}: unknown cache need {need!r}")
+        if not self.group_specs:
+            # a model without paged layers still counts tokens per request
+            self.group_specs.append(GroupSpec("none", page_size, num_pages, None))
+            self._group_layers.append(0)
+            self._group_shape.append((0, 0))
+        self.pools: List[Optional[torch.Tensor]] = []
+        self.states: Dict[int, torch.Tensor] = {}
+
+    def make_manager(self) -> CacheManager:
+        return CacheManager(self.group_specs, self.max_reside)
+
+    def allocate(self) -> None:
+        dev, dt = self.env.device, self.env.act_dtype
+        self.pools = []
+        for spec, layers, (hkv, d) in zip(self.group_specs, self._group_layers, self._group_shape):
+            if layers == 0:
+                self.pools.append(None)
+                continue
+            self.pools.append(torch.zeros((layers, 2, spec.num_pages, hkv, spec.page_size, d), dtype=dt, device=dev))
+        self.states = {i: torch.zeros((self.max_reside,) + tuple(n.shape), dtype=n.dtype, device=dev)
+                       for i, n in self._state_needs.items()}
+
+    def bytes_per_token(self) -> int:
+        total = 0
+        for layers, (hkv, d) in zip(self._group_layers, self._group_shape):
+            total += layers * 2 * hkv * d * torch.empty((), dtype=self.env.act_dtype).element_size()
+        return total
+
+    def poison(self) -> None:
+        """Fills every page with NaN, so that a read of a slot nobody wrote shows in the logits."""
+        for p in self.pools:
+            if p is not None:
+                p.fill_(float("nan"))
+
+    def layer_context(self, owner_index: int, batch, write: bool) -> LayerContext:
+        ctx = LayerContext(batch=batch, write_cache=write)
+        place = self.entry_place.get(owner_index)
+        if place is not None:
+            g, layer = place
+            pool = self.pools[g]
+            ctx.kv = KVView(k=pool[layer, 0], v=pool[layer, 1], block_table=batch.block_tables[g],
+                            page_size=self.group_specs[g].page_size)
+        if owner_index in self.states:
+            ctx.state = self.states[owner_index]
+        return ctx

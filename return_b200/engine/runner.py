@@ -1,0 +1,85 @@
+"""The step function: runs one batch of (request, next tokens) from the cache and returns the
+logits at the wanted places.
+
+The reference has two entry points that also sample, ``Model.prefill`` (which loops over chunk
+steps itself) and ``Model.decode`` (rollout/model.py:184-343), and never mixes the two in one
+forward.  Here there is one: ``ModelRunner.step(entries)``.  It runs exactly the tokens it is
+given, as one packed batch, against the keys and values that earlier steps left in the pages.
+Making room in the cache (``reserve``) is separate from running (``step``), so a scheduler can
+decide what fits before anything is launched.
+"""
+from __future__ import annotations
+
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager, KVCapacityError
+from ..cache.storage import CacheStorage
+from ..config import registry
+from ..models.decoder import DecoderModel
+from ..parts.base import BuildEnv
+from ..weights import loader
+from .batch import BatchStaging, StepBatch, StepEntry, build_host_batch
+from .config import EngineConfig
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, engine_config: EngineConfig, max_positions: int):
+        self.model = model
+        self.config = engine_config
+        self.env = model.env
+        self.max_positions = max_positions
+        self.storage = CacheStorage(model.cache_needs(), engine_config.page_size, engine_config.num_pages,
+                                    engine_config.max_reside, self.env)
+        self.manager: CacheManager = self.storage.make_manager()
+        self.storage.allocate()
+        self.staging = BatchStaging(self.env.device)
+        self.vocab_size = model.spec.vocab_size
+
+    # ------------------------------------------------------------------ building
+    @classmethod
+    def from_model_dir(cls, model_dir: str, engine_config: EngineConfig) -> "ModelRunner":
+        """Reads config.json, picks the architecture from the registry and loads the safetensors."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("return_b200 runs on a CUDA device (B200, sm_100a); none is visible")
+        arch, cfg = registry.read_config(model_dir)
+        device = torch.device(engine_config.device)
+        env = BuildEnv(engine_config.act_dtype, device)
+        # like the reference, the position tables are sized by the pool, not by
+        # max_position_embeddings (rollout/monkey_patch/qwen3.py:121-127)
+        max_positions = engine_config.max_model_len or min(engine_config.max_token, 1 << 20)
+        model = DecoderModel(arch.decoder_spec(cfg, max_positions), env)
+        expected = {n: shape for n, (shape, _) in loader.checkpoint_shapes(arch, cfg).items()}
+        params = loader.load_parameters(model.params(), arch.weight_sources(cfg), expected, model_dir,
+                                        env.act_dtype, device, arch.ignorable_tensors(cfg))
+        model.bind(params)
+        runner = cls(model, engine_config, max_positions)
+        runner.model_config = cfg
+        return runner
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, rid: Hashable) -> int:
+        return self.manager.add(rid)
+
+    def free_request(self, rid: Hashable) -> None:
+        self.manager.free(rid)
+
+    def reserve(self, rid: Hashable, tokens: Sequence[int], want: Sequence[int] = ()) -> StepEntry:
+        """Makes room for the request's next tokens and returns the step entry for them.
+        Raises KVCapacityError, changing nothing, if the pages do not suffice."""
+        n = len(tokens)
+        if self.manager.length(rid) + n > self.max_positions:
+            raise ValueError(f"request {rid!r} would reach {self.manager.length(rid) + n} tokens; "
+                             f"the engine was set up for {self.max_positions}")
+        start = self.manager.append(rid, n)
+        return StepEntry(rid=rid, tokens=tokens, want=want, start=start)
+
+    # ------------------------------------------------------------------ the step
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries as one batch; float32 logits [wanted places, vocab], in entry order."""
+        host = build_host_batch(entries, self.manager, self.vocab_size, self.max_positions)
+        with torch.cuda.device(self.env.device):
+            batch = StepBatch(host, self.env.device, self.staging)
+            return self.model.forward(batch, self.storage)

@@ -1,0 +1,222 @@
+"""Python face of the CUDA kernels: thin, checked wrappers over the ``extern "C"`` launchers.
+
+Every function here launches hand-written sm_100a kernels on torch's current CUDA stream.
+There is no CPU path and no library stand-in: a tensor that is not on a CUDA device, or a
+missing extension, raises.  The only library product on the engine's path is the bfloat16
+matrix product (cuBLAS through ``torch.mm``), where the reference's engine also calls a
+library (rollout/monkey_patch/qwen3.py:21-22,29-31,56).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"the kernels take float32 and bfloat16, not {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
+    return c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+_core = None
+
+_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "rope_cache.cu", "attention_simt.cu", "sampling.cu"]
+
+
+def core() -> ctypes.CDLL:
+    """The library of kernels that need no specialisation."""
+    global _core
+    if _core is None:
+        lib = build.load("return_core", _CORE_SOURCES)
+        P, I, F = c_void_p, c_int, c_float
+        lib.rb_embedding.argtypes = [P, I, P, P, I, I, I, P]
+        lib.rb_add_rmsnorm.argtypes = [P, P, P, P, I, F, F, P, I, I, I, P]
+        lib.rb_rmsnorm_rows.argtypes = [P, P, I, F, F, P, I, I, I, P]
+        lib.rb_swiglu.argtypes = [P, P, I, I, I, P]
+        lib.rb_gemm_f32.argtypes = [P, P, P, I, I, I, I, I, I, P]
+        lib.rb_qk_norm_rope_write.argtypes = [P, I, P, P, I, F, F, P, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P]
+        lib.rb_attention_simt.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, P]
+        lib.rb_sample.argtypes = [P, I, I, I, P, P, P, P, P, P, P]
+        lib.rb_argmax.argtypes = [P, I, I, I, P, P]
+        for name in ("rb_embedding", "rb_add_rmsnorm", "rb_rmsnorm_rows", "rb_swiglu", "rb_gemm_f32",
+                     "rb_qk_norm_rope_write", "rb_attention_simt", "rb_sample", "rb_argmax"):
+            getattr(lib, name).restype = c_int
+        _core = lib
+    return _core
+
+
+def build_all():
+    """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
+    return [build.library_path("return_core", _CORE_SOURCES)]
+
+
+# ------------------------------------------------------------------------------- elementwise
+
+def embedding(table: torch.Tensor, tokens: torch.Tensor, stream_out: torch.Tensor) -> None:
+    """stream_out[t] = float32(table[tokens[t]]); tokens int32 [T], stream_out float32 [T, H]."""
+    T, H = stream_out.shape
+    assert tokens.dtype == torch.int32 and stream_out.dtype == torch.float32
+    assert table.shape[1] == H and table.is_contiguous() and stream_out.is_contiguous()
+    _check(core().rb_embedding(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(stream_out),
+                               T, H, table.shape[0], _stream()), "embedding")
+
+
+def add_rmsnorm(stream: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, offset: float = 0.0) -> None:
+    """stream += delta (written back unless ``rows``); out = rmsnorm(stream) * (offset + weight).
+
+    ``rows`` (int32) picks the rows to normalise; out then has one row per entry of ``rows``.
+    """
+    H = stream.shape[1]
+    n = out.shape[0]
+    assert stream.dtype == torch.float32 and stream.is_contiguous() and out.is_contiguous()
+    assert out.shape[1] == H and weight.numel() == H
+    if delta is not None:
+        assert delta.dtype == out.dtype and delta.shape == stream.shape and delta.is_contiguous()
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() == n
+    else:
+        assert n == stream.shape[0]
+    _check(core().rb_add_rmsnorm(_ptr(stream), _ptr(delta), _ptr(rows), _ptr(weight), dtype_code(weight.dtype),
+                                 eps, offset, _ptr(out), dtype_code(out.dtype), n, H, _stream()), "add_rmsnorm")
+
+
+def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, offset: float = 0.0) -> None:
+    """out = rmsnorm over the last dim of contiguous x [..., N]."""
+    N = x.shape[-1]
+    assert x.is_contiguous() and out.is_contiguous() and out.dtype == x.dtype and weight.numel() == N
+    _check(core().rb_rmsnorm_rows(_ptr(x), _ptr(weight), dtype_code(weight.dtype), eps, offset, _ptr(out),
+                                  dtype_code(x.dtype), x.numel() // N, N, _stream()), "rmsnorm_rows")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    T, I2 = gate_up.shape
+    assert out.shape == (T, I2 // 2) and gate_up.is_contiguous() and out.is_contiguous()
+    assert out.dtype == gate_up.dtype
+    _check(core().rb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, _stream()), "swiglu")
+
+
+# ------------------------------------------------------------------------------- matrix products
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T in true float32 (FFMA, fixed order over K)."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == w.dtype == out.dtype == torch.float32
+    assert w.shape[1] == K and out.shape == (M, N)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(core().rb_gemm_f32(_ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                              _stream()), "gemm_f32")
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x @ w^T.  float32: the engine's own FFMA kernel.  bfloat16 operands: cuBLAS with
+    float32 accumulation, output bfloat16 or float32 (``out``'s dtype)."""
+    if x.dtype == torch.float32:
+        gemm_f32(x, w, out)
+        return
+    if not x.is_cuda:
+        raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if out.dtype == torch.float32:
+        torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    else:
+        torch.mm(x, w.t(), out=out)
+
+
+# ------------------------------------------------------------------------------- attention
+
+def qk_norm_rope_write(qkv, q_weight, k_weight, eps, cos, sin, rot_dim, pos, tok_seg, block_table,
+                       page_size, k_pool, v_pool, num_heads, num_kv_heads, head_dim, write_kv=True,
+                       offset=0.0) -> None:
+    """In place on qkv [T, (Hq+2Hkv)*D]: q heads normed and rotated; k heads normed, rotated and
+    written to ``k_pool``; v heads written to ``v_pool``.  Pools: [pages, Hkv, P, D]."""
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1
+    assert pos.dtype == tok_seg.dtype == block_table.dtype == torch.int32
+    assert k_pool.dtype == qkv.dtype and v_pool.dtype == qkv.dtype
+    if rot_dim:
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32
+        assert cos.shape[1] * 2 == rot_dim and cos.is_contiguous() and sin.is_contiguous()
+        assert rot_dim <= head_dim
+    else:
+        cos = sin = pos            # never read: a rotary width of zero rotates nothing
+    wd = dtype_code(q_weight.dtype) if q_weight is not None else F32
+    if q_weight is not None:
+        assert k_weight is not None and k_weight.dtype == q_weight.dtype
+    _check(core().rb_qk_norm_rope_write(
+        _ptr(qkv), qkv.stride(0), _ptr(q_weight), _ptr(k_weight), wd, eps, offset, _ptr(cos), _ptr(sin),
+        rot_dim, _ptr(pos), _ptr(tok_seg), _ptr(block_table), block_table.stride(0), page_size,
+        _ptr(k_pool), _ptr(v_pool), dtype_code(qkv.dtype), T, num_heads, num_kv_heads, head_dim,
+        1 if write_kv else 0, _stream()), "qk_norm_rope_write")
+
+
+def attention_simt(qkv, k_pool, v_pool, pos, tok_seg, block_table, page_size, out, num_heads,
+                   num_kv_heads, head_dim, scale, window=0) -> None:
+    """Paged causal attention, one warp per (token, head); out [T, Hq*D]."""
+    T = qkv.shape[0]
+    assert out.is_contiguous() and out.dtype == qkv.dtype and k_pool.dtype == qkv.dtype
+    _check(core().rb_attention_simt(
+        _ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(pos), _ptr(tok_seg), _ptr(block_table),
+        block_table.stride(0), page_size, _ptr(out), dtype_code(qkv.dtype), T, num_heads, num_kv_heads,
+        head_dim, scale, int(window or 0), _stream()), "attention_simt")
+
+
+def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,
+                    head_dim, scale, window=None) -> None:
+    """Attention of every token of the step over its request's cached keys (its own included).
+
+    float32: the CUDA-core kernel, whose result does not depend on how the work was cut.
+    bfloat16: the tensor-core kernels, one for prompt portions and one (split over the keys) for
+    single decoded tokens."""
+    attention_simt(qkv, k_pool, v_pool, batch.pos, batch.tok_seg, block_table, page_size, out,
+                   num_heads, num_kv_heads, head_dim, scale, window or 0)
+
+
+# ------------------------------------------------------------------------------- sampling
+
+def sample(logits, temperature, top_k, top_p, uniform, tokens_out, logprobs_out=None) -> None:
+    """One token per row of float32 logits [n, V]; per-row temperature, top_k, top_p and uniform draw."""
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and uniform.dtype == torch.float32
+    assert top_k.dtype == torch.int32 and tokens_out.dtype == torch.int32
+    _check(core().rb_sample(_ptr(logits), logits.stride(0), n, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                            _ptr(uniform), _ptr(tokens_out), _ptr(logprobs_out), _stream()), "sample")
+
+
+def argmax(logits, tokens_out) -> None:
+    n, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and tokens_out.dtype == torch.int32
+    _check(core().rb_argmax(_ptr(logits), logits.stride(0), n, V, _ptr(tokens_out), _stream()), "argmax")

@@ -1,0 +1,79 @@
+"""A decoder made of parts: embedding, a schedule of blocks, final norm, output head.
+
+The model knows nothing of Qwen3.  It is built from a ``DecoderSpec`` and asks each block for
+its parameters under the names ``layers.<i>.<part>.<param>``, plus ``embed``, ``final_norm.weight``
+and ``lm_head`` (an alias of ``embed`` when the specification ties them).  The forward pass of
+one step follows the reference's (rollout/monkey_patch/qwen3.py:71-81): embed, run the layers,
+final norm; the head is applied to the rows whose logits are wanted only
+(rollout/model.py:286-290).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..ext import ops
+from ..parts.base import BLOCKS, NORMS, BuildEnv, KVCacheNeed, LayerContext, ParamSpec, StateNeed
+from ..parts.spec import DecoderSpec
+
+
+class DecoderModel:
+    def __init__(self, spec: DecoderSpec, env: BuildEnv):
+        spec.validate()
+        self.spec = spec
+        self.env = env
+        self.blocks = [BLOCKS.build(b, env) for b in spec.layers]
+        self.final_norm = NORMS.build(spec.final_norm, env)
+        self.embed: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ parameters
+    def params(self) -> Dict[str, ParamSpec]:
+        s = self.spec
+        p = {"embed": ParamSpec((s.vocab_size, s.hidden_size))}
+        for i, block in enumerate(self.blocks):
+            for name, ps in block.params().items():
+                p[f"layers.{i}.{name}"] = ps
+        for name, ps in self.final_norm.params().items():
+            p[f"final_norm.{name}"] = ps
+        if not s.tie_embeddings:
+            p["lm_head"] = ParamSpec((s.vocab_size, s.hidden_size))
+        return p
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.embed = tensors["embed"]
+        self.lm_head = self.embed if self.spec.tie_embeddings else tensors["lm_head"]
+        for i, block in enumerate(self.blocks):
+            prefix = f"layers.{i}."
+            block.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
+        self.final_norm.bind({k[len("final_norm."):]: v for k, v in tensors.items() if k.startswith("final_norm.")})
+
+    # ------------------------------------------------------------------ caches
+    def cache_needs(self) -> List[object]:
+        """Per schedule entry: what the run's mixer wants cached (None if it owns no cache)."""
+        out = []
+        for e in self.spec.schedule:
+            out.append(self.blocks[e.layer].cache_need() if e.cache_of is None else None)
+        return out
+
+    # ------------------------------------------------------------------ one step
+    def forward(self, batch, storage) -> torch.Tensor:
+        """Runs the step's tokens through the schedule; returns float32 logits [n_want, vocab]."""
+        T = batch.num_tokens
+        H = self.spec.hidden_size
+        dev = self.env.device
+        stream = torch.empty((T, H), dtype=torch.float32, device=dev)
+        ops.embedding(self.embed, batch.tokens, stream)
+        delta = None
+        for index, entry in enumerate(self.spec.schedule):
+            owner = index if entry.cache_of is None else entry.cache_of
+            ctx = storage.layer_context(owner, batch, write=entry.cache_of is None)
+            delta = self.blocks[entry.layer].forward(stream, delta, ctx)
+        n_want = batch.num_want
+        logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=dev)
+        if n_want:
+            hidden = torch.empty((n_want, H), dtype=self.env.act_dtype, device=dev)
+            self.final_norm.add_forward(stream, delta, hidden, rows=batch.want_rows)
+            ops.linear(hidden, self.lm_head, logits)
+        return logits

@@ -1,0 +1,156 @@
+"""Interfaces of the parts and the registries that map a specification's ``kind`` to a class.
+
+A part is built from its specification and a ``BuildEnv`` (activation dtype and device), says
+which parameters it wants (``params``), receives them (``bind``) and runs (``forward``).  The
+five families and what each must offer:
+
+``Norm``              ``forward(x, out)``; ``add_forward(stream, delta, out, rows)``, the residual
+                      add fused with the norm (stream is the float32 residual).
+``PositionEncoding``  ``rotary_tables()`` -> (cos, sin, rotary_dim) for encodings that rotate pairs
+                      of a head, or ``apply(qkv, batch, ...)`` for any other in-place encoding.
+``Mixer``             ``cache_need()`` -> ``KVCacheNeed`` | ``StateNeed`` | None and
+                      ``forward(x, ctx)`` with x [T, hidden] -> [T, hidden].
+``FeedForward``       ``forward(x, ctx)``.
+``Block``             ``forward(stream, delta, ctx)`` -> the delta still to be added to the stream.
+
+Parameters have names local to the part ("qkv", "q_norm.weight").  Which checkpoint tensors
+fill them is the architecture's knowledge, not the part's.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Optional, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class BuildEnv:
+    act_dtype: torch.dtype            # torch.float32 (true 32-bit path) or torch.bfloat16
+    device: torch.device
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """A parameter a part wants.  role "matrix": operand of a matrix product, kept in the
+    activation dtype.  role "vector": a norm weight or the like; keeps float32 if stored so."""
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    init: str = "normal"              # random-weights law: "normal" N(0, .02) | "ones_normal" 1 + N(0, .1)
+
+
+@dataclass(frozen=True)
+class KVCacheNeed:
+    """The mixer wants paged keys and values: all of them, or a window."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """The mixer wants one tensor of fixed shape per request."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class KVView:
+    """One cache layer as a mixer sees it."""
+    k: torch.Tensor                   # [num_pages, Hkv, page_size, D]
+    v: torch.Tensor
+    block_table: torch.Tensor         # int32 [segments of the step, blocks]
+    page_size: int
+
+
+@dataclass
+class LayerContext:
+    """What a part gets beside its input for one run of a layer in one step."""
+    batch: Any                        # engine.batch.StepBatch
+    kv: Optional[KVView] = None
+    state: Optional[torch.Tensor] = None      # [num_slots, *StateNeed.shape]; row = batch.seg_slot
+    write_cache: bool = True
+
+
+class Part:
+    def __init__(self, spec, env: BuildEnv):
+        self.spec = spec
+        self.env = env
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for name, t in tensors.items():
+            setattr(self, "p_" + name.replace(".", "_"), t)
+
+
+class Norm(Part):
+    def forward(self, x, out):
+        raise NotImplementedError
+
+    def add_forward(self, stream, delta, out, rows=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary_tables(self):
+        return None
+
+    def apply(self, qkv, batch, num_heads, num_kv_heads, head_dim):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, x, ctx: LayerContext):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, ctx: LayerContext):
+        raise NotImplementedError
+
+
+class Block(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, stream, delta, ctx: LayerContext):
+        raise NotImplementedError
+
+
+# ------------------------------------------------------------------------------- registries
+
+class Registry:
+    def __init__(self, family: str):
+        self.family = family
+        self._classes: Dict[str, Callable] = {}
+
+    def register(self, kind: str, cls=None):
+        """``REG.register("kind", Class)`` or ``@REG.register("kind")``."""
+        def put(c):
+            self._classes[kind] = c
+            return c
+        return put(cls) if cls is not None else put
+
+    def unregister(self, kind: str) -> None:
+        self._classes.pop(kind, None)
+
+    def build(self, spec, env: BuildEnv):
+        kind = getattr(spec, "kind", None)
+        if kind not in self._classes:
+            raise KeyError(f"no {self.family} of kind {kind!r}; registered: {sorted(self._classes)}")
+        return self._classes[kind](spec, env)
+
+    def kinds(self):
+        return sorted(self._classes)
+
+
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+BLOCKS = Registry("block")
