@@ -83,6 +83,11 @@ class CacheStorage:
             if p is not None:
                 p.fill_(float("nan"))
 
+    def reset_slot(self, slot: int) -> None:
+        """A request that takes a slot starts from zero state."""
+        for t in self.states.values():
+            t[slot].zero_()
+
     def layer_context(self, owner_index: int, batch, write: bool) -> LayerContext:
         ctx = LayerContext(batch=batch, write_cache=write)
         place = self.entry_place.get(owner_index)

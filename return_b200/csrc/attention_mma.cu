@@ -1,0 +1,485 @@
+// Paged causal attention in bfloat16 on the tensor cores (mma.sync m16n8k16, float32 accumulate),
+// compiled for one head size: -DHEAD_DIM=<multiple of 16, 16..256>.
+//
+//   rb_attn_prefill   prompt portions: one CTA per (tile of 64 query rows of one segment, q head).
+//   rb_attn_decode    single decoded tokens: one CTA per (segment, kv head, split of the keys); the
+//                     G query heads of the kv head share every K/V tile (rows of one MMA tile).
+//   rb_attn_combine   merges the splits of rb_attn_decode.
+//
+// Same contract as the reference's kernels (rollout/attention.py:45-142 prefill, :430-514 split
+// decode, :517-540 combine): online softmax with float32 running maximum and sum, probabilities
+// rounded to bfloat16 for the P.V product, empty splits neutral (m = -inf, l = 0).  Different:
+// keys arrive rotated, pages are found through a per-segment block table, K/V tiles are aligned
+// to absolute positions (so a row's arithmetic in the prefill kernel does not depend on how the
+// prompt was cut), and a sliding window bounds the keys from below.
+//
+// K and V of one layer: [num_pages, Hkv, P, D] bfloat16.  Shared-memory tiles are [rows][D] with
+// the 16-byte chunks of a row XOR-swizzled by the row index, which keeps ldmatrix conflict-free.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<head size>"
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head size: multiple of 16 in 16..256");
+
+namespace {
+
+constexpr int D = HEAD_DIM;
+constexpr int CHUNKS = D / 8;                 // 16-byte chunks in a row
+constexpr int SWZ = (CHUNKS % 8 == 0) ? 7 : (CHUNKS % 4 == 0) ? 3 : 1;
+constexpr int KSTEPS = D / 16;                // k16 steps over the head dim
+constexpr int DTILES = D / 8;                 // n8 tiles over the head dim
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ int soff(int row, int chunk) { return row * D + ((chunk ^ (row & SWZ)) << 3); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = pred ? 16 : 0;          // 0: nothing is read, the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Copies `rows` keys starting at absolute position j0 (rows of D elements) of one kv head into a
+// swizzled tile.  A key outside [lo, hi] (or on a page that was given back) is zero-filled and
+// never read.  `lane`/`nthreads`: the calling group's thread index and size.
+__device__ __forceinline__ void load_kv_rows(bf16* tile, const bf16* pool, const int* bt, int page_size,
+                                             int Hkv, int kvh, int j0, int rows, int lo, int hi,
+                                             int lane, int nthreads) {
+    for (int c = lane; c < rows * CHUNKS; c += nthreads) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        const int j = j0 + r;
+        bool pred = j >= lo && j <= hi;
+        const bf16* src = pool;
+        if (pred) {
+            const int page = bt[j / page_size];
+            pred = page >= 0;
+            if (pred) src = pool + (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * D + ch * 8;
+        }
+        cp_async16(tile + soff(r, ch), src, pred);
+    }
+}
+
+// ---------------------------------------------------------------------------------------- prefill
+constexpr int PF_M = 64;      // query rows per CTA (4 warps x 16)
+constexpr int PF_N = 64;      // keys per tile
+
+__global__ void __launch_bounds__(128)
+attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
+                    const bf16* __restrict__ vpool, const int* __restrict__ tiles,
+                    const int* __restrict__ cu_q, const int* __restrict__ seg_pos0,
+                    const int* __restrict__ block_table, int bt_stride, int page_size,
+                    bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
+    bf16* sK = sQ + PF_M * D;                 // two stages
+    bf16* sV = sK + 2 * PF_N * D;             // two stages
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int h = blockIdx.y, kvh = h / (Hq / Hkv);
+    const int seg = tiles[2 * blockIdx.x], row0 = tiles[2 * blockIdx.x + 1];
+    const int q_begin = cu_q[seg];
+    const int m_rows = min(PF_M, cu_q[seg + 1] - q_begin - row0);
+    const int p0 = seg_pos0[seg] + row0;      // position of the tile's first query
+    const int p_last = p0 + m_rows - 1;
+    const int lo_min = window > 0 ? max(0, p0 - window + 1) : 0;
+    const int jt_begin = lo_min / PF_N, jt_end = p_last / PF_N;
+    const int* bt = block_table + (size_t)seg * bt_stride;
+
+    for (int c = tid; c < PF_M * CHUNKS; c += 128) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        const bool pred = r < m_rows;
+        const bf16* src = pred ? q + (size_t)(q_begin + row0 + r) * ld + (size_t)h * D + ch * 8 : q;
+        cp_async16(sQ + soff(r, ch), src, pred);
+    }
+    load_kv_rows(sK, kpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, PF_N, lo_min, p_last, tid, 128);
+    load_kv_rows(sV, vpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, PF_N, lo_min, p_last, tid, 128);
+    cp_async_commit();
+
+    unsigned qf[KSTEPS][4];
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const int wrow = warp * 16;
+    const bool warp_active = wrow < m_rows;
+    const int pos_r0 = p0 + wrow + g, pos_r1 = pos_r0 + 8;          // positions of this thread's two rows
+
+    for (int jt = jt_begin; jt <= jt_end; ++jt) {
+        const int stage = (jt - jt_begin) & 1;
+        if (jt < jt_end) {
+            load_kv_rows(sK + (stage ^ 1) * PF_N * D, kpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, PF_N, lo_min, p_last, tid, 128);
+            load_kv_rows(sV + (stage ^ 1) * PF_N * D, vpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, PF_N, lo_min, p_last, tid, 128);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (jt == jt_begin) {
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk)
+                ldsm_x4(qf[kk], sQ + soff(wrow + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
+        }
+        const int j_base = jt * PF_N;
+        // a tile that starts above the warp's last row, or ends below its first row's window, adds nothing
+        const bool skip = !warp_active || j_base > p0 + wrow + 15 ||
+                          (window > 0 && j_base + PF_N - 1 <= p0 + wrow - window);
+        if (!skip) {
+            const bf16* tK = sK + stage * PF_N * D;
+            const bf16* tV = sV + stage * PF_N * D;
+            float s[PF_N / 8][4];
+#pragma unroll
+            for (int nt = 0; nt < PF_N / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+            for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+                for (int np = 0; np < PF_N / 16; ++np) {
+                    unsigned kf[4];
+                    ldsm_x4(kf, tK + soff(np * 16 + ((lane >> 4) << 3) + (lane & 7), 2 * kk + ((lane >> 3) & 1)));
+                    mma_bf16(s[2 * np], qf[kk], kf[0], kf[1]);
+                    mma_bf16(s[2 * np + 1], qf[kk], kf[2], kf[3]);
+                }
+            }
+            // scale, mask, running maximum
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < PF_N / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j_base + nt * 8 + 2 * t4 + (e & 1);
+                    const int pr = (e & 2) ? pos_r1 : pos_r0;
+                    const bool vis = j <= pr && (window <= 0 || j > pr - window);
+                    const float v = vis ? s[nt][e] * scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+                }
+            }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+            const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float a0 = exp2f(m_run[0] - mu0), a1 = exp2f(m_run[1] - mu1);
+            m_run[0] = mn0; m_run[1] = mn1;
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < PF_N / 8; ++nt) {
+                s[nt][0] = exp2f(s[nt][0] - mu0); s[nt][1] = exp2f(s[nt][1] - mu0);
+                s[nt][2] = exp2f(s[nt][2] - mu1); s[nt][3] = exp2f(s[nt][3] - mu1);
+                sum0 += s[nt][0] + s[nt][1];
+                sum1 += s[nt][2] + s[nt][3];
+            }
+            l_run[0] = l_run[0] * a0 + sum0;      // per-thread partial sums; quads are added at the end
+            l_run[1] = l_run[1] * a1 + sum1;
+#pragma unroll
+            for (int i = 0; i < DTILES; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+            // O += P V
+#pragma unroll
+            for (int ks = 0; ks < PF_N / 16; ++ks) {
+                unsigned pf[4];
+                pf[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+                pf[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+                pf[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+                pf[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+                for (int dp = 0; dp < DTILES / 2; ++dp) {
+                    unsigned vf[4];
+                    ldsm_x4_trans(vf, tV + soff(ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7), 2 * dp + (lane >> 4)));
+                    mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
+                    mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
+                }
+            }
+        }
+        __syncthreads();      // everyone is done with this stage before the next load overwrites it
+    }
+
+    if (!warp_active) return;
+    float l0 = l_run[0], l1 = l_run[1];
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.f / l0, inv1 = 1.f / l1;
+    const int r0 = wrow + g, r1 = r0 + 8;
+    const size_t ostride = (size_t)Hq * D;
+    bf16* orow0 = out + (size_t)(q_begin + row0 + r0) * ostride + (size_t)h * D;
+    bf16* orow1 = out + (size_t)(q_begin + row0 + r1) * ostride + (size_t)h * D;
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+        const int d = i * 8 + 2 * t4;
+        if (r0 < m_rows) *reinterpret_cast<unsigned*>(orow0 + d) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+        if (r1 < m_rows) *reinterpret_cast<unsigned*>(orow1 + d) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    }
+}
+
+// ---------------------------------------------------------------------------------------- decode
+constexpr int DC_WARPS = 4;
+constexpr int DC_STAGES = (D <= 128) ? 4 : 2;   // pipeline depth per warp, bounded by shared memory
+constexpr int DC_N = 16;      // keys per warp tile
+
+__global__ void __launch_bounds__(DC_WARPS * 32)
+attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
+                   const bf16* __restrict__ vpool, const int* __restrict__ dec_segs,
+                   const int* __restrict__ cu_q, const int* __restrict__ seg_kv_len,
+                   const int* __restrict__ block_table, int bt_stride, int page_size,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
+                   int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                    // 16 x D
+    bf16* sKV = sQ + 16 * D;                                         // [warp][stage][K 16xD | V 16xD]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int G = Hq / Hkv;
+    const int seg = dec_segs[blockIdx.x];
+    const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y - kvh * m_tiles;
+    const int split = blockIdx.z;
+    const int h0 = kvh * G + mt * 16;
+    const int rows_valid = min(16, G - mt * 16);
+    const int tok_row = cu_q[seg];
+    const int kv_len = seg_kv_len[seg];
+    const int lo = window > 0 ? max(0, kv_len - window) : 0;        // first visible key
+    const int hi = kv_len - 1;                                       // the query's own position
+    const int* bt = block_table + (size_t)seg * bt_stride;
+    const int first = lo / DC_N, n_tiles = hi / DC_N - first + 1;
+    const int per_split = (n_tiles + num_splits - 1) / num_splits;
+    const int t_begin = first + split * per_split;
+    const int t_end = min(first + n_tiles, t_begin + per_split);     // exclusive
+
+    for (int c = tid; c < 16 * CHUNKS; c += DC_WARPS * 32) {
+        const int r = c / CHUNKS, ch = c - r * CHUNKS;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < rows_valid) v = *reinterpret_cast<const uint4*>(q + (size_t)tok_row * ld + (size_t)(h0 + r) * D + ch * 8);
+        *reinterpret_cast<uint4*>(sQ + soff(r, ch)) = v;
+    }
+    __syncthreads();
+    unsigned qf[KSTEPS][4];
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk)
+        ldsm_x4(qf[kk], sQ + soff((lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    bf16* my = sKV + (size_t)warp * DC_STAGES * 2 * DC_N * D;
+    const int n_my = t_begin + warp < t_end ? (t_end - t_begin - warp + DC_WARPS - 1) / DC_WARPS : 0;
+    auto issue = [&](int i) {
+        bf16* st = my + (size_t)(i % DC_STAGES) * 2 * DC_N * D;
+        const int j0 = (t_begin + warp + i * DC_WARPS) * DC_N;
+        load_kv_rows(st, kpool, bt, page_size, Hkv, kvh, j0, DC_N, lo, hi, lane, 32);
+        load_kv_rows(st + DC_N * D, vpool, bt, page_size, Hkv, kvh, j0, DC_N, lo, hi, lane, 32);
+    };
+#pragma unroll
+    for (int s = 0; s < DC_STAGES - 1; ++s) {
+        if (s < n_my) issue(s);
+        cp_async_commit();
+    }
+    for (int i = 0; i < n_my; ++i) {
+        if (i + DC_STAGES - 1 < n_my) issue(i + DC_STAGES - 1);
+        cp_async_commit();
+        cp_async_wait<DC_STAGES - 1>();
+        __syncwarp();
+        const bf16* tK = my + (size_t)(i % DC_STAGES) * 2 * DC_N * D;
+        const bf16* tV = tK + DC_N * D;
+        const int j_base = (t_begin + warp + i * DC_WARPS) * DC_N;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            unsigned kf[4];
+            ldsm_x4(kf, tK + soff(((lane >> 4) << 3) + (lane & 7), 2 * kk + ((lane >> 3) & 1)));
+            mma_bf16(s[0], qf[kk], kf[0], kf[1]);
+            mma_bf16(s[1], qf[kk], kf[2], kf[3]);
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = j_base + nt * 8 + 2 * t4 + (e & 1);
+                const float v = (j >= lo && j <= hi) ? s[nt][e] * scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float a0 = exp2f(m_run[0] - mu0), a1 = exp2f(m_run[1] - mu1);
+        m_run[0] = mn0; m_run[1] = mn1;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            s[nt][0] = exp2f(s[nt][0] - mu0); s[nt][1] = exp2f(s[nt][1] - mu0);
+            s[nt][2] = exp2f(s[nt][2] - mu1); s[nt][3] = exp2f(s[nt][3] - mu1);
+            sum0 += s[nt][0] + s[nt][1];
+            sum1 += s[nt][2] + s[nt][3];
+        }
+        l_run[0] = l_run[0] * a0 + sum0;
+        l_run[1] = l_run[1] * a1 + sum1;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) { o[d][0] *= a0; o[d][1] *= a0; o[d][2] *= a1; o[d][3] *= a1; }
+        unsigned pf[4];
+        pf[0] = pack_bf16(s[0][0], s[0][1]);
+        pf[1] = pack_bf16(s[0][2], s[0][3]);
+        pf[2] = pack_bf16(s[1][0], s[1][1]);
+        pf[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {
+            unsigned vf[4];
+            ldsm_x4_trans(vf, tV + soff((((lane >> 3) & 1) << 3) + (lane & 7), 2 * dp + (lane >> 4)));
+            mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
+            mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                              // the pipeline buffers become merge buffers
+
+    float* mbuf = reinterpret_cast<float*>(sKV);                  // [warp][16] maxima, then [warp][16] sums
+    float* lbuf = mbuf + DC_WARPS * 16;
+    float* obuf = lbuf + DC_WARPS * 16;                           // [warp][16][D]
+    float l0 = l_run[0], l1 = l_run[1];
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (t4 == 0) {
+        mbuf[warp * 16 + g] = m_run[0]; mbuf[warp * 16 + g + 8] = m_run[1];
+        lbuf[warp * 16 + g] = l0;       lbuf[warp * 16 + g + 8] = l1;
+    }
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+        const int d = i * 8 + 2 * t4;
+        if (g < rows_valid) { obuf[(warp * 16 + g) * D + d] = o[i][0]; obuf[(warp * 16 + g) * D + d + 1] = o[i][1]; }
+        if (g + 8 < rows_valid) { obuf[(warp * 16 + g + 8) * D + d] = o[i][2]; obuf[(warp * 16 + g + 8) * D + d + 1] = o[i][3]; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < rows_valid * D; idx += DC_WARPS * 32) {
+        const int r = idx / D, d = idx - r * D;
+        float mg = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) mg = fmaxf(mg, mbuf[w * 16 + r]);
+        float lg = 0.f, og = 0.f;
+#pragma unroll
+        for (int w = 0; w < DC_WARPS; ++w) {
+            const float mw = mbuf[w * 16 + r];
+            const float sc = mw == -INFINITY ? 0.f : exp2f(mw - mg);
+            lg += lbuf[w * 16 + r] * sc;
+            og += obuf[(w * 16 + r) * D + d] * sc;
+        }
+        const int h = h0 + r;
+        if (num_splits == 1) {
+            out[(size_t)tok_row * Hq * D + (size_t)h * D + d] = __float2bfloat16_rn(og / lg);
+        } else {
+            const size_t pidx = ((size_t)blockIdx.x * Hq + h) * num_splits + split;
+            part_o[pidx * D + d] = og;
+            if (d == 0) { part_ml[pidx * 2] = mg; part_ml[pidx * 2 + 1] = lg; }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    const int* __restrict__ dec_segs, const int* __restrict__ cu_q,
+                    bf16* __restrict__ out, int Hq, int num_splits) {
+    const int i = blockIdx.x, h = blockIdx.y;
+    const int tok_row = cu_q[dec_segs[i]];
+    const size_t base = ((size_t)i * Hq + h) * num_splits;
+    float mg = -INFINITY;
+    for (int s = 0; s < num_splits; ++s) mg = fmaxf(mg, part_ml[(base + s) * 2]);
+    float lg = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        lg += ms == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(ms - mg);
+    }
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < num_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            if (ms != -INFINITY) acc += part_o[(base + s) * D + d] * exp2f(ms - mg);
+        }
+        out[(size_t)tok_row * Hq * D + (size_t)h * D + d] = __float2bfloat16_rn(acc / lg);
+    }
+}
+
+}  // namespace
+
+RB_EXPORT int rb_attn_head_dim() { return D; }
+
+RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
+                              int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
+                              int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale,
+                              int window, cudaStream_t st) {
+    if (n_tiles <= 0) return 0;
+    const size_t smem = (size_t)(PF_M + 4 * PF_N) * D * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(n_tiles, Hq);
+    attn_prefill_kernel<<<grid, 128, smem, st>>>((const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, tiles,
+                                                 cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
+                                                 Hq, Hkv, scale * LOG2E, window);
+    return rb_launch_status();
+}
+
+// Floats of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D], part_ml [n_dec, Hq, splits, 2].
+RB_EXPORT long long rb_attn_decode_scratch_floats(int n_dec, int Hq, int num_splits) {
+    return num_splits <= 1 ? 0 : (long long)n_dec * Hq * num_splits * (D + 2);
+}
+
+RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
+                             int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
+                             int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
+                             float scale, int window, int num_splits, cudaStream_t st) {
+    if (n_dec <= 0) return 0;
+    if (num_splits < 1 || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
+    const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
+    const size_t pipe = (size_t)DC_WARPS * DC_STAGES * 2 * DC_N * D * sizeof(bf16);
+    const size_t merge = (size_t)DC_WARPS * 16 * (D + 2) * sizeof(float);
+    const size_t smem = (size_t)16 * D * sizeof(bf16) + (pipe > merge ? pipe : merge);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_dec * Hq * num_splits * D : nullptr;
+    dim3 grid(n_dec, Hkv * m_tiles, num_splits);
+    attn_decode_kernel<<<grid, DC_WARPS * 32, smem, st>>>(
+        (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
+        bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits);
+    int rc = rb_launch_status();
+    if (rc != 0 || num_splits == 1) return rc;
+    dim3 cgrid(n_dec, Hq);
+    attn_combine_kernel<<<cgrid, 128, 0, st>>>(part_o, part_ml, dec_segs, cu_q, (bf16*)out, Hq, num_splits);
+    return rb_launch_status();
+}

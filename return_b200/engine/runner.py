@@ -60,7 +60,9 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> int:
-        return self.manager.add(rid)
+        slot = self.manager.add(rid)
+        self.storage.reset_slot(slot)
+        return slot
 
     def free_request(self, rid: Hashable) -> None:
         self.manager.free(rid)

@@ -75,9 +75,16 @@ def core() -> ctypes.CDLL:
     return _core
 
 
+# head sizes compiled ahead of time by build_all(); any other multiple of 16 compiles on first use
+PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
+
+
 def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
-    return [build.library_path("return_core", _CORE_SOURCES)]
+    paths = [build.library_path("return_core", _CORE_SOURCES)]
+    for d in PREBUILT_HEAD_DIMS:
+        paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], {"HEAD_DIM": d}))
+    return paths
 
 
 # ------------------------------------------------------------------------------- elementwise
@@ -193,6 +200,65 @@ def attention_simt(qkv, k_pool, v_pool, pos, tok_seg, block_table, page_size, ou
         head_dim, scale, int(window or 0), _stream()), "attention_simt")
 
 
+_attn_libs = {}
+
+
+def attention_lib(head_dim: int) -> ctypes.CDLL:
+    """The tensor-core attention kernels, compiled for this head size on first use."""
+    lib = _attn_libs.get(head_dim)
+    if lib is None:
+        if head_dim % 16 or not (16 <= head_dim <= 256):
+            raise KernelError(f"head_dim={head_dim}: the attention kernels take multiples of 16 from 16 to 256")
+        lib = build.load(f"return_attn_d{head_dim}", ["attention_mma.cu"], {"HEAD_DIM": head_dim})
+        P, I, F = c_void_p, c_int, c_float
+        lib.rb_attn_prefill.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P]
+        lib.rb_attn_decode.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P]
+        lib.rb_attn_decode_scratch_floats.argtypes = [I, I, I]
+        lib.rb_attn_decode_scratch_floats.restype = ctypes.c_longlong
+        lib.rb_attn_prefill.restype = lib.rb_attn_decode.restype = lib.rb_attn_head_dim.restype = c_int
+        if lib.rb_attn_head_dim() != head_dim:
+            raise KernelError("attention library was compiled for another head size")
+        _attn_libs[head_dim] = lib
+    return lib
+
+
+NUM_SMS = 148
+
+
+def decode_splits(n_ctas_base: int, max_kv_len: int) -> int:
+    """How many ways the keys of a decoded token are split: enough CTAs to fill the GPU, but at
+    least 128 keys per CTA."""
+    by_fill = (NUM_SMS + n_ctas_base - 1) // max(1, n_ctas_base)
+    by_work = max(1, (max_kv_len + 127) // 128)
+    return max(1, min(by_fill, by_work, 64))
+
+
+def attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
+                          num_kv_heads, head_dim, scale, window=0) -> None:
+    """Tensor-core attention for the listed (segment, first row) tiles of up to 64 query rows."""
+    assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
+    assert tiles.dtype == torch.int32 and tiles.is_contiguous()
+    lib = attention_lib(head_dim)
+    _check(lib.rb_attn_prefill(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles), tiles.shape[0],
+                               _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table), block_table.stride(0), page_size,
+                               _ptr(out), num_heads, num_kv_heads, scale, int(window or 0), _stream()),
+           "attention_prefill")
+
+
+def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, block_table, page_size, out,
+                         num_heads, num_kv_heads, head_dim, scale, window=0, num_splits=1) -> None:
+    """Tensor-core attention for segments of one token, the keys split ``num_splits`` ways."""
+    assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
+    lib = attention_lib(head_dim)
+    n = decode_segs.shape[0]
+    floats = lib.rb_attn_decode_scratch_floats(n, num_heads, num_splits)
+    scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device) if floats else None
+    _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
+                              _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
+                              _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
+                              num_splits, _stream()), "attention_decode")
+
+
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,
                     head_dim, scale, window=None) -> None:
     """Attention of every token of the step over its request's cached keys (its own included).
@@ -200,8 +266,24 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
     float32: the CUDA-core kernel, whose result does not depend on how the work was cut.
     bfloat16: the tensor-core kernels, one for prompt portions and one (split over the keys) for
     single decoded tokens."""
-    attention_simt(qkv, k_pool, v_pool, batch.pos, batch.tok_seg, block_table, page_size, out,
-                   num_heads, num_kv_heads, head_dim, scale, window or 0)
+    if qkv.dtype == torch.float32:
+        attention_simt(qkv, k_pool, v_pool, batch.pos, batch.tok_seg, block_table, page_size, out,
+                       num_heads, num_kv_heads, head_dim, scale, window or 0)
+        return
+    host = batch.host
+    if host.prefill_tiles.shape[0]:
+        attention_prefill_mma(qkv, k_pool, v_pool, batch.prefill_tiles, batch.cu_q, batch.seg_pos0, block_table,
+                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
+    n_dec = host.decode_segs.shape[0]
+    if n_dec:
+        group = num_heads // num_kv_heads
+        base = n_dec * num_kv_heads * ((group + 15) // 16)
+        longest = int(host.seg_kv_len[host.decode_segs].max())
+        if window:
+            longest = min(longest, int(window))
+        attention_decode_mma(qkv, k_pool, v_pool, batch.decode_segs, batch.cu_q, batch.seg_kv_len, block_table,
+                             page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
+                             decode_splits(base, longest))
 
 
 # ------------------------------------------------------------------------------- sampling

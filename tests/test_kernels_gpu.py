@@ -1,0 +1,395 @@
+"""Each CUDA kernel alone against its plain float32 reference, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+import helpers
+from helpers import plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _ops():
+    from return_b200.ext import ops
+    return ops
+
+
+def _tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+
+
+# ------------------------------------------------------------------------------- elementwise
+
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embedding(table_dtype):
+    ops = _ops()
+    V, H = 301, 136
+    table = torch.randn(V, H, device=DEV).to(table_dtype)
+    tokens = torch.randint(0, V, (37,), device=DEV, dtype=torch.int32)
+    out = torch.empty(37, H, device=DEV)
+    ops.embedding(table, tokens, out)
+    assert torch.equal(out, table[tokens.long()].float())
+    bad = torch.tensor([5, V, -1], device=DEV, dtype=torch.int32)      # outside the table: NaN, no foreign read
+    out = torch.zeros(3, H, device=DEV)
+    ops.embedding(table, bad, out)
+    assert torch.isfinite(out[0]).all() and torch.isnan(out[1:]).all()
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H", [24, 200, 4096 + 8])
+def test_add_rmsnorm(act, wdt, H):
+    ops = _ops()
+    T, eps = 19, 3e-5
+    stream = torch.randn(T, H, device=DEV)
+    delta = torch.randn(T, H, device=DEV).to(act)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(wdt)
+    want_stream = stream + delta.float()
+    want = plain.rms_norm(want_stream, w.float(), eps)
+    out = torch.empty(T, H, device=DEV, dtype=act)
+    s2 = stream.clone()
+    ops.add_rmsnorm(s2, delta, w, eps, out)
+    assert torch.allclose(s2, want_stream, atol=1e-6)
+    assert torch.allclose(out.float(), want, **_tol(act))
+    # no delta: the stream is only read
+    s3 = stream.clone()
+    ops.add_rmsnorm(s3, None, w, eps, out)
+    assert torch.equal(s3, stream)
+    assert torch.allclose(out.float(), plain.rms_norm(stream, w.float(), eps), **_tol(act))
+    # rows: only the listed rows, a row may be listed twice, the stream stays as it is
+    rows = torch.tensor([3, 3, 18, 0], device=DEV, dtype=torch.int32)
+    out4 = torch.empty(4, H, device=DEV, dtype=act)
+    s4 = stream.clone()
+    ops.add_rmsnorm(s4, delta, w, eps, out4, rows=rows)
+    assert torch.equal(s4, stream)
+    assert torch.allclose(out4.float(), want[rows.long()], **_tol(act))
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("N", [16, 48, 80, 256])
+def test_rmsnorm_rows(act, N):
+    ops = _ops()
+    x = torch.randn(7, 5, N, device=DEV).to(act)
+    w = (1 + 0.1 * torch.randn(N, device=DEV))
+    out = torch.empty_like(x)
+    ops.rmsnorm_rows(x, w, 1e-6, out, offset=1.0)
+    want = x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-6) * (1.0 + w)
+    assert torch.allclose(out.float(), want, **_tol(act))
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("I", [8, 100, 224, 1000])
+def test_swiglu(act, I):
+    ops = _ops()
+    gu = (3 * torch.randn(13, 2 * I, device=DEV)).to(act)
+    out = torch.empty(13, I, device=DEV, dtype=act)
+    ops.swiglu(gu, out)
+    g, u = gu.float()[:, :I], gu.float()[:, I:]
+    assert torch.allclose(out.float(), g * torch.sigmoid(g) * u, **_tol(act))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 257), (65, 64, 16), (100, 200, 96), (2, 384, 96)])
+def test_gemm_f32_is_exact_float32(M, N, K):
+    ops = _ops()
+    x = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV)
+    out = torch.empty(M, N, device=DEV)
+    ops.gemm_f32(x, w, out)
+    want = (x.double() @ w.double().T)
+    assert (out.double() - want).abs().max() < 1e-4 * max(1.0, K ** 0.5)
+    # a row's result does not depend on which other rows are in the product
+    one = torch.empty(1, N, device=DEV)
+    ops.gemm_f32(x[M - 1:M], w, one)
+    assert torch.equal(one[0], out[M - 1])
+    # no TF32: a value that TF32 would round away survives
+    x2 = torch.tensor([[1.0, 2.0 ** -12]], device=DEV)
+    w2 = torch.tensor([[1.0, 1.0]], device=DEV)
+    o2 = torch.empty(1, 1, device=DEV)
+    ops.gemm_f32(x2, w2, o2)
+    assert o2.item() == 1.0 + 2.0 ** -12
+
+
+def test_linear_bf16_float32_out():
+    ops = _ops()
+    x = torch.randn(5, 96, device=DEV).bfloat16()
+    w = torch.randn(384, 96, device=DEV).bfloat16()
+    out = torch.empty(5, 384, device=DEV)
+    ops.linear(x, w, out)
+    assert torch.allclose(out, x.float() @ w.float().T, atol=1e-3, rtol=1e-3)
+    with pytest.raises(ops.KernelError):
+        ops.linear(x.cpu(), w.cpu(), out.cpu())
+
+
+# ------------------------------------------------------------------------------- cache layout helpers
+
+class Paged:
+    """Random requests laid out in pages in a scrambled order, with the step's tables."""
+
+    def __init__(self, kv_lens, q_lens, Hq, Hkv, D, P, dtype, seed=0, poison=True):
+        g = torch.Generator().manual_seed(seed)
+        self.n = len(kv_lens)
+        self.Hq, self.Hkv, self.D, self.P = Hq, Hkv, D, P
+        self.kv_lens, self.q_lens = kv_lens, q_lens
+        blocks = [(L + P - 1) // P for L in kv_lens]
+        n_pages = sum(blocks) + 3
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.k = [torch.randn(L, Hkv, D, generator=g) for L in kv_lens]
+        self.v = [torch.randn(L, Hkv, D, generator=g) for L in kv_lens]
+        self.q = [torch.randn(ql, Hq, D, generator=g) for ql in q_lens]
+        fill = float("nan") if poison else 0.0
+        kpool = torch.full((n_pages, Hkv, P, D), fill)
+        vpool = torch.full((n_pages, Hkv, P, D), fill)
+        bt = torch.full((self.n, max(blocks)), -1, dtype=torch.int32)
+        it = iter(perm)
+        for i, L in enumerate(kv_lens):
+            for b in range(blocks[i]):
+                page = next(it)
+                bt[i, b] = page
+                rows = min(P, L - b * P)
+                kpool[page, :, :rows] = self.k[i][b * P:b * P + rows].transpose(0, 1)
+                vpool[page, :, :rows] = self.v[i][b * P:b * P + rows].transpose(0, 1)
+        self.kpool, self.vpool, self.bt = kpool.to(dtype).to(DEV), vpool.to(dtype).to(DEV), bt.to(DEV)
+        T = sum(q_lens)
+        qkv = torch.zeros(T, (Hq + 2 * Hkv) * D)
+        pos, tok_seg, cu_q = [], [], [0]
+        row = 0
+        for i, ql in enumerate(q_lens):
+            qkv[row:row + ql, :Hq * D] = self.q[i].reshape(ql, -1)
+            pos += list(range(kv_lens[i] - ql, kv_lens[i]))
+            tok_seg += [i] * ql
+            row += ql
+            cu_q.append(row)
+        self.qkv = qkv.to(dtype).to(DEV)
+        i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        self.pos, self.tok_seg, self.cu_q = i32(pos), i32(tok_seg), i32(cu_q)
+        self.seg_pos0 = i32([kv_lens[i] - q_lens[i] for i in range(self.n)])
+        self.seg_kv_len = i32(kv_lens)
+        self.dtype = dtype
+
+    def reference(self, scale, window=None):
+        outs = []
+        rd = lambda t: t.to(self.dtype).float()
+        for i in range(self.n):
+            L, ql = self.kv_lens[i], self.q_lens[i]
+            o = plain.attention_scores_softmax_pv(rd(self.q[i]), rd(self.k[i]), rd(self.v[i]),
+                                                  torch.arange(L - ql, L), torch.arange(L), scale, window)
+            outs.append(o.reshape(ql, -1))
+        return torch.cat(outs)
+
+
+ATT_SHAPES = [  # Hq, Hkv, D, P
+    (4, 2, 16, 16), (6, 3, 32, 8), (5, 1, 48, 16), (8, 8, 64, 4), (7, 7, 80, 32), (32, 8, 128, 16), (3, 1, 256, 64),
+    (20, 1, 64, 16),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D,P", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention_simt(dtype, Hq, Hkv, D, P, window):
+    ops = _ops()
+    pg = Paged([1, 70, 200, 33, 129], [1, 70, 1, 20, 3], Hq, Hkv, D, P, dtype, seed=D)
+    out = torch.empty(sum(pg.q_lens), Hq * D, device=DEV, dtype=dtype)
+    scale = 0.7 / math.sqrt(D)
+    ops.attention_simt(pg.qkv, pg.kpool, pg.vpool, pg.pos, pg.tok_seg, pg.bt, P, out, Hq, Hkv, D, scale, window or 0)
+    assert torch.allclose(out.float().cpu(), pg.reference(scale, window), **_tol(dtype))
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,P", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 100])
+def test_attention_prefill_mma(Hq, Hkv, D, P, window):
+    ops = _ops()
+    kv_lens, q_lens = [2, 70, 200, 64, 129, 300], [2, 70, 3, 64, 65, 130]
+    pg = Paged(kv_lens, q_lens, Hq, Hkv, D, P, torch.bfloat16, seed=D + 1)
+    tiles = [(i, r0) for i, ql in enumerate(q_lens) for r0 in range(0, ql, 64)]
+    tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    out = torch.full((sum(q_lens), Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 0.7 / math.sqrt(D)
+    ops.attention_prefill_mma(pg.qkv, pg.kpool, pg.vpool, tiles, pg.cu_q, pg.seg_pos0, pg.bt, P, out, Hq, Hkv, D,
+                              scale, window or 0)
+    assert torch.allclose(out.float().cpu(), pg.reference(scale, window), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,P", ATT_SHAPES)
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("splits", [1, 3, 8])
+def test_attention_decode_mma(Hq, Hkv, D, P, window, splits):
+    ops = _ops()
+    kv_lens = [1, 70, 200, 16, 129, 511, 17]
+    pg = Paged(kv_lens, [1] * len(kv_lens), Hq, Hkv, D, P, torch.bfloat16, seed=D + 2)
+    segs = torch.arange(len(kv_lens), dtype=torch.int32, device=DEV)
+    out = torch.full((len(kv_lens), Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 0.7 / math.sqrt(D)
+    ops.attention_decode_mma(pg.qkv, pg.kpool, pg.vpool, segs, pg.cu_q, pg.seg_kv_len, pg.bt, P, out, Hq, Hkv, D,
+                             scale, window or 0, num_splits=splits)
+    assert torch.allclose(out.float().cpu(), pg.reference(scale, window), atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_far_key_among_hundreds_and_the_windows_edge(dtype):
+    """Random keys would hide a wrong page or an off-by-one at the window's edge; here one key's score
+    stands out, so the output must be (almost exactly) that key's value."""
+    ops = _ops()
+    Hq, Hkv, D, P = 4, 2, 32, 16
+    L, W = 777, 200
+    for target, window, visible in ((5, None, True), (L - 1, None, True), (L - W, W, True), (L - W - 1, W, False),
+                                    (431, None, True)):
+        for q_len in (1, 3):
+            pg = Paged([L], [q_len], Hq, Hkv, D, P, dtype, seed=target)
+            # every query head points along the target key of its kv head, strongly
+            k_t = pg.k[0][target]                                     # [Hkv, D]
+            q = (30.0 * k_t / k_t.norm(dim=-1, keepdim=True)).repeat_interleave(Hq // Hkv, 0)
+            pg.qkv[:, :Hq * D] = q.reshape(1, -1).to(dtype).to(DEV)
+            pg.q = [q.unsqueeze(0).expand(q_len, Hq, D).contiguous()]
+            scale = 1.0
+            want = pg.reference(scale, window)
+            last_row_sees = visible
+            outs = []
+            o = torch.empty(q_len, Hq * D, device=DEV, dtype=dtype)
+            ops.attention_simt(pg.qkv, pg.kpool, pg.vpool, pg.pos, pg.tok_seg, pg.bt, P, o, Hq, Hkv, D, scale, window or 0)
+            outs.append(o)
+            if dtype == torch.bfloat16:
+                o2 = torch.empty_like(o)
+                if q_len == 1:
+                    ops.attention_decode_mma(pg.qkv, pg.kpool, pg.vpool, torch.zeros(1, dtype=torch.int32, device=DEV),
+                                             pg.cu_q, pg.seg_kv_len, pg.bt, P, o2, Hq, Hkv, D, scale, window or 0, num_splits=5)
+                else:
+                    ops.attention_prefill_mma(pg.qkv, pg.kpool, pg.vpool, torch.tensor([[0, 0]], dtype=torch.int32, device=DEV),
+                                              pg.cu_q, pg.seg_pos0, pg.bt, P, o2, Hq, Hkv, D, scale, window or 0)
+                outs.append(o2)
+            v_t = pg.v[0][target].repeat_interleave(Hq // Hkv, 0).reshape(-1)
+            for o in outs:
+                assert torch.allclose(o.float().cpu(), want, **_tol(dtype))
+                close = torch.allclose(o[-1].float().cpu(), v_t.to(dtype).float(), atol=5e-2)
+                assert close == last_row_sees
+
+
+# ------------------------------------------------------------------------------- rope + cache write
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D,P,rot", [(4, 2, 16, 16, 16), (6, 3, 32, 8, 32), (5, 1, 48, 16, 48), (3, 1, 80, 4, 32),
+                                             (32, 8, 128, 16, 128)])
+@pytest.mark.parametrize("with_norm", [True, False])
+def test_qk_norm_rope_write(dtype, Hq, Hkv, D, P, rot, with_norm):
+    ops = _ops()
+    g = torch.Generator().manual_seed(D)
+    starts, lens = [0, 37, 5], [20, 1, 9]
+    T = sum(lens)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
+    qw = (1 + 0.1 * torch.randn(D, generator=g)) if with_norm else None
+    kw = (1 + 0.1 * torch.randn(D, generator=g)) if with_norm else None
+    eps, theta = 2e-5, 5000.0
+    half = rot // 2
+    inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float32) / half))
+    ang = torch.outer(torch.arange(64, dtype=torch.float32), inv)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([s + i for s, L in zip(starts, lens) for i in range(L)], dtype=torch.int32)
+    tok_seg = torch.tensor([i for i, L in enumerate(lens) for _ in range(L)], dtype=torch.int32)
+    n_blocks = [(s + L + P - 1) // P for s, L in zip(starts, lens)]
+    perm = torch.randperm(sum(n_blocks) + 2, generator=g).tolist()
+    bt = torch.full((3, max(n_blocks)), -1, dtype=torch.int32)
+    it = iter(perm)
+    for i, nb in enumerate(n_blocks):
+        for b in range(nb):
+            bt[i, b] = next(it)
+    n_pages = sum(n_blocks) + 2
+    kpool = torch.full((n_pages, Hkv, P, D), float("nan"), dtype=dtype, device=DEV)
+    vpool = torch.full((n_pages, Hkv, P, D), float("nan"), dtype=dtype, device=DEV)
+    dev_qkv = qkv.clone().to(DEV)
+    ops.qk_norm_rope_write(dev_qkv, qw.to(DEV) if with_norm else None, kw.to(DEV) if with_norm else None, eps,
+                           cos.to(DEV), sin.to(DEV), rot, pos.to(DEV), tok_seg.to(DEV), bt.to(DEV), P, kpool, vpool,
+                           Hq, Hkv, D)
+
+    def norm_rot(x, w):                 # x [T, heads, D] float32
+        if w is not None:
+            x = plain.rms_norm(x, w, eps)
+        c, s = cos[pos.long()][:, None, :], sin[pos.long()][:, None, :]
+        x1, x2 = x[..., :half], x[..., half:rot]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, x[..., rot:]], -1)
+
+    x = qkv.float()
+    q_ref = norm_rot(x[:, :Hq * D].view(T, Hq, D), qw)
+    k_ref = norm_rot(x[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D), kw)
+    v_ref = x[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+    tol = _tol(dtype)
+    assert torch.allclose(dev_qkv[:, :Hq * D].float().cpu().view(T, Hq, D), q_ref, **tol)
+    written = torch.zeros(n_pages, P, dtype=torch.bool)
+    for t in range(T):
+        page, row = int(bt[tok_seg[t], pos[t] // P]), int(pos[t]) % P
+        written[page, row] = True
+        assert torch.allclose(kpool[page, :, row].float().cpu(), k_ref[t], **tol)
+        assert torch.equal(vpool[page, :, row].float().cpu(), v_ref[t])
+    # nothing else was touched
+    assert torch.isnan(kpool.float().cpu()[~written[:, None, :].expand(-1, Hkv, -1)]).all()
+    # without a cache write, k is normed and rotated in place and the pools stay as they are
+    dev2 = qkv.clone().to(DEV)
+    kp2 = torch.full_like(kpool, float("nan"))
+    ops.qk_norm_rope_write(dev2, qw.to(DEV) if with_norm else None, kw.to(DEV) if with_norm else None, eps,
+                           cos.to(DEV), sin.to(DEV), rot, pos.to(DEV), tok_seg.to(DEV), bt.to(DEV), P, kp2, kp2,
+                           Hq, Hkv, D, write_kv=False)
+    assert torch.isnan(kp2.float()).all()
+    assert torch.allclose(dev2[:, Hq * D:(Hq + Hkv) * D].float().cpu().view(T, Hkv, D), k_ref, **tol)
+
+
+# ------------------------------------------------------------------------------- sampling
+
+def test_argmax_and_greedy_rows():
+    ops = _ops()
+    V = 1531
+    logits = torch.randn(9, V, device=DEV)
+    logits[3, 77] = logits[3, 900] = 50.0                       # a tie: the lowest index wins
+    toks = torch.empty(9, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, toks)
+    want = logits.argmax(-1)
+    want[3] = 77
+    assert torch.equal(toks.long(), want)
+    temp = torch.zeros(9, device=DEV)
+    toks2 = torch.empty_like(toks)
+    lp = torch.empty(9, device=DEV)
+    ops.sample(logits, temp, torch.zeros(9, dtype=torch.int32, device=DEV), torch.ones(9, device=DEV),
+               torch.rand(9, device=DEV), toks2, lp)
+    assert torch.equal(toks2, toks)
+    ref_lp = torch.log_softmax(logits.double(), -1).gather(1, want[:, None])[:, 0]
+    assert torch.allclose(lp.double(), ref_lp, atol=1e-4)
+
+
+@pytest.mark.parametrize("V", [50, 1000, 151936])
+def test_sample_matches_the_filtered_distribution(V):
+    """The chosen token is the one whose interval of the kept distribution's CDF (vocabulary order) holds u."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(V)
+    n = 24
+    logits = (2.5 * torch.randn(n, V, generator=g))
+    temps = [0.8, 1.0, 1.3, 0.5] * 6
+    top_ks = [0, 0, 5, 40, 0, 1, 0, 3] * 3
+    top_ps = [1.0, 0.9, 1.0, 0.7, 0.3, 1.0, 0.05, 0.95] * 3
+    u = torch.rand(n, generator=g)
+    toks = torch.empty(n, dtype=torch.int32, device=DEV)
+    lp = torch.empty(n, device=DEV)
+    ops.sample(logits.to(DEV), torch.tensor(temps, device=DEV), torch.tensor(top_ks, dtype=torch.int32, device=DEV),
+               torch.tensor(top_ps, device=DEV), u.to(DEV), toks, lp)
+    for i in range(n):
+        probs = plain.filtered_probs(logits[i], temps[i], top_ks[i], top_ps[i])
+        tok = int(toks[i])
+        assert probs[tok] > 0, f"row {i}: token {tok} is outside the kept set"
+        cdf = probs.cumsum(0)
+        lo = float(cdf[tok] - probs[tok])
+        assert lo - 1e-4 <= float(u[i]) <= float(cdf[tok]) + 1e-4, (i, tok, lo, float(u[i]), float(cdf[tok]))
+        assert abs(float(lp[i]) - plain.logprob(logits[i], tok)) < 1e-3
+
+
+def test_sample_frequencies():
+    ops = _ops()
+    V, n = 12, 4000
+    logits = torch.tensor([2.0, 1.5, 1.0, 0.5, 0.0, -0.5, -1.0, -1.5, -2.0, -2.5, -3.0, -9.0])
+    probs = plain.filtered_probs(logits, 0.9, 6, 0.85)
+    rows = logits.repeat(n, 1).to(DEV)
+    toks = torch.empty(n, dtype=torch.int32, device=DEV)
+    ops.sample(rows, torch.full((n,), 0.9, device=DEV), torch.full((n,), 6, dtype=torch.int32, device=DEV),
+               torch.full((n,), 0.85, device=DEV), torch.rand(n, device=DEV), toks, None)
+    freq = torch.bincount(toks.long().cpu(), minlength=V).double() / n
+    assert (freq[probs == 0] == 0).all()
+    assert (freq - probs).abs().max() < 0.03

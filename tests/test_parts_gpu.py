@@ -1,0 +1,268 @@
+"""Each part alone against the plain implementation; schedules; and a toy architecture with a mixer
+that keeps state of its own, registered from here without touching the framework's files."""
+import dataclasses
+import math
+import os
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import helpers
+from helpers import plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _env(dtype):
+    from return_b200.parts import BuildEnv
+    return BuildEnv(dtype, torch.device(DEV))
+
+
+def _tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=4e-2, rtol=4e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_part(dtype):
+    from return_b200.parts import NORMS, NormSpec
+    norm = NORMS.build(NormSpec(size=72, eps=1e-5), _env(dtype))
+    assert list(norm.params()) == ["weight"] and norm.params()["weight"].shape == (72,)
+    w = 1 + 0.1 * torch.randn(72, device=DEV)
+    norm.bind({"weight": w})
+    x = torch.randn(11, 72, device=DEV).to(dtype)
+    out = torch.empty_like(x)
+    norm.forward(x, out)
+    assert torch.allclose(out.float(), plain.rms_norm(x.float(), w, 1e-5), **_tol(dtype))
+
+
+def test_rope_part_tables():
+    from return_b200.parts import POSITION_ENCODINGS, RopeSpec
+    rope = POSITION_ENCODINGS.build(RopeSpec(rotary_dim=48, theta=50000.0, max_positions=300), _env(torch.float32))
+    cos, sin, rot = rope.rotary_tables()
+    c, s = plain.rope_tables(torch.arange(300), 48, 50000.0)
+    assert rot == 48 and torch.equal(cos.cpu(), c) and torch.equal(sin.cpu(), s)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_feed_forward_part(dtype):
+    from return_b200.parts import FEED_FORWARDS, SwiGLUSpec
+    ff = FEED_FORWARDS.build(SwiGLUSpec(hidden_size=40, intermediate_size=104), _env(dtype))
+    assert {k: v.shape for k, v in ff.params().items()} == {"gate_up": (208, 40), "down": (40, 104)}
+    g, u, d = (0.2 * torch.randn(104, 40), 0.2 * torch.randn(104, 40), 0.2 * torch.randn(40, 104))
+    rd = lambda t: t.to(dtype).float()
+    ff.bind({"gate_up": torch.cat([g, u]).to(dtype).to(DEV), "down": d.to(dtype).to(DEV)})
+    x = torch.randn(9, 40).to(dtype)
+    y = ff.forward(x.to(DEV), None)
+    w = {"mlp.gate_proj.weight": rd(g), "mlp.up_proj.weight": rd(u), "mlp.down_proj.weight": rd(d)}
+    assert torch.allclose(y.float().cpu(), plain.swiglu_mlp(w, "", x.float()), **_tol(dtype))
+
+
+def _runner_for(spec, params, dtype, page_size=8, max_token=512, max_reside=4):
+    from return_b200.engine.config import EngineConfig
+    from return_b200.engine.runner import ModelRunner
+    from return_b200.models.decoder import DecoderModel
+    model = DecoderModel(spec, _env(dtype))
+    model.bind(params)
+    cfg = EngineConfig(max_token=max_token, max_reside=max_reside, page_size=page_size,
+                       dtype="float32" if dtype == torch.float32 else "bfloat16", use_cuda_graph=False, device=DEV)
+    r = ModelRunner(model, cfg, max_positions=max_token)
+    r.storage.poison()
+    return r
+
+
+def _params_from_dir(model_dir, spec, dtype):
+    from return_b200.config import registry
+    from return_b200.models.decoder import DecoderModel
+    from return_b200.weights import loader
+    arch, cfg = registry.read_config(model_dir)
+    model = DecoderModel(spec, _env(dtype))
+    expected = {n: s for n, (s, _) in loader.checkpoint_shapes(arch, cfg).items()}
+    # a spec with fewer or reordered layers still takes its parameters by name
+    params = loader.load_parameters(DecoderModel(arch.decoder_spec(cfg, 512), _env(dtype)).params(),
+                                    arch.weight_sources(cfg), expected, model_dir, dtype, DEV)
+    return {k: v for k, v in params.items() if k in model.params()}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ["A", "C"])
+def test_attention_part_and_block_alone(tmp_path, case, dtype):
+    """One block of the model, stepped in two portions, against plain.decoder_layer on the whole."""
+    from return_b200.config import registry
+    from return_b200.parts import LayerContext
+    d = helpers.make_model_dir(tmp_path, case)
+    arch, cfg = registry.read_config(d)
+    full = arch.decoder_spec(cfg, 512)
+    spec = dataclasses.replace(full, layers=full.layers[:1], schedule=full.schedule[:1])
+    runner = _runner_for(spec, _params_from_dir(d, spec, dtype), dtype, page_size=helpers.CASES[case][2])
+    c, w = plain.read_config(d), plain.read_weights(d)
+    T, H = 45, cfg.hidden_size
+    x = torch.randn(T, H)
+    want, _ = plain.decoder_layer(c, w, 0, x, torch.arange(T), plain.layer_windows(c)[0])
+    # the attention part alone: plain projections + attention + output projection of the normed input
+    a = plain.rms_norm(x, w["model.layers.0.input_layernorm.weight"], c["rms_norm_eps"])
+    q, k, v = plain.attention_project_qkv(c, w, "model.layers.0.", a, torch.arange(T))
+    o = plain.attention_scores_softmax_pv(q, k, v, torch.arange(T), torch.arange(T), c["head_dim"] ** -0.5,
+                                          plain.layer_windows(c)[0])
+    want_mixer = plain.linear(o.reshape(T, -1), w["model.layers.0.self_attn.o_proj.weight"])
+
+    from return_b200.engine.batch import StepBatch, build_host_batch
+    runner.add_request("r")
+    block = runner.model.blocks[0]
+    got, got_mixer = [], []
+    for lo, hi in ((0, 29), (29, T)):
+        entry = runner.reserve("r", [0] * (hi - lo))
+        batch = StepBatch(build_host_batch([entry], runner.manager), torch.device(DEV), runner.staging)
+        ctx = runner.storage.layer_context(0, batch, write=True)
+        got_mixer.append(block.mixer.forward(a[lo:hi].to(dtype).to(DEV), ctx).float().cpu())
+        stream = x[lo:hi].clone().to(DEV)
+        delta = block.forward(stream, None, ctx)
+        got.append((stream + delta.float()).cpu())
+    assert torch.allclose(torch.cat(got_mixer), want_mixer, **_tol(dtype))
+    assert torch.allclose(torch.cat(got), want, **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_schedule_names_a_layer_twice_and_shares_a_cache(tmp_path, dtype):
+    from return_b200.config import registry
+    from return_b200.parts import ScheduleEntry
+    d = helpers.make_model_dir(tmp_path, "A")
+    arch, cfg = registry.read_config(d)
+    base = arch.decoder_spec(cfg, 512)
+    ids = helpers.random_ids(256, 41, 9)
+    for sched, plain_sched in (
+            ((ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)), [(0, None), (1, None), (0, None)]),
+            ((ScheduleEntry(0), ScheduleEntry(1, cache_of=0)), [(0, None), (1, 0)]),
+            ((ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_of=0), ScheduleEntry(0, cache_of=1)),
+             [(1, None), (0, None), (1, 0), (0, 1)])):
+        spec = dataclasses.replace(base, schedule=sched)
+        runner = _runner_for(spec, _params_from_dir(d, spec, dtype), dtype, page_size=16)
+        owners = sum(1 for e in sched if e.cache_of is None)
+        assert runner.storage.pools[0].shape[0] == owners          # one cache layer per owning run
+        runner.add_request("r")
+        rows = []
+        for lo, hi in ((0, 17), (17, 18), (18, 41)):
+            e = runner.reserve("r", ids[lo:hi], list(range(hi - lo)))
+            rows.append(runner.step([e]).cpu())
+        want = helpers.plain_logits(d, ids, schedule=plain_sched)
+        tol = 1e-4 if dtype == torch.float32 else 6e-2
+        assert (torch.cat(rows) - want).abs().max() < tol
+
+
+# ------------------------------------------------------------------------------- a toy architecture
+
+@dataclass(frozen=True)
+class RunningMeanSpec:
+    hidden_size: int
+    kind: str = "running_mean"
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    num_hidden_layers: int
+    rms_norm_eps: float
+    architectures: tuple = ("ToyRunningMeanLM",)
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(raw["vocab_size"], raw["hidden_size"], raw["intermediate_size"], raw["num_hidden_layers"],
+                   raw["rms_norm_eps"])
+
+    def to_dict(self):
+        d = dataclasses.asdict(self)
+        d["architectures"] = list(self.architectures)
+        d["model_type"] = "toy_running_mean"
+        return d
+
+
+def _register_toy():
+    """A mixer whose state is the running sum of its inputs and their count: y_t = W mean(x_0..x_t)."""
+    from return_b200.config import registry
+    from return_b200.parts import MIXERS, BlockSpec, DecoderSpec, Mixer, NormSpec, ParamSpec, StateNeed, SwiGLUSpec
+    from return_b200.weights.loader import Source
+
+    class RunningMean(Mixer):
+        def params(self):
+            return {"w": ParamSpec((self.spec.hidden_size, self.spec.hidden_size))}
+
+        def cache_need(self):
+            return StateNeed((self.spec.hidden_size + 1,), torch.float32)
+
+        def forward(self, x, ctx):
+            host = ctx.batch.host
+            out = torch.empty_like(x)
+            H = self.spec.hidden_size
+            for i in range(host.num_segments):
+                a, b, slot = int(host.cu_q[i]), int(host.cu_q[i + 1]), int(host.seg_slot[i])
+                st = ctx.state[slot]
+                sums = x[a:b].float().cumsum(0) + st[:H]
+                counts = torch.arange(1, b - a + 1, device=x.device, dtype=torch.float32) + st[H]
+                out[a:b] = ((sums / counts[:, None]) @ self.p_w.float().T).to(x.dtype)
+                st[:H] = sums[-1]
+                st[H] = counts[-1]
+            return out
+
+    MIXERS.register("running_mean", RunningMean)
+
+    def decoder_spec(cfg, max_positions=None):
+        norm = NormSpec(cfg.hidden_size, cfg.rms_norm_eps)
+        block = BlockSpec(RunningMeanSpec(cfg.hidden_size), SwiGLUSpec(cfg.hidden_size, cfg.intermediate_size), norm, norm)
+        return DecoderSpec(cfg.vocab_size, cfg.hidden_size, (block,) * cfg.num_hidden_layers,
+                           DecoderSpec.in_order(cfg.num_hidden_layers), norm, tie_embeddings=True)
+
+    def weight_sources(cfg):
+        m = {"embed": Source(("tok.weight",)), "final_norm.weight": Source(("out_norm.weight",))}
+        for i in range(cfg.num_hidden_layers):
+            m[f"layers.{i}.mixer.w"] = Source((f"blocks.{i}.mean.w",))
+            m[f"layers.{i}.feed_forward.gate_up"] = Source((f"blocks.{i}.ff.gate", f"blocks.{i}.ff.up"))
+            m[f"layers.{i}.feed_forward.down"] = Source((f"blocks.{i}.ff.down",))
+            m[f"layers.{i}.mixer_norm.weight"] = Source((f"blocks.{i}.n1",))
+            m[f"layers.{i}.feed_forward_norm.weight"] = Source((f"blocks.{i}.n2",))
+        return m
+
+    registry.register_architecture(registry.Architecture(
+        name="ToyRunningMeanLM", model_type="toy_running_mean", config_cls=ToyConfig,
+        decoder_spec=decoder_spec, weight_sources=weight_sources))
+
+
+def _toy_reference(model_dir, cfg, ids):
+    from safetensors.torch import load_file
+    w = load_file(os.path.join(model_dir, "model.safetensors"))
+    x = w["tok.weight"][torch.tensor(ids)]
+    for i in range(cfg.num_hidden_layers):
+        a = plain.rms_norm(x, w[f"blocks.{i}.n1"], cfg.rms_norm_eps)
+        mean = a.cumsum(0) / torch.arange(1, len(ids) + 1)[:, None]
+        x = x + mean @ w[f"blocks.{i}.mean.w"].T
+        b = plain.rms_norm(x, w[f"blocks.{i}.n2"], cfg.rms_norm_eps)
+        g, u = b @ w[f"blocks.{i}.ff.gate"].T, b @ w[f"blocks.{i}.ff.up"].T
+        x = x + (g * torch.sigmoid(g) * u) @ w[f"blocks.{i}.ff.down"].T
+    return plain.rms_norm(x, w["out_norm.weight"], cfg.rms_norm_eps) @ w["tok.weight"].T
+
+
+def test_toy_mixer_with_state_of_its_own(tmp_path):
+    from return_b200.config import registry
+    from return_b200.engine.replay import TraceReplayer
+    from return_b200.parts import MIXERS
+    from return_b200.weights import loader
+    _register_toy()
+    try:
+        cfg = ToyConfig(vocab_size=90, hidden_size=24, intermediate_size=40, num_hidden_layers=2, rms_norm_eps=1e-5)
+        d = loader.write_random_model(os.path.join(str(tmp_path), "toy"), cfg, seed=11)
+        arch, read = registry.read_config(d)
+        assert arch.name == "ToyRunningMeanLM" and read == cfg
+        reqs = {f"t{i}": helpers.random_ids(90, n, 100 + i) for i, n in enumerate((30, 7, 19, 12, 25))}
+        steps = helpers.mixed(reqs, max_live=3, portion=6, decode_tail=3, seed=5)
+        rp = TraceReplayer(d, "float32", helpers.pool_tokens(steps), page_size=16, max_reside=3)
+        st = rp.runner.storage
+        assert len(st.states) == 2 and all(t.shape == (3, 25) for t in st.states.values())
+        got = helpers.collect(steps, [None if (lg := rp.run_step(s)) is None else lg.cpu() for s in steps])
+        for rid, ids in reqs.items():
+            assert (got[rid] - _toy_reference(d, cfg, ids)).abs().max() < 1e-4, rid
+        assert rp.runner.manager.free_slots == 3
+    finally:
+        registry.unregister_architecture("ToyRunningMeanLM")
+        MIXERS.unregister("running_mean")
