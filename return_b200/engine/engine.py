@@ -1,0 +1,202 @@
+"""The Python entry point: ``Engine`` generates tokens for requests on one GPU.
+
+In the reference's manner (rollout/engine.py:65-72,127-129,341-348): requests are ``Request``
+records with its field names, ``submit`` hands one in, ``stats()`` reports throughput counters,
+``KVCapacityError`` reports a pool that is too small.  The reference's engine is an asyncio task
+behind Ray actors; this one is a plain object with a synchronous ``generate`` and a step-wise
+interface (``add_request`` / ``step`` / ``has_unfinished``); ``AsyncEngine`` wraps it with the
+reference's ``start`` / ``await submit`` / ``release`` shape.
+"""
+from __future__ import annotations
+
+import asyncio
+import time
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+import torch
+
+from ..cache.manager import KVCapacityError
+from ..sampling.sampler import Sampler, uniform_draw
+from .config import EngineConfig
+from .request import GenerationResult, Request
+from .runner import ModelRunner
+from .scheduler import Scheduler, StepPlan
+
+
+class Engine:
+    def __init__(self, model: Union[str, ModelRunner], config: Optional[EngineConfig] = None, **overrides):
+        """``model``: a folder with config.json and model.safetensors (the model class is chosen by
+        config.json), or a ready ``ModelRunner``.  ``overrides`` are EngineConfig fields
+        (max_token, max_reside, page_size, prefill_chunk, dtype, seed, ...)."""
+        if isinstance(model, ModelRunner):
+            self.runner = model
+            self.config = model.config
+        else:
+            import dataclasses
+            self.config = dataclasses.replace(config or EngineConfig(), **overrides)
+            self.runner = ModelRunner.from_model_dir(model, self.config)
+        self.scheduler = Scheduler(self.runner.manager, self.config.prefill_chunk, self.runner.max_positions)
+        self.sampler = Sampler(self.runner.env.device, max(16, self.config.max_reside))
+        self._t_start = time.perf_counter()
+        self._acc_decode = self._acc_prefill = 0.0
+        self._dc_tok = self._pf_tok = 0
+        self._steps = self._preemptions = 0
+        self._auto_id = 0
+
+    # ------------------------------------------------------------------ step-wise interface
+    def add_request(self, req: Request) -> None:
+        if req.seed is None:
+            req.seed = (self.config.seed * 1000003 + self.scheduler._arrivals) & 0x7FFFFFFFFFFFFFFF
+        self.scheduler.add(req)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def step(self) -> List[Request]:
+        """One scheduling decision and one step of the model.  Returns the requests that ended in it
+        (finished, or failed with ``finish_reason == "error"``)."""
+        t0 = time.perf_counter()
+        plan: StepPlan = self.scheduler.schedule()
+        self._preemptions += len(plan.preempted)
+        ended = list(plan.failed)
+        if not plan.entries:
+            return ended
+        from .batch import StepEntry
+        entries, samplers = [], []
+        for e in plan.entries:
+            entries.append(StepEntry(e.request.id, e.tokens, [len(e.tokens) - 1] if e.sample else [], e.start))
+            if e.sample:
+                r = e.request
+                samplers.append((r, (r.temperature, r.top_k, r.top_p, uniform_draw(r.seed, len(r.output)))))
+        logits = self.runner.step(entries)
+        sampled: Dict[Hashable, tuple] = {}
+        if samplers:
+            toks, lps = self.sampler.sample(logits, [p for _, p in samplers])
+            for (r, _), t, lp in zip(samplers, toks, lps):
+                sampled[r.id] = (t, lp)
+        else:
+            torch.cuda.current_stream().synchronize()
+        ended += self.scheduler.commit(plan, sampled)
+        dt = time.perf_counter() - t0
+        n_dec = sum(1 for e in plan.entries if len(e.tokens) == 1 and e.sample and len(e.request.output) > 1)
+        n_pf = plan.num_tokens - n_dec
+        if n_pf:
+            self._acc_prefill += dt
+        else:
+            self._acc_decode += dt
+        self._dc_tok += n_dec
+        self._pf_tok += n_pf
+        self._steps += 1
+        return ended
+
+    # ------------------------------------------------------------------ whole generations
+    def generate(self, prompts: Sequence[Union[Request, Sequence[int]]], max_new_tokens: int = 32,
+                 temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0,
+                 stop_ids: Optional[List[List[int]]] = None, seed: Optional[int] = None) -> List[GenerationResult]:
+        """Generates for every prompt (token ids, or ``Request`` records with their own options) and
+        returns the results in the order given.  A request that cannot fit the pool raises
+        ``KVCapacityError``."""
+        reqs: List[Request] = []
+        for i, p in enumerate(prompts):
+            if isinstance(p, Request):
+                r = p
+            else:
+                r = Request(id=f"gen-{self._auto_id}", prompt_ids=list(p), max_new_tokens=max_new_tokens,
+                            temperature=temperature, top_p=top_p, top_k=top_k, stop_ids=list(stop_ids or []),
+                            seed=None if seed is None else seed + i)
+                self._auto_id += 1
+            self.add_request(r)
+            reqs.append(r)
+        while self.has_unfinished():
+            for r in self.step():
+                if r.finish_reason == "error" and r in reqs:
+                    raise r.error
+        return [GenerationResult(r.id, list(r.output), list(r.output_logprobs), len(r.output), r.finish_reason)
+                for r in reqs]
+
+    # ------------------------------------------------------------------ counters (rollout/engine.py:84-125,308-315)
+    @property
+    def run_time(self) -> float:
+        return time.perf_counter() - self._t_start
+
+    @property
+    def decode_tps(self):
+        return self._dc_tok / self._acc_decode if self._acc_decode > 0 else None
+
+    @property
+    def prefill_tps(self):
+        return self._pf_tok / self._acc_prefill if self._acc_prefill > 0 else None
+
+    def stats(self) -> dict:
+        m = self.runner.manager
+        rt = self.run_time
+        return {
+            "run_time": rt, "steps": self._steps,
+            "running": len(self.scheduler.running), "pending": len(self.scheduler.waiting),
+            "decode_tps": self.decode_tps, "prefill_tps": self.prefill_tps,
+            "decode_duty": self._acc_decode / rt if rt > 0 else 0.0,
+            "prefill_duty": self._acc_prefill / rt if rt > 0 else 0.0,
+            "preemptions": self._preemptions,
+            "page_used": m.pages_used()[0], "page_total": m.groups[0].num_pages,
+        }
+
+
+class AsyncEngine:
+    """The reference's calling shape: ``start()``, ``await submit(request)``, ``release(id)``, ``stats()``.
+
+    ``submit`` resolves when the request has finished and returns it; a request that cannot fit
+    raises ``KVCapacityError`` from ``submit``.  Steps run in a worker thread, as the reference runs
+    its model calls (rollout/engine.py:370,394).  A finished request holds nothing here, so
+    ``release`` has nothing to give back and exists for callers written against the reference."""
+
+    def __init__(self, engine: Engine):
+        self.engine = engine
+        self._futures: Dict[Hashable, asyncio.Future] = {}
+        self._wake = asyncio.Event()
+        self._task: Optional[asyncio.Task] = None
+
+    def start(self) -> None:
+        self._task = asyncio.get_running_loop().create_task(self._run())
+
+    async def stop(self) -> None:
+        if self._task is not None:
+            self._task.cancel()
+            try:
+                await self._task
+            except asyncio.CancelledError:
+                pass
+            self._task = None
+
+    async def submit(self, req: Request) -> Request:
+        fut = asyncio.get_running_loop().create_future()
+        try:
+            self.engine.add_request(req)
+        except Exception as e:          # too long for the pool: report to this caller only
+            fut.set_exception(e)
+            return await fut
+        self._futures[req.id] = fut
+        self._wake.set()
+        return await fut
+
+    def release(self, rid) -> None:
+        return None
+
+    def stats(self) -> dict:
+        return self.engine.stats()
+
+    async def _run(self) -> None:
+        while True:
+            self._wake.clear()
+            if not self.engine.has_unfinished():
+                await self._wake.wait()
+                continue
+            ended = await asyncio.to_thread(self.engine.step)
+            for r in ended:
+                fut = self._futures.pop(r.id, None)
+                if fut is None or fut.done():
+                    continue
+                if r.finish_reason == "error":
+                    fut.set_exception(r.error)
+                else:
+                    fut.set_result(r)
+            await asyncio.sleep(0)

@@ -1,0 +1,152 @@
+"""Generation through the Python entry point and the command line."""
+import asyncio
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+from helpers import plain
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(model_dir, dtype="float32", **kw):
+    from return_b200.engine.config import EngineConfig
+    from return_b200.engine.engine import Engine
+    base = dict(max_token=1024, max_reside=4, page_size=16, prefill_chunk=64, dtype=dtype, use_cuda_graph=False)
+    base.update(kw)
+    return Engine(model_dir, EngineConfig(**base))
+
+
+def _plain_greedy(model_dir, prompts, n, stop_ids=()):
+    c, w = plain.read_config(model_dir), plain.read_weights(model_dir)
+    return [plain.greedy_generate(c, w, p, n, stop_ids) for p in prompts]
+
+
+@pytest.mark.parametrize("case,lens,new,chunk", [("A", (5, 17, 33), 8, 64), ("B", (1, 9, 40, 71), 12, 13), ("C", (3, 50, 90), 10, 32)])
+def test_greedy_generation_equals_plain(tmp_path, case, lens, new, chunk):
+    d = helpers.make_model_dir(tmp_path, case)
+    vocab = helpers.CASES[case][0]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, 1 + i) for i, n in enumerate(lens)]
+    want = _plain_greedy(d, prompts, new)
+    eng = _engine(d, "float32", page_size=helpers.CASES[case][2], prefill_chunk=chunk)
+    got = eng.generate(prompts, max_new_tokens=new, temperature=0.0)
+    assert [r.output_ids for r in got] == want
+    assert all(r.finish_reason == "length" and r.num_tokens == new for r in got)
+    # the log-probabilities are those of the raw logits
+    c, w = plain.read_config(d), plain.read_weights(d)
+    ids = prompts[1] + got[1].output_ids
+    lg = plain.forward_logits(c, w, ids)
+    for k, (tok, lp) in enumerate(zip(got[1].output_ids, got[1].output_logprobs)):
+        assert abs(lp - plain.logprob(lg[len(prompts[1]) - 1 + k], tok)) < 1e-3
+    assert eng.runner.manager.pages_used() == [0] * len(eng.runner.manager.groups)
+    st = eng.stats()
+    assert st["steps"] > 0 and st["page_used"] == 0 and st["decode_tps"] is not None
+
+
+def test_bfloat16_greedy_mostly_equals_plain(tmp_path):
+    d = helpers.make_model_dir(tmp_path, "B")
+    prompts = [helpers.random_ids(384, n, 5 + i) for i, n in enumerate((9, 40, 71))]
+    want = _plain_greedy(d, prompts, 12)
+    got = _engine(d, "bfloat16", page_size=8).generate(prompts, max_new_tokens=12, temperature=0.0)
+    same = sum(a == b for r, w in zip(got, want) for a, b in zip(r.output_ids, w))
+    assert same >= 0.8 * 36, (same, [r.output_ids for r in got], want)
+    assert [r.output_ids[0] for r in got] == [w[0] for w in want]
+
+
+def test_stop_sequence(tmp_path):
+    d = helpers.make_model_dir(tmp_path, "B")
+    prompt = helpers.random_ids(384, 20, 3)
+    free = _plain_greedy(d, [prompt], 10)[0]
+    stop = [free[3:5]]
+    got = _engine(d).generate([prompt], max_new_tokens=10, temperature=0.0, stop_ids=stop)[0]
+    assert got.output_ids == free[:5] and got.finish_reason == "stop"
+
+
+def test_sampling_is_reproducible_and_independent_of_the_batch(tmp_path):
+    from return_b200.engine.request import Request
+    d = helpers.make_model_dir(tmp_path, "B")
+    prompts = [helpers.random_ids(384, n, 30 + i) for i, n in enumerate((1, 9, 40, 71))]
+    mk = lambda i: Request(f"s{i}", prompts[i], max_new_tokens=12, temperature=0.8, top_p=0.95, top_k=50, seed=100 + i)
+    together = _engine(d, page_size=8, prefill_chunk=13).generate([mk(i) for i in range(4)])
+    again = _engine(d, page_size=8, prefill_chunk=64).generate([mk(i) for i in range(4)])
+    alone = [_engine(d, page_size=8).generate([mk(i)])[0] for i in range(4)]
+    for a, b, c in zip(together, again, alone):
+        assert a.output_ids == b.output_ids == c.output_ids
+    assert len({tuple(r.output_ids) for r in together}) == 4
+    other = _engine(d, page_size=8).generate([Request("x", prompts[2], max_new_tokens=12, temperature=0.8, seed=999)])[0]
+    assert other.output_ids != together[2].output_ids
+    # sampled tokens lie in the kept set of the plain filter, and their log-probs are the raw ones
+    c, w = plain.read_config(d), plain.read_weights(d)
+    r = together[3]
+    lg = plain.forward_logits(c, w, prompts[3] + r.output_ids)
+    for k, tok in enumerate(r.output_ids):
+        row = lg[len(prompts[3]) - 1 + k]
+        assert plain.filtered_probs(row, 0.8, 50, 0.95)[tok] > 0
+        assert abs(r.output_logprobs[k] - plain.logprob(row, tok)) < 1e-3
+
+
+def test_pool_too_small_for_all_preempts_and_still_gives_the_same_tokens(tmp_path):
+    d = helpers.make_model_dir(tmp_path, "A")
+    prompts = [helpers.random_ids(256, n, 50 + i) for i, n in enumerate((30, 28, 25, 20))]
+    want = _plain_greedy(d, prompts, 24)
+    eng = _engine(d, max_token=160, max_reside=4, page_size=16, prefill_chunk=32)     # 10 pages for ~200 tokens
+    got = eng.generate(prompts, max_new_tokens=24, temperature=0.0)
+    assert [r.output_ids for r in got] == want
+    assert eng.stats()["preemptions"] > 0
+    eng.runner.manager.check()
+
+
+def test_request_larger_than_the_pool_raises(tmp_path):
+    from return_b200.cache.manager import KVCapacityError
+    d = helpers.make_model_dir(tmp_path, "A")
+    eng = _engine(d, max_token=64, page_size=16)
+    with pytest.raises(KVCapacityError):
+        eng.generate([list(range(70))], max_new_tokens=2)
+    with pytest.raises(KVCapacityError):
+        eng.generate([list(range(60))], max_new_tokens=10, temperature=0.0)       # outgrows the pool while decoding
+    assert eng.runner.manager.pages_used() == [0] and not eng.has_unfinished()
+    assert len(eng.generate([list(range(20))], max_new_tokens=4, temperature=0.0)[0].output_ids) == 4
+
+
+def test_async_engine_in_the_references_shape(tmp_path):
+    from return_b200.engine.engine import AsyncEngine
+    from return_b200.engine.request import Request
+    d = helpers.make_model_dir(tmp_path, "A")
+    prompts = [helpers.random_ids(256, n, 70 + i) for i, n in enumerate((5, 17, 33))]
+    want = _plain_greedy(d, prompts, 6)
+
+    async def main():
+        eng = AsyncEngine(_engine(d))
+        eng.start()
+        reqs = [Request(f"a{i}", p, max_new_tokens=6, temperature=0.0) for i, p in enumerate(prompts)]
+        done = await asyncio.gather(*(eng.submit(r) for r in reqs))
+        for r in done:
+            eng.release(r.id)
+        stats = eng.stats()
+        await eng.stop()
+        return done, stats
+
+    done, stats = asyncio.run(main())
+    assert [r.output for r in done] == want and stats["running"] == 0
+
+
+def test_command_line(tmp_path):
+    cfg_path = os.path.join(str(tmp_path), "config.json")
+    with open(cfg_path, "w") as f:
+        json.dump(helpers.tiny_config("B").to_dict(), f)
+    model = os.path.join(str(tmp_path), "model")
+    run = lambda *a: subprocess.run([sys.executable, "-m", "return_b200", *a], cwd=helpers.ROOT,
+                                    capture_output=True, text=True, timeout=600)
+    p = run("random-weights", "--config", cfg_path, "--seed", "2", "--out", model, "--dtype", "float32")
+    assert p.returncode == 0, p.stderr[-2000:]
+    prompt = helpers.random_ids(384, 9, 4)
+    p = run("generate", "--model", model, "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+            "--new", "5", "--temperature", "0", "--max-token", "256", "--max-reside", "2", "--page-size", "8")
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = json.loads(p.stdout.strip().splitlines()[-1])
+    assert out["output_ids"] == _plain_greedy(model, [prompt], 5)[0] and out["finish_reason"] == "length"
