@@ -174,3 +174,73 @@ class BatchStaging:
         i = (self._next - 1) % len(self._slots)
         if self._slots[i] is not None:
             self._slots[i][2].record()
+
+
+class _StaticHost:
+    """What the kernels' dispatch looks at on the host, for a captured decode step of n tokens."""
+
+    def __init__(self, n: int):
+        self.num_tokens = self.num_segments = self.num_want = n
+        self.decode_segs = np.arange(n, dtype=np.int32)
+        self.prefill_tiles = np.zeros((0, 2), np.int32)
+        self.cu_q = np.arange(n + 1, dtype=np.int32)
+        self.seg_slot = np.zeros(n, np.int32)
+        self.seg_kv_len = np.ones(n, np.int32)
+
+
+class StaticDecodeBatch:
+    """Tables of a step of exactly ``n`` single decoded tokens at fixed device addresses, so that the
+    step can be captured in a CUDA graph once and replayed with new contents.  The block tables
+    have a fixed width (``max_blocks`` of each group); the split count of the decode attention is
+    fixed too, because a captured launch cannot change its grid."""
+
+    def __init__(self, n: int, max_blocks: Sequence[int], device, fixed_decode_splits: int):
+        self.n = n
+        self.num_tokens = self.num_segments = self.num_want = n
+        self.fixed_decode_splits = fixed_decode_splits
+        self.host = _StaticHost(n)
+        self._max_blocks = list(max_blocks)
+        sizes = [n, n, n, n, n + 1, n, n, n, n] + [n * b for b in max_blocks]
+        offs, total = [], 0
+        for sz in sizes:
+            offs.append(total)
+            total += (sz + 3) // 4 * 4
+        self._pinned = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self._dev = torch.zeros(total, dtype=torch.int32, device=device)
+        hv = self._pinned.numpy()
+        names = ("tokens", "pos", "tok_seg", "seg_slot", "cu_q", "seg_pos0", "seg_kv_len", "want_rows", "decode_segs")
+        self._h = {}
+        for name, off, sz in zip(names, offs, sizes):
+            self._h[name] = hv[off:off + sz]
+            setattr(self, name, self._dev[off:off + sz])
+        self._h_bt, self.block_tables = [], []
+        for b, off in zip(max_blocks, offs[len(names):]):
+            self._h_bt.append(hv[off:off + n * b].reshape(n, b))
+            self.block_tables.append(self._dev[off:off + n * b].view(n, b))
+        self.prefill_tiles = torch.zeros((0, 2), dtype=torch.int32, device=device)
+        self._h["tok_seg"][:] = np.arange(n)
+        self._h["cu_q"][:] = np.arange(n + 1)
+        self._h["want_rows"][:] = np.arange(n)
+        self._h["decode_segs"][:] = np.arange(n)
+        self._h["seg_kv_len"][:] = 1
+        for bt in self._h_bt:
+            bt[:] = -1                       # before the first fill: no page is read or written
+        self._event = torch.cuda.Event()
+        self.upload()
+
+    def fill(self, host: HostBatch) -> None:
+        """Takes the contents of a packed decode step of n tokens."""
+        assert host.num_tokens == self.n and host.num_segments == self.n
+        self._event.synchronize()            # the copy that last read the pinned buffer is done
+        for name in ("tokens", "pos", "seg_slot", "seg_pos0", "seg_kv_len"):
+            self._h[name][:] = getattr(host, name)
+        for dst, src in zip(self._h_bt, host.block_tables):
+            if src.shape[1] > dst.shape[1]:
+                raise ValueError("a request is longer than the captured block table")
+            dst[:, :src.shape[1]] = src
+        self.host.seg_kv_len = host.seg_kv_len
+        self.upload()
+
+    def upload(self) -> None:
+        self._dev.copy_(self._pinned, non_blocking=True)
+        self._event.record()

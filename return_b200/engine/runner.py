@@ -20,7 +20,8 @@ from ..config import registry
 from ..models.decoder import DecoderModel
 from ..parts.base import BuildEnv
 from ..weights import loader
-from .batch import BatchStaging, StepBatch, StepEntry, build_host_batch
+from ..ext import ops
+from .batch import BatchStaging, StaticDecodeBatch, StepBatch, StepEntry, build_host_batch
 from .config import EngineConfig
 
 
@@ -36,6 +37,9 @@ class ModelRunner:
         self.storage.allocate()
         self.staging = BatchStaging(self.env.device)
         self.vocab_size = model.spec.vocab_size
+        self._graphs = {}                   # decode batch size -> (graph, static batch, static logits)
+        self._graph_pool = None
+        self.launches_per_replay = {}       # decode batch size -> kernels of this package in its graph
 
     # ------------------------------------------------------------------ building
     @classmethod
@@ -53,6 +57,25 @@ class ModelRunner:
         expected = {n: shape for n, (shape, _) in loader.checkpoint_shapes(arch, cfg).items()}
         params = loader.load_parameters(model.params(), arch.weight_sources(cfg), expected, model_dir,
                                         env.act_dtype, device, arch.ignorable_tensors(cfg))
+        model.bind(params)
+        runner = cls(model, engine_config, max_positions)
+        runner.model_config = cfg
+        return runner
+
+    @classmethod
+    def from_random(cls, cfg, engine_config: EngineConfig, seed: int = 0) -> "ModelRunner":
+        """A model of configuration ``cfg`` with random weights made on the device (no model folder)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("return_b200 runs on a CUDA device (B200, sm_100a); none is visible")
+        arch = registry.resolve(cfg.to_dict())
+        device = torch.device(engine_config.device)
+        env = BuildEnv(engine_config.act_dtype, device)
+        max_positions = engine_config.max_model_len or min(engine_config.max_token, 1 << 20)
+        model = DecoderModel(arch.decoder_spec(cfg, max_positions), env)
+        shapes = loader.checkpoint_shapes(arch, cfg)
+        with torch.cuda.device(device):
+            params = loader.random_parameters(model.params(), arch.weight_sources(cfg), shapes, seed,
+                                              env.act_dtype, device)
         model.bind(params)
         runner = cls(model, engine_config, max_positions)
         runner.model_config = cfg
@@ -83,5 +106,48 @@ class ModelRunner:
         """Runs the entries as one batch; float32 logits [wanted places, vocab], in entry order."""
         host = build_host_batch(entries, self.manager, self.vocab_size, self.max_positions)
         with torch.cuda.device(self.env.device):
+            if self.config.use_cuda_graph and host.num_tokens == host.num_segments and self.model.graph_safe:
+                return self._graphed_decode(host)
             batch = StepBatch(host, self.env.device, self.staging)
             return self.model.forward(batch, self.storage)
+
+    # ------------------------------------------------------------------ CUDA graphs for decode steps
+    def _graphed_decode(self, host) -> torch.Tensor:
+        """A step of single decoded tokens replays a graph captured for its batch size, as the
+        reference does (rollout/model.py:346-407); graphs are captured on first use."""
+        n = host.num_tokens
+        entry = self._graphs.get(n)
+        if entry is None:
+            entry = self._capture(n)
+        graph, static, logits = entry
+        static.fill(host)
+        graph.replay()
+        if host.num_want == n and (host.want_rows == range(n)).all():
+            return logits
+        return logits.index_select(0, torch.as_tensor(host.want_rows, dtype=torch.int64).to(logits.device))
+
+    def _capture(self, n: int):
+        max_blocks = [(self.max_positions + g.page_size - 1) // g.page_size for g in self.manager.groups]
+        # every mixer of a captured step sees the same fixed split count
+        static = StaticDecodeBatch(n, max_blocks, self.env.device, ops.decode_splits_for_graph(n))
+        side = torch.cuda.Stream(device=self.env.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                      # warm-up outside the capture
+            self.model.forward(static, self.storage)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(self.env.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self.model.forward(static, self.storage)
+        self.launches_per_replay[n] = ops.launch_count - before
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        self._graphs[n] = (graph, static, logits)
+        return self._graphs[n]
+
+    def capture_decode_graphs(self, batch_sizes=None) -> None:
+        """Captures the decode graphs ahead of the first request (the reference's ``build_graph``)."""
+        for n in (batch_sizes or range(1, self.config.max_reside + 1)):
+            if n not in self._graphs:
+                self._capture(n)

@@ -43,7 +43,13 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(code: int, what: str) -> None:
+# kernels of this package launched by this process (a captured graph counts once, at capture)
+launch_count = 0
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global launch_count
+    launch_count += kernels
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code} at launch")
 
@@ -233,6 +239,13 @@ def decode_splits(n_ctas_base: int, max_kv_len: int) -> int:
     return max(1, min(by_fill, by_work, 64))
 
 
+def decode_splits_for_graph(n_decode: int) -> int:
+    """The split count baked into a captured decode step of ``n_decode`` tokens.  It cannot follow
+    the lengths of the requests, so it is chosen to fill the GPU with eight kv-head groups a
+    request (more heads only add CTAs); splits that get no keys are neutral."""
+    return max(1, min((NUM_SMS + n_decode * 8 - 1) // (n_decode * 8), 16))
+
+
 def attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
                           num_kv_heads, head_dim, scale, window=0) -> None:
     """Tensor-core attention for the listed (segment, first row) tiles of up to 64 query rows."""
@@ -256,7 +269,7 @@ def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, blo
     _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
                               _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
                               _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
-                              num_splits, _stream()), "attention_decode")
+                              num_splits, _stream()), "attention_decode", 2 if num_splits > 1 else 1)
 
 
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,
@@ -281,9 +294,10 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
         longest = int(host.seg_kv_len[host.decode_segs].max())
         if window:
             longest = min(longest, int(window))
+        fixed = getattr(batch, "fixed_decode_splits", None)
         attention_decode_mma(qkv, k_pool, v_pool, batch.decode_segs, batch.cu_q, batch.seg_kv_len, block_table,
                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
-                             decode_splits(base, longest))
+                             fixed or decode_splits(base, longest))
 
 
 # ------------------------------------------------------------------------------- sampling

@@ -49,6 +49,10 @@ class DecoderModel:
             block.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
         self.final_norm.bind({k[len("final_norm."):]: v for k, v in tensors.items() if k.startswith("final_norm.")})
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+
     # ------------------------------------------------------------------ caches
     def cache_needs(self) -> List[object]:
         """Per schedule entry: what the run's mixer wants cached (None if it owns no cache)."""

@@ -73,6 +73,10 @@ class LayerContext:
 
 
 class Part:
+    # False for a part whose forward looks at the step's tables on the host (its launches then
+    # depend on the data, and a step that holds it is never captured in a CUDA graph)
+    graph_safe = True
+
     def __init__(self, spec, env: BuildEnv):
         self.spec = spec
         self.env = env

@@ -23,6 +23,10 @@ class PreNormBlock(Block):
         self._children = {"mixer": self.mixer, "feed_forward": self.feed_forward,
                           "mixer_norm": self.mixer_norm, "feed_forward_norm": self.feed_forward_norm}
 
+    @property
+    def graph_safe(self):
+        return all(part.graph_safe for part in self._children.values())
+
     def params(self):
         return {f"{child}.{name}": p for child, part in self._children.items()
                 for name, p in part.params().items()}

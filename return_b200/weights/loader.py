@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import hashlib
 import json
+import math
 import os
 from dataclasses import dataclass
 from typing import Dict, List, Set, Tuple
@@ -161,4 +162,28 @@ def checkpoint_shapes(arch, config) -> Dict[str, Tuple[Tuple[int, ...], str]]:
             rows = [spec.shape[0] // len(names)] * len(names)
         for n, r in zip(names, rows):
             out[n] = ((r,) + tuple(spec.shape[1:]), spec.init)
+    return out
+
+
+def random_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source],
+                      shapes: Dict[str, Tuple[Tuple[int, ...], str]], seed: int, act_dtype: torch.dtype,
+                      device) -> Dict[str, torch.Tensor]:
+    """Random parameters made on the device, without a model folder: for benchmarks of models too
+    large to write out first.  Same laws as ``write_random_model``, but the numbers come from the
+    device's generator, so they differ from those of a folder written with the same seed."""
+    out: Dict[str, torch.Tensor] = {}
+    for pname, spec in params.items():
+        dt = act_dtype
+        dst = torch.empty(spec.shape, dtype=dt, device=device)
+        row = 0
+        for n in sources[pname].names:
+            shp, init = shapes[n]
+            k = shp[0]
+            # large matrices are drawn in slabs so that the float32 temporary stays small
+            step = max(1, (1 << 26) // max(1, math.prod(shp[1:])))
+            for r0 in range(0, k, step):
+                r1 = min(k, r0 + step)
+                dst[row + r0:row + r1].copy_(random_tensor(seed, f"{n}:{r0}", (r1 - r0,) + tuple(shp[1:]), init, dt, device))
+            row += k
+        out[pname] = dst
     return out

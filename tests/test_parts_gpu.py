@@ -186,6 +186,8 @@ def _register_toy():
     from return_b200.weights.loader import Source
 
     class RunningMean(Mixer):
+        graph_safe = False          # forward walks the segments on the host
+
         def params(self):
             return {"w": ParamSpec((self.spec.hidden_size, self.spec.hidden_size))}
 
