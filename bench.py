@@ -90,6 +90,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers where memory or time needs it")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="a reduced run for profiling: only the decode steps, or only the prefill")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -118,6 +120,14 @@ def main():
     torch.cuda.synchronize()
     build_s = time.time() - t0
     hbm_gbs, bf16_tflops, peak_src = peaks()
+
+    if args.only != "all":
+        if args.only == "decode":
+            r = benchmark.decode_throughput(runner, args.batch, PROMPT_LEN, K, W)
+        else:
+            r = benchmark.prefill_throughput(runner, PROMPT_LEN, iters=K, warmup=W)
+        print(json.dumps({"only": args.only, "layers": args.layers, "batch": args.batch, **r}))
+        return 0
 
     clocks = ClockSampler()
     clocks.start()

@@ -61,23 +61,30 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-// Copies `rows` keys starting at absolute position j0 (rows of D elements) of one kv head into a
-// swizzled tile.  A key outside [lo, hi] (or on a page that was given back) is zero-filled and
-// never read.  `lane`/`nthreads`: the calling group's thread index and size.
+// Copies ROWS keys starting at absolute position j0 (rows of D elements) of one kv head into a
+// swizzled tile, with NTHREADS threads: a group of NTHREADS / ROWS threads owns a row, looks its
+// page up once, and its threads take neighbouring 16-byte chunks so that each 32-byte sector is
+// asked for once.  A key outside [lo, hi] (or on a page that was given back) is zero-filled and
+// never read.
+template <int ROWS, int NTHREADS>
 __device__ __forceinline__ void load_kv_rows(bf16* tile, const bf16* pool, const int* bt, int page_size,
-                                             int Hkv, int kvh, int j0, int rows, int lo, int hi,
-                                             int lane, int nthreads) {
-    for (int c = lane; c < rows * CHUNKS; c += nthreads) {
-        const int r = c / CHUNKS, ch = c - r * CHUNKS;
-        const int j = j0 + r;
-        bool pred = j >= lo && j <= hi;
-        const bf16* src = pool;
-        if (pred) {
-            const int page = bt[j / page_size];
-            pred = page >= 0;
-            if (pred) src = pool + (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * D + ch * 8;
-        }
-        cp_async16(tile + soff(r, ch), src, pred);
+                                             int Hkv, int kvh, int j0, int lo, int hi, int tid) {
+    constexpr int TPR = NTHREADS / ROWS;          // threads per row
+    constexpr int CPT = CHUNKS / TPR;             // chunks per thread
+    static_assert(NTHREADS % ROWS == 0 && CHUNKS % TPR == 0, "rows and chunks must divide evenly");
+    const int r = tid / TPR, sub = tid - r * TPR;
+    const int j = j0 + r;
+    bool pred = j >= lo && j <= hi;
+    const bf16* src = pool;
+    if (pred) {
+        const int page = bt[j / page_size];
+        pred = page >= 0;
+        if (pred) src = pool + (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * D;
+    }
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ch = c * TPR + sub;
+        cp_async16(tile + soff(r, ch), pred ? src + ch * 8 : pool, pred);
     }
 }
 
@@ -113,8 +120,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
         const bf16* src = pred ? q + (size_t)(q_begin + row0 + r) * ld + (size_t)h * D + ch * 8 : q;
         cp_async16(sQ + soff(r, ch), src, pred);
     }
-    load_kv_rows(sK, kpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, PF_N, lo_min, p_last, tid, 128);
-    load_kv_rows(sV, vpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, PF_N, lo_min, p_last, tid, 128);
+    load_kv_rows<PF_N, 128>(sK, kpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, lo_min, p_last, tid);
+    load_kv_rows<PF_N, 128>(sV, vpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, lo_min, p_last, tid);
     cp_async_commit();
 
     unsigned qf[KSTEPS][4];
@@ -129,8 +136,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     for (int jt = jt_begin; jt <= jt_end; ++jt) {
         const int stage = (jt - jt_begin) & 1;
         if (jt < jt_end) {
-            load_kv_rows(sK + (stage ^ 1) * PF_N * D, kpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, PF_N, lo_min, p_last, tid, 128);
-            load_kv_rows(sV + (stage ^ 1) * PF_N * D, vpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, PF_N, lo_min, p_last, tid, 128);
+            load_kv_rows<PF_N, 128>(sK + (stage ^ 1) * PF_N * D, kpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, lo_min, p_last, tid);
+            load_kv_rows<PF_N, 128>(sV + (stage ^ 1) * PF_N * D, vpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, lo_min, p_last, tid);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -234,8 +241,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------- decode
-constexpr int DC_WARPS = 4;
-constexpr int DC_STAGES = (D <= 128) ? 4 : 2;   // pipeline depth per warp, bounded by shared memory
+constexpr int DC_WARPS = (D <= 128) ? 8 : 4;
+constexpr int DC_STAGES = (D <= 128) ? 3 : 2;   // pipeline depth per warp, bounded by shared memory
 constexpr int DC_N = 16;      // keys per warp tile
 
 __global__ void __launch_bounds__(DC_WARPS * 32)
@@ -288,8 +295,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
     auto issue = [&](int i) {
         bf16* st = my + (size_t)(i % DC_STAGES) * 2 * DC_N * D;
         const int j0 = (t_begin + warp + i * DC_WARPS) * DC_N;
-        load_kv_rows(st, kpool, bt, page_size, Hkv, kvh, j0, DC_N, lo, hi, lane, 32);
-        load_kv_rows(st + DC_N * D, vpool, bt, page_size, Hkv, kvh, j0, DC_N, lo, hi, lane, 32);
+        load_kv_rows<DC_N, 32>(st, kpool, bt, page_size, Hkv, kvh, j0, lo, hi, lane);
+        load_kv_rows<DC_N, 32>(st + DC_N * D, vpool, bt, page_size, Hkv, kvh, j0, lo, hi, lane);
     };
 #pragma unroll
     for (int s = 0; s < DC_STAGES - 1; ++s) {
@@ -304,16 +311,23 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         const bf16* tK = my + (size_t)(i % DC_STAGES) * 2 * DC_N * D;
         const bf16* tV = tK + DC_N * D;
         const int j_base = (t_begin + warp + i * DC_WARPS) * DC_N;
-        float s[2][4];
-        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
-        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        float s[2][4], s2[2][4];                  // two chains over the head dim, added at the end
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s[0][e] = s[1][e] = s2[0][e] = s2[1][e] = 0.f; }
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
             unsigned kf[4];
             ldsm_x4(kf, tK + soff(((lane >> 4) << 3) + (lane & 7), 2 * kk + ((lane >> 3) & 1)));
-            mma_bf16(s[0], qf[kk], kf[0], kf[1]);
-            mma_bf16(s[1], qf[kk], kf[2], kf[3]);
+            if (kk & 1) {
+                mma_bf16(s2[0], qf[kk], kf[0], kf[1]);
+                mma_bf16(s2[1], qf[kk], kf[2], kf[3]);
+            } else {
+                mma_bf16(s[0], qf[kk], kf[0], kf[1]);
+                mma_bf16(s[1], qf[kk], kf[2], kf[3]);
+            }
         }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { s[0][e] += s2[0][e]; s[1][e] += s2[1][e]; }
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {

@@ -23,14 +23,44 @@ __global__ void embedding_kernel(const TW* __restrict__ table, const int* __rest
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_f32(src[i]);
 }
 
+// Sixteen bytes of the table per thread and iteration, for rows whose length allows it.
+template <typename TW>
+__global__ void embedding_vec_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                                     float* __restrict__ stream, int H, int V) {
+    constexpr int E = 16 / sizeof(TW);
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    float* dst = stream + (size_t)t * H;
+    const bool bad = id < 0 || id >= V;
+    const TW* src = table + (size_t)(bad ? 0 : id) * H;
+    for (int i = threadIdx.x * E; i < H; i += blockDim.x * E) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+        const TW* e = reinterpret_cast<const TW*>(&raw);
+        float out[E];
+#pragma unroll
+        for (int k = 0; k < E; ++k) out[k] = bad ? __int_as_float(0x7fc00000) : to_f32(e[k]);
+#pragma unroll
+        for (int k = 0; k < E; k += 4)
+            *reinterpret_cast<float4*>(dst + i + k) = make_float4(out[k], out[k + 1], out[k + 2], out[k + 3]);
+    }
+}
+
 RB_EXPORT int rb_embedding(const void* table, int table_dtype, const int* tokens, float* stream,
                            int T, int H, int V, cudaStream_t st) {
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (table_dtype == RB_F32)
-        embedding_kernel<float><<<T, threads, 0, st>>>((const float*)table, tokens, stream, H, V);
-    else
-        embedding_kernel<bf16><<<T, threads, 0, st>>>((const bf16*)table, tokens, stream, H, V);
+    const bool aligned = ((uintptr_t)table % 16) == 0 && ((uintptr_t)stream % 16) == 0;
+    if (table_dtype == RB_F32) {
+        if (aligned && H % 4 == 0)
+            embedding_vec_kernel<float><<<T, threads, 0, st>>>((const float*)table, tokens, stream, H, V);
+        else
+            embedding_kernel<float><<<T, threads, 0, st>>>((const float*)table, tokens, stream, H, V);
+    } else {
+        if (aligned && H % 8 == 0)
+            embedding_vec_kernel<bf16><<<T, threads, 0, st>>>((const bf16*)table, tokens, stream, H, V);
+        else
+            embedding_kernel<bf16><<<T, threads, 0, st>>>((const bf16*)table, tokens, stream, H, V);
+    }
     return rb_launch_status();
 }
 
@@ -65,10 +95,110 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ stream, const TA* __restr
         o[i] = from_f32<TA>(xrow[i] * rstd * (offset + load_as_f32(w, w_dtype, i)));
 }
 
+// The same, four elements per vector and up to VPT vectors per thread held in registers: every
+// load of a row is in flight at once, which is what a step of a few rows needs (it is bound by
+// the latency of one trip to memory, not by bandwidth).  Needs H % 4 == 0 and H <= 4 * VPT * threads.
+template <typename TA> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+        return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<unsigned*>(&a);
+        raw.y = *reinterpret_cast<unsigned*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename TA, typename TW, int VPT>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ stream, const TA* __restrict__ delta,
+                                       const int* __restrict__ rows, const TW* __restrict__ w,
+                                       float eps, float offset, TA* __restrict__ out, int H) {
+    __shared__ float scratch[33];
+    const int orow = blockIdx.x;
+    const int irow = rows ? rows[orow] : orow;
+    float* s = stream + (size_t)irow * H;
+    const TA* d = delta ? delta + (size_t)irow * H : nullptr;
+    const int nvec = H >> 2;
+    float4 x[VPT], wv[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = threadIdx.x + v * blockDim.x;
+        x[v] = i < nvec ? Vec4<float>::load(s + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (d) {
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int i = threadIdx.x + v * blockDim.x;
+            if (i < nvec) {
+                const float4 dv = Vec4<TA>::load(d + 4 * i);
+                x[v].x += dv.x; x[v].y += dv.y; x[v].z += dv.z; x[v].w += dv.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = threadIdx.x + v * blockDim.x;
+        wv[v] = i < nvec ? Vec4<TW>::load(w + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) ss += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
+    if (d && !rows) {
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int i = threadIdx.x + v * blockDim.x;
+            if (i < nvec) Vec4<float>::store(s + 4 * i, x[v]);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    TA* o = out + (size_t)orow * H;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int i = threadIdx.x + v * blockDim.x;
+        if (i < nvec)
+            Vec4<TA>::store(o + 4 * i, make_float4(x[v].x * rstd * (offset + wv[v].x), x[v].y * rstd * (offset + wv[v].y),
+                                                   x[v].z * rstd * (offset + wv[v].z), x[v].w * rstd * (offset + wv[v].w)));
+    }
+}
+
+template <typename TA, typename TW>
+static int launch_add_rmsnorm_vec(float* stream, const void* delta, const int* rows, const void* w, float eps,
+                                  float offset, void* out, int n_rows, int H, cudaStream_t st) {
+    const int nvec = H >> 2;
+    int threads = 128;
+    while (threads < 1024 && threads * 4 < nvec) threads <<= 1;
+    if (threads >= nvec)
+        add_rmsnorm_vec_kernel<TA, TW, 1><<<n_rows, threads, 0, st>>>(stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
+    else if (threads * 2 >= nvec)
+        add_rmsnorm_vec_kernel<TA, TW, 2><<<n_rows, threads, 0, st>>>(stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
+    else
+        add_rmsnorm_vec_kernel<TA, TW, 4><<<n_rows, threads, 0, st>>>(stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
+    return rb_launch_status();
+}
+
 RB_EXPORT int rb_add_rmsnorm(float* stream, const void* delta, const int* rows, const void* w,
                              int w_dtype, float eps, float offset, void* out, int act_dtype,
                              int n_rows, int H, cudaStream_t st) {
     if (n_rows <= 0) return 0;
+    const bool aligned = ((uintptr_t)stream % 16) == 0 && ((uintptr_t)delta % 16) == 0 &&
+                         ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0;
+    if (aligned && H % 4 == 0 && H <= 4 * 4 * 1024) {
+        if (act_dtype == RB_F32 && w_dtype == RB_F32) return launch_add_rmsnorm_vec<float, float>(stream, delta, rows, w, eps, offset, out, n_rows, H, st);
+        if (act_dtype == RB_F32) return launch_add_rmsnorm_vec<float, bf16>(stream, delta, rows, w, eps, offset, out, n_rows, H, st);
+        if (w_dtype == RB_F32) return launch_add_rmsnorm_vec<bf16, float>(stream, delta, rows, w, eps, offset, out, n_rows, H, st);
+        return launch_add_rmsnorm_vec<bf16, bf16>(stream, delta, rows, w, eps, offset, out, n_rows, H, st);
+    }
     const size_t smem = (size_t)(H + 33) * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     int threads = 128;

@@ -1,0 +1,137 @@
+// out[M, N] = x[M, K] * W[N, K]^T in bfloat16 for a handful of rows (M <= 64): the matrix products
+// of a decode step, which stream every weight once and are bound by HBM bandwidth.
+//
+// The weight matrix is the A operand of mma.sync.m16n8k16 (16 weight rows per warp), the tokens are
+// the B operand (8 tokens per instruction), so a product with few tokens wastes no tensor-core rows.
+// A CTA owns 16 weight rows; its 8 warps split K and add their partial sums through shared memory.
+// Every lane reads 16 contiguous bytes of a weight row and of a token row straight into registers:
+// within a block of 32 k the four 16-byte pieces of a row are handed to the MMA in a permuted
+// order, the same for both operands, which leaves the dot product unchanged and makes all loads
+// full 16-byte vectors without shared-memory staging.  Accumulation is float32.
+//
+// Needs K % 8 == 0 and 16-byte aligned rows (ldx, ldw multiples of 8 elements).
+#include "common.cuh"
+
+namespace {
+
+constexpr int SK_WARPS = 8;
+constexpr int SK_ROWS = 16;       // weight rows per CTA
+constexpr int SK_UNROLL = 4;      // k32 blocks in flight per warp
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {       // read once: do not keep in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int MT, typename TOut>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ out,
+                   int M, int N, int K, int ldx, int ldw, int ldo) {
+    __shared__ float red[SK_WARPS][SK_ROWS][8 * MT + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int n0 = blockIdx.x * SK_ROWS;
+    const int r0 = n0 + g, r1 = r0 + 8;
+    const bool ok0 = r0 < N, ok1 = r1 < N;
+    const bf16* w0 = w + (size_t)(ok0 ? r0 : 0) * ldw + 8 * t4;
+    const bf16* w1 = w + (size_t)(ok1 ? r1 : 0) * ldw + 8 * t4;
+    const bf16* xr[MT];
+    bool xok[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        const int m = mt * 8 + g;
+        xok[mt] = m < M;
+        xr[mt] = x + (size_t)(xok[mt] ? m : 0) * ldx + 8 * t4;
+    }
+    const int nkb = (K + 31) >> 5;
+    const int per = (nkb + SK_WARPS - 1) / SK_WARPS;
+    const int kb_begin = warp * per, kb_end = min(nkb, kb_begin + per);
+    float acc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    for (int kb = kb_begin; kb < kb_end; kb += SK_UNROLL) {
+        uint4 a0[SK_UNROLL], a1[SK_UNROLL], b[SK_UNROLL][MT];
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+            const int k = (kb + u) << 5;
+            const bool kin = kb + u < kb_end && k + 8 * t4 < K;
+            a0[u] = (kin && ok0) ? ld_stream16(w0 + k) : zero;
+            a1[u] = (kin && ok1) ? ld_stream16(w1 + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+            const int k = (kb + u) << 5;
+            const bool kin = kb + u < kb_end && k + 8 * t4 < K;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+                b[u][mt] = (kin && xok[mt]) ? __ldg(reinterpret_cast<const uint4*>(xr[mt] + k)) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                mma_bf16(acc[mt], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b[u][mt].x, b[u][mt].y);
+                mma_bf16(acc[mt], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[u][mt].z, b[u][mt].w);
+            }
+        }
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        red[warp][g][mt * 8 + 2 * t4] = acc[mt][0];
+        red[warp][g][mt * 8 + 2 * t4 + 1] = acc[mt][1];
+        red[warp][g + 8][mt * 8 + 2 * t4] = acc[mt][2];
+        red[warp][g + 8][mt * 8 + 2 * t4 + 1] = acc[mt][3];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < SK_ROWS * 8 * MT; idx += SK_WARPS * 32) {
+        const int n = idx & (SK_ROWS - 1), m = idx >> 4;
+        if (m < M && n0 + n < N) {
+            float s = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < SK_WARPS; ++wi) s += red[wi][n][m];
+            store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
+        }
+    }
+}
+
+template <int MT>
+int launch(const bf16* x, const bf16* w, void* out, int out_f32, int M, int N, int K, int ldx, int ldw, int ldo,
+           cudaStream_t st) {
+    const int grid = (N + SK_ROWS - 1) / SK_ROWS;
+    if (out_f32)
+        gemm_skinny_kernel<MT, float><<<grid, SK_WARPS * 32, 0, st>>>(x, w, (float*)out, M, N, K, ldx, ldw, ldo);
+    else
+        gemm_skinny_kernel<MT, bf16><<<grid, SK_WARPS * 32, 0, st>>>(x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
+    return rb_launch_status();
+}
+
+}  // namespace
+
+RB_EXPORT int rb_gemm_skinny_max_rows() { return 32; }
+
+RB_EXPORT int rb_gemm_skinny(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                             int ldx, int ldw, int ldo, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 32 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
+        return (int)cudaErrorInvalidValue;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)w;
+    if (M <= 8) return launch<1>(xp, wp, out, out_f32, M, N, K, ldx, ldw, ldo, st);
+    if (M <= 16) return launch<2>(xp, wp, out, out_f32, M, N, K, ldx, ldw, ldo, st);
+    return launch<4>(xp, wp, out, out_f32, M, N, K, ldx, ldw, ldo, st);
+}

@@ -26,7 +26,9 @@ __global__ void qk_norm_rope_write_kernel(
         TA* __restrict__ kpool, TA* __restrict__ vpool,
         int Hq, int Hkv, int D, int write_kv) {
     const int t = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);      // one warp per head
+    const int nwarps = gridDim.y * (blockDim.x >> 5);
     const int p = pos[t];
     const int half = rot_dim >> 1;
     const float* cs = cos_t + (size_t)p * half;
@@ -86,12 +88,14 @@ RB_EXPORT int rb_qk_norm_rope_write(
     if (T <= 0) return 0;
     if (rot_dim > D || (rot_dim & 1)) return (int)cudaErrorInvalidValue;
     const int threads = 128;
+    const int heads = write_kv ? Hq + 2 * Hkv : Hq + Hkv;
+    const dim3 grid(T, (heads + 3) / 4);
     if (act_dtype == RB_F32)
-        qk_norm_rope_write_kernel<float><<<T, threads, 0, st>>>(
+        qk_norm_rope_write_kernel<float><<<grid, threads, 0, st>>>(
             (float*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
             block_table, bt_stride, page_size, (float*)kpool, (float*)vpool, Hq, Hkv, D, write_kv);
     else
-        qk_norm_rope_write_kernel<bf16><<<T, threads, 0, st>>>(
+        qk_norm_rope_write_kernel<bf16><<<grid, threads, 0, st>>>(
             (bf16*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
             block_table, bt_stride, page_size, (bf16*)kpool, (bf16*)vpool, Hq, Hkv, D, write_kv);
     return rb_launch_status();

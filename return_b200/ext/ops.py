@@ -56,7 +56,7 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
 
 _core = None
 
-_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "rope_cache.cu", "attention_simt.cu", "sampling.cu"]
+_CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "rope_cache.cu", "attention_simt.cu", "sampling.cu"]
 
 
 def core() -> ctypes.CDLL:
@@ -70,6 +70,8 @@ def core() -> ctypes.CDLL:
         lib.rb_rmsnorm_rows.argtypes = [P, P, I, F, F, P, I, I, I, P]
         lib.rb_swiglu.argtypes = [P, P, I, I, I, P]
         lib.rb_gemm_f32.argtypes = [P, P, P, I, I, I, I, I, I, P]
+        lib.rb_gemm_skinny.argtypes = [P, P, P, I, I, I, I, I, I, I, P]
+        lib.rb_gemm_skinny.restype = c_int
         lib.rb_qk_norm_rope_write.argtypes = [P, I, P, P, I, F, F, P, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P]
         lib.rb_attention_simt.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, P]
         lib.rb_sample.argtypes = [P, I, I, I, P, P, P, P, P, P, P]
@@ -153,15 +155,34 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                               _stream()), "gemm_f32")
 
 
+SKINNY_MAX_ROWS = 32
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 32 in bfloat16: the weight-streaming kernel of decode steps."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+    assert w.shape[1] == K and out.shape == (M, N) and M <= SKINNY_MAX_ROWS
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(core().rb_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0, M, N, K,
+                                 x.stride(0), w.stride(0), out.stride(0), _stream()), "gemm_skinny")
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = x @ w^T.  float32: the engine's own FFMA kernel.  bfloat16 operands: cuBLAS with
-    float32 accumulation, output bfloat16 or float32 (``out``'s dtype)."""
+    """out = x @ w^T.  float32: the engine's own FFMA kernel.  bfloat16 with up to 32 rows: the
+    engine's weight-streaming kernel.  bfloat16 with more rows: cuBLAS with float32 accumulation.
+    The output is bfloat16 or float32 (``out``'s dtype)."""
     if x.dtype == torch.float32:
         gemm_f32(x, w, out)
         return
     if not x.is_cuda:
         raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    if (x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        gemm_skinny(x, w, out)
+        return
     if out.dtype == torch.float32:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:

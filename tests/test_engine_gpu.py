@@ -104,7 +104,7 @@ def test_pool_too_small_for_all_preempts_and_still_gives_the_same_tokens(tmp_pat
 def test_request_larger_than_the_pool_raises(tmp_path):
     from return_b200.cache.manager import KVCapacityError
     d = helpers.make_model_dir(tmp_path, "A")
-    eng = _engine(d, max_token=64, page_size=16)
+    eng = _engine(d, max_token=64, page_size=16, max_model_len=128)
     with pytest.raises(KVCapacityError):
         eng.generate([list(range(70))], max_new_tokens=2)
     with pytest.raises(KVCapacityError):

@@ -112,13 +112,35 @@ def test_gemm_f32_is_exact_float32(M, N, K):
     assert o2.item() == 1.0 + 2.0 ** -12
 
 
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("N,K", [(16, 32), (100, 72), (384, 96), (1000, 4096), (4104, 1544)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_skinny(M, N, K, out_dtype):
+    ops = _ops()
+    g = torch.Generator().manual_seed(M * 1000 + N)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16().to(DEV)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_skinny(x, w, out)
+    want = x.double() @ w.double().T
+    tol = 2e-3 if out_dtype == torch.float32 else 2e-2
+    assert (out.double() - want).abs().max() < tol
+    # a view with a row stride (the q part of a qkv buffer) works too
+    big = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    big[:, :K] = x
+    out2 = torch.empty_like(out)
+    ops.gemm_skinny(big[:, :K], w, out2)
+    assert torch.equal(out2, out)
+
+
 def test_linear_bf16_float32_out():
     ops = _ops()
-    x = torch.randn(5, 96, device=DEV).bfloat16()
-    w = torch.randn(384, 96, device=DEV).bfloat16()
-    out = torch.empty(5, 384, device=DEV)
-    ops.linear(x, w, out)
-    assert torch.allclose(out, x.float() @ w.float().T, atol=1e-3, rtol=1e-3)
+    for M in (5, 70):                      # few rows: the engine's kernel; more: the library
+        x = torch.randn(M, 96, device=DEV).bfloat16()
+        w = torch.randn(384, 96, device=DEV).bfloat16()
+        out = torch.empty(M, 384, device=DEV)
+        ops.linear(x, w, out)
+        assert torch.allclose(out, x.float() @ w.float().T, atol=1e-3, rtol=1e-3)
     with pytest.raises(ops.KernelError):
         ops.linear(x.cpu(), w.cpu(), out.cpu())
 
