@@ -8,6 +8,7 @@ sampling options are the fields of its ``Request`` (rollout/engine.py:17-21).
   generate        tokens for prompts given as ids (``--prompt-ids``) or drawn at random (``--prompt-len``)
   random-weights  write a model folder (config.json, model.safetensors) from a config.json and a seed
   bench           decode tokens/s per batch size and prefill tokens/s
+  kernel-bench    one kernel alone on random data
   replay          trace replay (what ``bin/trace_run`` does), from a file of JSON lines
 """
 from __future__ import annotations
@@ -89,6 +90,18 @@ def cmd_bench(args) -> int:
     return 0
 
 
+def cmd_kernel_bench(args) -> int:
+    from . import benchmark
+    fn = {"attention_decode": benchmark.kernel_attention_decode, "attention_prefill": benchmark.kernel_attention_prefill,
+          "gemm": benchmark.kernel_gemm}[args.kernel]
+    kw = {}
+    for item in args.set or []:
+        k, v = item.split("=")
+        kw[k] = int(v)
+    print(json.dumps(fn(**kw)))
+    return 0
+
+
 def cmd_replay(args) -> int:
     import torch
     from .engine.replay import TraceReplayer
@@ -138,6 +151,11 @@ def main(argv=None) -> int:
     b.add_argument("--steps", type=int, default=50)
     b.add_argument("--warmup", type=int, default=10)
     b.set_defaults(fn=cmd_bench)
+
+    k = sub.add_parser("kernel-bench", help="time one kernel alone on random data (for profiles)")
+    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm"])
+    k.add_argument("--set", action="append", help="an integer argument of the kernel case, e.g. batch=64 ctx=2048 M=8")
+    k.set_defaults(fn=cmd_kernel_bench)
 
     t = sub.add_parser("replay", help="trace replay from a file")
     t.add_argument("--model", required=True)
