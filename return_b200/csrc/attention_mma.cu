@@ -51,6 +51,25 @@ __device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16_u(unsigned smem_addr, const void* gmem, bool pred) {
+    const int bytes = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void ldsm_x4_u(unsigned (&r)[4], unsigned smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans_u(unsigned (&r)[4], unsigned smem_addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr));
+}
+// 2^x for x <= 0 (and -inf -> 0): the hardware approximation, two units in the last place
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -290,26 +309,59 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
     for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-    bf16* my = sKV + (size_t)warp * DC_STAGES * 2 * DC_N * D;
+    // Everything that depends on the lane only is worked out once: byte offsets of the ldmatrix
+    // rows inside a stage, and of the 16-byte chunks this lane copies.
+    constexpr unsigned TILE_BYTES = DC_N * D * 2;               // one K or V tile
+    constexpr unsigned STAGE_BYTES = 2 * TILE_BYTES;
+    const unsigned my_u = smem_u32(sKV) + warp * DC_STAGES * STAGE_BYTES;
+    unsigned koff[KSTEPS], voff[DTILES / 2];
+    {
+        const int row = ((lane >> 4) << 3) + (lane & 7), c0 = (lane >> 3) & 1;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) koff[kk] = (unsigned)(row * D + (((2 * kk + c0) ^ (row & SWZ)) << 3)) * 2u;
+    }
+    {
+        const int row = (((lane >> 3) & 1) << 3) + (lane & 7), c0 = lane >> 4;
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp)
+            voff[dp] = TILE_BYTES + (unsigned)(row * D + (((2 * dp + c0) ^ (row & SWZ)) << 3)) * 2u;
+    }
+    constexpr int CPT = CHUNKS / 2;                               // two lanes a row
+    const int lr = lane >> 1, lsub = lane & 1;
+    unsigned doff[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) doff[c] = (unsigned)(lr * D + (((2 * c + lsub) ^ (lr & SWZ)) << 3)) * 2u;
+
     const int n_my = t_begin + warp < t_end ? (t_end - t_begin - warp + DC_WARPS - 1) / DC_WARPS : 0;
-    auto issue = [&](int i) {
-        bf16* st = my + (size_t)(i % DC_STAGES) * 2 * DC_N * D;
-        const int j0 = (t_begin + warp + i * DC_WARPS) * DC_N;
-        load_kv_rows<DC_N, 32>(st, kpool, bt, page_size, Hkv, kvh, j0, lo, hi, lane);
-        load_kv_rows<DC_N, 32>(st + DC_N * D, vpool, bt, page_size, Hkv, kvh, j0, lo, hi, lane);
+    auto issue = [&](int i, int stage) {
+        const unsigned st = my_u + stage * STAGE_BYTES;
+        const int j = (t_begin + warp + i * DC_WARPS) * DC_N + lr;
+        bool pred = j >= lo && j <= hi;
+        size_t eoff = 0;
+        if (pred) {
+            const int page = bt[j / page_size];
+            pred = page >= 0;
+            if (pred) eoff = (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * D + lsub * 8;
+        }
+        const bf16* ks = kpool + eoff;
+        const bf16* vs = vpool + eoff;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) cp_async16_u(st + doff[c], ks + c * 16, pred);
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) cp_async16_u(st + TILE_BYTES + doff[c], vs + c * 16, pred);
     };
 #pragma unroll
     for (int s = 0; s < DC_STAGES - 1; ++s) {
-        if (s < n_my) issue(s);
+        if (s < n_my) issue(s, s);
         cp_async_commit();
     }
+    int stage = 0, fill_stage = DC_STAGES - 1;
     for (int i = 0; i < n_my; ++i) {
-        if (i + DC_STAGES - 1 < n_my) issue(i + DC_STAGES - 1);
+        if (i + DC_STAGES - 1 < n_my) issue(i + DC_STAGES - 1, fill_stage);
         cp_async_commit();
         cp_async_wait<DC_STAGES - 1>();
         __syncwarp();
-        const bf16* tK = my + (size_t)(i % DC_STAGES) * 2 * DC_N * D;
-        const bf16* tV = tK + DC_N * D;
+        const unsigned tile = my_u + stage * STAGE_BYTES;
         const int j_base = (t_begin + warp + i * DC_WARPS) * DC_N;
         float s[2][4], s2[2][4];                  // two chains over the head dim, added at the end
 #pragma unroll
@@ -317,7 +369,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
             unsigned kf[4];
-            ldsm_x4(kf, tK + soff(((lane >> 4) << 3) + (lane & 7), 2 * kk + ((lane >> 3) & 1)));
+            ldsm_x4_u(kf, tile + koff[kk]);
             if (kk & 1) {
                 mma_bf16(s2[0], qf[kk], kf[0], kf[1]);
                 mma_bf16(s2[1], qf[kk], kf[2], kf[3]);
@@ -326,17 +378,27 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
                 mma_bf16(s[1], qf[kk], kf[2], kf[3]);
             }
         }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { s[0][e] += s2[0][e]; s[1][e] += s2[1][e]; }
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        if (j_base >= lo && j_base + DC_N - 1 <= hi) {            // every key of the tile is visible
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+            for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = j_base + nt * 8 + 2 * t4 + (e & 1);
-                const float v = (j >= lo && j <= hi) ? s[nt][e] * scale_log2 : -INFINITY;
-                s[nt][e] = v;
-                if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+                for (int e = 0; e < 4; ++e) {
+                    const float v = (s[nt][e] + s2[nt][e]) * scale_log2;
+                    s[nt][e] = v;
+                    if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = j_base + nt * 8 + 2 * t4 + (e & 1);
+                    const float v = (j >= lo && j <= hi) ? (s[nt][e] + s2[nt][e]) * scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
+                }
             }
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -345,20 +407,25 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
         const float mu0 = mn0 == -INFINITY ? 0.f : mn0, mu1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float a0 = exp2f(m_run[0] - mu0), a1 = exp2f(m_run[1] - mu1);
-        m_run[0] = mn0; m_run[1] = mn1;
+        // the accumulators are rescaled only when a running maximum moved (it rarely does after the first tiles)
+        if (__any_sync(0xffffffffu, mn0 != m_run[0] || mn1 != m_run[1])) {
+            const float a0 = fast_exp2(m_run[0] - mu0), a1 = fast_exp2(m_run[1] - mu1);
+            l_run[0] *= a0;
+            l_run[1] *= a1;
+#pragma unroll
+            for (int d = 0; d < DTILES; ++d) { o[d][0] *= a0; o[d][1] *= a0; o[d][2] *= a1; o[d][3] *= a1; }
+            m_run[0] = mn0; m_run[1] = mn1;
+        }
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - mu0); s[nt][1] = exp2f(s[nt][1] - mu0);
-            s[nt][2] = exp2f(s[nt][2] - mu1); s[nt][3] = exp2f(s[nt][3] - mu1);
+            s[nt][0] = fast_exp2(s[nt][0] - mu0); s[nt][1] = fast_exp2(s[nt][1] - mu0);
+            s[nt][2] = fast_exp2(s[nt][2] - mu1); s[nt][3] = fast_exp2(s[nt][3] - mu1);
             sum0 += s[nt][0] + s[nt][1];
             sum1 += s[nt][2] + s[nt][3];
         }
-        l_run[0] = l_run[0] * a0 + sum0;
-        l_run[1] = l_run[1] * a1 + sum1;
-#pragma unroll
-        for (int d = 0; d < DTILES; ++d) { o[d][0] *= a0; o[d][1] *= a0; o[d][2] *= a1; o[d][3] *= a1; }
+        l_run[0] += sum0;
+        l_run[1] += sum1;
         unsigned pf[4];
         pf[0] = pack_bf16(s[0][0], s[0][1]);
         pf[1] = pack_bf16(s[0][2], s[0][3]);
@@ -367,11 +434,13 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
 #pragma unroll
         for (int dp = 0; dp < DTILES / 2; ++dp) {
             unsigned vf[4];
-            ldsm_x4_trans(vf, tV + soff((((lane >> 3) & 1) << 3) + (lane & 7), 2 * dp + (lane >> 4)));
+            ldsm_x4_trans_u(vf, tile + voff[dp]);
             mma_bf16(o[2 * dp], pf, vf[0], vf[1]);
             mma_bf16(o[2 * dp + 1], pf, vf[2], vf[3]);
         }
         __syncwarp();
+        stage = stage + 1 == DC_STAGES ? 0 : stage + 1;
+        fill_stage = fill_stage + 1 == DC_STAGES ? 0 : fill_stage + 1;
     }
     cp_async_wait<0>();
     __syncthreads();                                              // the pipeline buffers become merge buffers

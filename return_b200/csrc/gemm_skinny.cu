@@ -16,7 +16,6 @@ namespace {
 
 constexpr int SK_WARPS = 8;
 constexpr int SK_ROWS = 16;       // weight rows per CTA
-constexpr int SK_UNROLL = 4;      // k32 blocks in flight per warp
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {       // read once: do not keep in L1
     uint4 v;
@@ -36,10 +35,16 @@ template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+template <int MT, int U>
+struct Regs {                         // one buffer: U blocks of 32 k of the weight rows and of the tokens
+    uint4 a0[U], a1[U], b[U][MT];
+};
+
 template <int MT, typename TOut>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ out,
                    int M, int N, int K, int ldx, int ldw, int ldo) {
+    constexpr int U = MT == 1 ? 4 : 2;                    // k32 blocks per buffer; two buffers in flight
     __shared__ float red[SK_WARPS][SK_ROWS][8 * MT + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
@@ -64,31 +69,40 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
     for (int mt = 0; mt < MT; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    for (int kb = kb_begin; kb < kb_end; kb += SK_UNROLL) {
-        uint4 a0[SK_UNROLL], a1[SK_UNROLL], b[SK_UNROLL][MT];
+    auto load = [&](Regs<MT, U>& r, int kb) {            // blocks past the warp's slice load zeros
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int k = (kb + u) << 5;
             const bool kin = kb + u < kb_end && k + 8 * t4 < K;
-            a0[u] = (kin && ok0) ? ld_stream16(w0 + k) : zero;
-            a1[u] = (kin && ok1) ? ld_stream16(w1 + k) : zero;
+            r.a0[u] = (kin && ok0) ? ld_stream16(w0 + k) : zero;
+            r.a1[u] = (kin && ok1) ? ld_stream16(w1 + k) : zero;
         }
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int k = (kb + u) << 5;
             const bool kin = kb + u < kb_end && k + 8 * t4 < K;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
-                b[u][mt] = (kin && xok[mt]) ? __ldg(reinterpret_cast<const uint4*>(xr[mt] + k)) : zero;
+                r.b[u][mt] = (kin && xok[mt]) ? __ldg(reinterpret_cast<const uint4*>(xr[mt] + k)) : zero;
         }
+    };
+    auto compute = [&](const Regs<MT, U>& r) {
 #pragma unroll
-        for (int u = 0; u < SK_UNROLL; ++u) {
+        for (int u = 0; u < U; ++u) {
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-                mma_bf16(acc[mt], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b[u][mt].x, b[u][mt].y);
-                mma_bf16(acc[mt], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[u][mt].z, b[u][mt].w);
+                mma_bf16(acc[mt], r.a0[u].x, r.a1[u].x, r.a0[u].y, r.a1[u].y, r.b[u][mt].x, r.b[u][mt].y);
+                mma_bf16(acc[mt], r.a0[u].z, r.a1[u].z, r.a0[u].w, r.a1[u].w, r.b[u][mt].z, r.b[u][mt].w);
             }
         }
+    };
+    Regs<MT, U> ra, rb;
+    load(ra, kb_begin);
+    for (int kb = kb_begin; kb < kb_end; kb += 2 * U) {  // the next buffer is in flight while one is used
+        load(rb, kb + U);
+        compute(ra);
+        load(ra, kb + 2 * U);
+        compute(rb);
     }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {

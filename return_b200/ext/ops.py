@@ -253,18 +253,26 @@ NUM_SMS = 148
 
 
 def decode_splits(n_ctas_base: int, max_kv_len: int) -> int:
-    """How many ways the keys of a decoded token are split: enough CTAs to fill the GPU, but at
-    least 128 keys per CTA."""
-    by_fill = (NUM_SMS + n_ctas_base - 1) // max(1, n_ctas_base)
-    by_work = max(1, (max_kv_len + 127) // 128)
-    return max(1, min(by_fill, by_work, 64))
+    """How many ways the keys of a decoded token are split.  One CTA runs per SM, so the time of
+    the launch goes with (waves of CTAs) x (keys per CTA); the split count that makes this
+    smallest wins, with at least 128 keys per CTA and the smaller count on a tie."""
+    tiles = max(1, (max_kv_len + 15) // 16)
+    best, best_cost = 1, None
+    for s in range(1, 65):
+        if s > 1 and (max_kv_len + s - 1) // s < 128:
+            break
+        waves = (n_ctas_base * s + NUM_SMS - 1) // NUM_SMS
+        cost = waves * ((tiles + s - 1) // s + 4)          # + a few tiles' worth of fixed work per CTA
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def decode_splits_for_graph(n_decode: int) -> int:
     """The split count baked into a captured decode step of ``n_decode`` tokens.  It cannot follow
     the lengths of the requests, so it is chosen to fill the GPU with eight kv-head groups a
     request (more heads only add CTAs); splits that get no keys are neutral."""
-    return max(1, min((NUM_SMS + n_decode * 8 - 1) // (n_decode * 8), 16))
+    return decode_splits(n_decode * 8, 4096)
 
 
 def attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
