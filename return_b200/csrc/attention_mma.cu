@@ -80,13 +80,50 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
+// Position -> (block, row in page).  Page sizes are powers of two in practice; any size works.
+struct Paging {
+    int page_size, shift;                       // shift < 0: not a power of two
+    __device__ __forceinline__ explicit Paging(int p) : page_size(p), shift(-1) {
+        if ((p & (p - 1)) == 0) {
+            shift = 0;
+            while ((1 << shift) < p) ++shift;
+        }
+    }
+    __device__ __forceinline__ int block(int j) const { return shift >= 0 ? j >> shift : j / page_size; }
+    __device__ __forceinline__ int row(int j) const { return shift >= 0 ? j & (page_size - 1) : j % page_size; }
+};
+
+// The part of a request's block table that a CTA walks, copied to shared memory once: a lookup on
+// the way to every tile would put a trip to L2 into the loop.  Entries past the capacity are read
+// from global memory.
+constexpr int BT_CAP = 2048;
+struct StagedTable {
+    const int* global_row;
+    const int* staged;
+    int first, count;
+    __device__ __forceinline__ int page(int block) const {
+        const int i = block - first;
+        return (i >= 0 && i < count) ? staged[i] : global_row[block];
+    }
+};
+__device__ __forceinline__ StagedTable stage_table(int* smem_bt, const int* bt_row, int first_block, int last_block,
+                                                   int tid, int nthreads) {
+    StagedTable t;
+    t.global_row = bt_row;
+    t.staged = smem_bt;
+    t.first = first_block;
+    t.count = max(0, min(BT_CAP, last_block - first_block + 1));
+    for (int i = tid; i < t.count; i += nthreads) smem_bt[i] = bt_row[first_block + i];
+    return t;                                    // the caller synchronises before the first lookup
+}
+
 // Copies ROWS keys starting at absolute position j0 (rows of D elements) of one kv head into a
 // swizzled tile, with NTHREADS threads: a group of NTHREADS / ROWS threads owns a row, looks its
 // page up once, and its threads take neighbouring 16-byte chunks so that each 32-byte sector is
 // asked for once.  A key outside [lo, hi] (or on a page that was given back) is zero-filled and
 // never read.
 template <int ROWS, int NTHREADS>
-__device__ __forceinline__ void load_kv_rows(bf16* tile, const bf16* pool, const int* bt, int page_size,
+__device__ __forceinline__ void load_kv_rows(bf16* tile, const bf16* pool, const StagedTable& bt, const Paging& pg,
                                              int Hkv, int kvh, int j0, int lo, int hi, int tid) {
     constexpr int TPR = NTHREADS / ROWS;          // threads per row
     constexpr int CPT = CHUNKS / TPR;             // chunks per thread
@@ -96,9 +133,9 @@ __device__ __forceinline__ void load_kv_rows(bf16* tile, const bf16* pool, const
     bool pred = j >= lo && j <= hi;
     const bf16* src = pool;
     if (pred) {
-        const int page = bt[j / page_size];
+        const int page = bt.page(pg.block(j));
         pred = page >= 0;
-        if (pred) src = pool + (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * D;
+        if (pred) src = pool + (((size_t)page * Hkv + kvh) * pg.page_size + pg.row(j)) * D;
     }
 #pragma unroll
     for (int c = 0; c < CPT; ++c) {
@@ -121,6 +158,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);
     bf16* sK = sQ + PF_M * D;                 // two stages
     bf16* sV = sK + 2 * PF_N * D;             // two stages
+    int* sBT = reinterpret_cast<int*>(sV + 2 * PF_N * D);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const int h = blockIdx.y, kvh = h / (Hq / Hkv);
@@ -131,7 +169,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     const int p_last = p0 + m_rows - 1;
     const int lo_min = window > 0 ? max(0, p0 - window + 1) : 0;
     const int jt_begin = lo_min / PF_N, jt_end = p_last / PF_N;
-    const int* bt = block_table + (size_t)seg * bt_stride;
+    const Paging pg(page_size);
+    const StagedTable bt = stage_table(sBT, block_table + (size_t)seg * bt_stride, pg.block(lo_min), pg.block(p_last), tid, 128);
+    __syncthreads();
 
     for (int c = tid; c < PF_M * CHUNKS; c += 128) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
@@ -139,8 +179,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
         const bf16* src = pred ? q + (size_t)(q_begin + row0 + r) * ld + (size_t)h * D + ch * 8 : q;
         cp_async16(sQ + soff(r, ch), src, pred);
     }
-    load_kv_rows<PF_N, 128>(sK, kpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, lo_min, p_last, tid);
-    load_kv_rows<PF_N, 128>(sV, vpool, bt, page_size, Hkv, kvh, jt_begin * PF_N, lo_min, p_last, tid);
+    load_kv_rows<PF_N, 128>(sK, kpool, bt, pg, Hkv, kvh, jt_begin * PF_N, lo_min, p_last, tid);
+    load_kv_rows<PF_N, 128>(sV, vpool, bt, pg, Hkv, kvh, jt_begin * PF_N, lo_min, p_last, tid);
     cp_async_commit();
 
     unsigned qf[KSTEPS][4];
@@ -155,8 +195,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     for (int jt = jt_begin; jt <= jt_end; ++jt) {
         const int stage = (jt - jt_begin) & 1;
         if (jt < jt_end) {
-            load_kv_rows<PF_N, 128>(sK + (stage ^ 1) * PF_N * D, kpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, lo_min, p_last, tid);
-            load_kv_rows<PF_N, 128>(sV + (stage ^ 1) * PF_N * D, vpool, bt, page_size, Hkv, kvh, (jt + 1) * PF_N, lo_min, p_last, tid);
+            load_kv_rows<PF_N, 128>(sK + (stage ^ 1) * PF_N * D, kpool, bt, pg, Hkv, kvh, (jt + 1) * PF_N, lo_min, p_last, tid);
+            load_kv_rows<PF_N, 128>(sV + (stage ^ 1) * PF_N * D, vpool, bt, pg, Hkv, kvh, (jt + 1) * PF_N, lo_min, p_last, tid);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -260,8 +300,16 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------- decode
-constexpr int DC_WARPS = (D <= 128) ? 8 : 4;
+#ifdef RB_DC_WARPS                 // tuning builds may fix the decode kernel's shape
+constexpr int DC_WARPS = RB_DC_WARPS;
+#else
+constexpr int DC_WARPS = 4;        // two CTAs share an SM for D <= 128, so one CTA's tail overlaps another's body
+#endif
+#ifdef RB_DC_STAGES
+constexpr int DC_STAGES = RB_DC_STAGES;
+#else
 constexpr int DC_STAGES = (D <= 128) ? 3 : 2;   // pipeline depth per warp, bounded by shared memory
+#endif
 constexpr int DC_N = 16;      // keys per warp tile
 
 __global__ void __launch_bounds__(DC_WARPS * 32)
@@ -273,7 +321,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
                    int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                    // 16 x D
-    bf16* sKV = sQ + 16 * D;                                         // [warp][stage][K 16xD | V 16xD]
+    int* sBT = reinterpret_cast<int*>(sQ + 16 * D);                  // the block-table entries this CTA walks
+    bf16* sKV = reinterpret_cast<bf16*>(sBT + BT_CAP);               // [warp][stage][K 16xD | V 16xD]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const int G = Hq / Hkv;
@@ -286,11 +335,13 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
     const int kv_len = seg_kv_len[seg];
     const int lo = window > 0 ? max(0, kv_len - window) : 0;        // first visible key
     const int hi = kv_len - 1;                                       // the query's own position
-    const int* bt = block_table + (size_t)seg * bt_stride;
     const int first = lo / DC_N, n_tiles = hi / DC_N - first + 1;
     const int per_split = (n_tiles + num_splits - 1) / num_splits;
     const int t_begin = first + split * per_split;
     const int t_end = min(first + n_tiles, t_begin + per_split);     // exclusive
+    const Paging pg(page_size);
+    const StagedTable bt = stage_table(sBT, block_table + (size_t)seg * bt_stride, pg.block(max(lo, t_begin * DC_N)),
+                                       pg.block(min(hi, t_end * DC_N - 1)), tid, DC_WARPS * 32);
 
     for (int c = tid; c < 16 * CHUNKS; c += DC_WARPS * 32) {
         const int r = c / CHUNKS, ch = c - r * CHUNKS;
@@ -339,9 +390,9 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         bool pred = j >= lo && j <= hi;
         size_t eoff = 0;
         if (pred) {
-            const int page = bt[j / page_size];
+            const int page = bt.page(pg.block(j));
             pred = page >= 0;
-            if (pred) eoff = (((size_t)page * Hkv + kvh) * page_size + (j % page_size)) * D + lsub * 8;
+            if (pred) eoff = (((size_t)page * Hkv + kvh) * pg.page_size + pg.row(j)) * D + lsub * 8;
         }
         const bf16* ks = kpool + eoff;
         const bf16* vs = vpool + eoff;
@@ -519,7 +570,7 @@ RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const vo
                               int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale,
                               int window, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
-    const size_t smem = (size_t)(PF_M + 4 * PF_N) * D * sizeof(bf16);
+    const size_t smem = (size_t)(PF_M + 4 * PF_N) * D * sizeof(bf16) + BT_CAP * sizeof(int);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -547,7 +598,7 @@ RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const voi
     const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
     const size_t pipe = (size_t)DC_WARPS * DC_STAGES * 2 * DC_N * D * sizeof(bf16);
     const size_t merge = (size_t)DC_WARPS * 16 * (D + 2) * sizeof(float);
-    const size_t smem = (size_t)16 * D * sizeof(bf16) + (pipe > merge ? pipe : merge);
+    const size_t smem = (size_t)16 * D * sizeof(bf16) + BT_CAP * sizeof(int) + (pipe > merge ? pipe : merge);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
