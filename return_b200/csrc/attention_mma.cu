@@ -617,3 +617,34 @@ RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const voi
     attn_combine_kernel<<<cgrid, 128, 0, st>>>(part_o, part_ml, dec_segs, cu_q, (bf16*)out, Hq, num_splits);
     return rb_launch_status();
 }
+
+// ------------------------------------------------------------------ decode attention without allocation
+// See attention_static.h.  The scratch of the split kernel is this array; host code must not pass
+// its name to a kernel (in host code the name is a host-side stand-in, not a device address), so
+// the address is looked up once per device with cudaGetSymbolAddress.
+#include "attention_static.h"
+
+static __device__ __align__(256) float g_decode_scratch[RB_ATTN_STATIC_SCRATCH_FLOATS];
+
+RB_EXPORT long long rb_attn_decode_static_capacity() { return RB_ATTN_STATIC_SCRATCH_FLOATS; }
+
+RB_EXPORT int rb_attn_decode_static(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
+                                    int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
+                                    int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale,
+                                    int window, int num_splits, cudaStream_t st) {
+    if (n_dec <= 0) return 0;
+    if (num_splits < 1) return (int)cudaErrorInvalidValue;
+    if (rb_attn_decode_scratch_floats(n_dec, Hq, num_splits) > (long long)RB_ATTN_STATIC_SCRATCH_FLOATS)
+        return RB_ERR_SCRATCH_TOO_LARGE;
+    constexpr int MAX_DEVICES = 64;
+    static float* scratch_of_device[MAX_DEVICES] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return RB_ERR_SCRATCH_LOOKUP;
+    if (scratch_of_device[dev] == nullptr) {             // set-up, once per device, that device current
+        float* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_decode_scratch) != cudaSuccess || p == nullptr) return RB_ERR_SCRATCH_LOOKUP;
+        scratch_of_device[dev] = p;
+    }
+    return rb_attn_decode(q, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
+                          scratch_of_device[dev], out, Hq, Hkv, scale, window, num_splits, st);
+}

@@ -1,0 +1,97 @@
+"""rb_attn_decode_static, the decode-attention entry point that allocates nothing.
+
+Some users of the kernels cannot allocate device memory when they call: a host that gave all free
+memory to the KV pool at start-up, a decode loop that must never enter cudaMalloc, a program that
+links the library without PyTorch.  For them the split kernel's scratch sits in a device array
+inside the library.  This test calls the entry point through its exported C symbol, with raw
+pointers, twice in a row on different inputs (the array keeps the first call's contents, which
+must not leak into the second), and compares with the ordinary entry point that takes a scratch
+buffer.  It is collected last, so a run that stops at the first failure has run everything else.
+"""
+import ctypes
+import math
+from ctypes import c_float, c_int, c_void_p
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+HQ, HKV, D, P = 8, 2, 64, 16
+
+
+def _library():
+    from return_b200.ext import build
+    lib = ctypes.CDLL(build.library_path(f"return_attn_d{D}", ["attention_mma.cu"], {"HEAD_DIM": D}))
+    Ptr, I = c_void_p, c_int
+    lib.rb_attn_decode_static.argtypes = [Ptr, I, Ptr, Ptr, Ptr, I, Ptr, Ptr, Ptr, I, I, Ptr, I, I, c_float, I, I, Ptr]
+    lib.rb_attn_decode_static.restype = c_int
+    lib.rb_attn_decode_static_capacity.restype = ctypes.c_longlong
+    return lib
+
+
+def _case(seed, kv_lens):
+    g = torch.Generator().manual_seed(seed)
+    n = len(kv_lens)
+    blocks = [(L + P - 1) // P for L in kv_lens]
+    n_pages = sum(blocks) + 2
+    perm = iter(torch.randperm(n_pages, generator=g).tolist())
+    kpool = torch.randn(n_pages, HKV, P, D, generator=g).bfloat16().to(DEV)
+    vpool = torch.randn(n_pages, HKV, P, D, generator=g).bfloat16().to(DEV)
+    bt = torch.full((n, max(blocks)), -1, dtype=torch.int32)
+    for i, nb in enumerate(blocks):
+        for b in range(nb):
+            bt[i, b] = next(perm)
+    qkv = torch.randn(n, (HQ + 2 * HKV) * D, generator=g).bfloat16().to(DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return dict(qkv=qkv, kpool=kpool, vpool=vpool, bt=bt.to(DEV), segs=i32(list(range(n))), cu_q=i32(list(range(n + 1))),
+                kv_len=i32(kv_lens), n=n)
+
+
+def _static(lib, c, splits, window=0):
+    out = torch.full((c["n"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ptr = lambda t: c_void_p(t.data_ptr())
+    rc = lib.rb_attn_decode_static(ptr(c["qkv"]), c["qkv"].stride(0), ptr(c["kpool"]), ptr(c["vpool"]), ptr(c["segs"]),
+                                   c["n"], ptr(c["cu_q"]), ptr(c["kv_len"]), ptr(c["bt"]), c["bt"].stride(0), P,
+                                   ptr(out), HQ, HKV, 1.0 / math.sqrt(D), window, splits,
+                                   c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    return rc, out
+
+
+def _ordinary(c, splits, window=0):
+    from return_b200.ext import ops
+    out = torch.full((c["n"], HQ * D), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attention_decode_mma(c["qkv"], c["kpool"], c["vpool"], c["segs"], c["cu_q"], c["kv_len"], c["bt"], P, out,
+                             HQ, HKV, D, 1.0 / math.sqrt(D), window, num_splits=splits)
+    torch.cuda.synchronize()
+    return out
+
+
+def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
+    lib = _library()
+    first = _case(1, [300, 17, 129, 64, 511])
+    second = _case(2, [40, 200, 333])                      # fewer, other requests: stale scratch must not show
+    for case, splits, window in ((first, 4, 0), (second, 3, 0), (first, 1, 0), (second, 5, 90)):
+        rc, got = _static(lib, case, splits, window)
+        assert rc == 0
+        want = _ordinary(case, splits, window)
+        assert torch.isfinite(got.float()).all()
+        assert torch.allclose(got.float(), want.float(), atol=3e-2, rtol=3e-2)
+
+
+def test_static_scratch_entry_point_refuses_what_does_not_fit():
+    lib = _library()
+    cap = lib.rb_attn_decode_static_capacity()
+    assert cap == 1 << 20
+    c = _case(3, [64] * 8)
+    # n_dec * Hq * splits * (D + 2) floats must fit: 8 * 8 * 64 * 66 = 270k fits, a made-up huge head count does not
+    rc, _ = _static(lib, c, 64)
+    assert rc == 0
+    out = torch.empty((8, HQ * D), dtype=torch.bfloat16, device=DEV)
+    ptr = lambda t: c_void_p(t.data_ptr())
+    rc = lib.rb_attn_decode_static(ptr(c["qkv"]), c["qkv"].stride(0), ptr(c["kpool"]), ptr(c["vpool"]), ptr(c["segs"]),
+                                   c["n"], ptr(c["cu_q"]), ptr(c["kv_len"]), ptr(c["bt"]), c["bt"].stride(0), P,
+                                   ptr(out), 4096, 1024, 0.125, 0, 64, c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == -2                                        # RB_ERR_SCRATCH_TOO_LARGE: nothing was launched
+    torch.cuda.synchronize()
