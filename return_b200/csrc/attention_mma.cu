@@ -159,6 +159,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
     bf16* sK = sQ + PF_M * D;                 // two stages
     bf16* sV = sK + 2 * PF_N * D;             // two stages
     int* sBT = reinterpret_cast<int*>(sV + 2 * PF_N * D);
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const int h = blockIdx.y, kvh = h / (Hq / Hkv);
@@ -323,6 +325,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                    // 16 x D
     int* sBT = reinterpret_cast<int*>(sQ + 16 * D);                  // the block-table entries this CTA walks
     bf16* sKV = reinterpret_cast<bf16*>(sBT + BT_CAP);               // [warp][stage][K 16xD | V 16xD]
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const int G = Hq / Hkv;
@@ -493,6 +497,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         stage = stage + 1 == DC_STAGES ? 0 : stage + 1;
         fill_stage = fill_stage + 1 == DC_STAGES ? 0 : fill_stage + 1;
     }
+    pdl_trigger_late();
     cp_async_wait<0>();
     __syncthreads();                                              // the pipeline buffers become merge buffers
 
@@ -541,6 +546,8 @@ __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     const int* __restrict__ dec_segs, const int* __restrict__ cu_q,
                     bf16* __restrict__ out, int Hq, int num_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x, h = blockIdx.y;
     const int tok_row = cu_q[dec_segs[i]];
     const size_t base = ((size_t)i * Hq + h) * num_splits;
@@ -578,10 +585,9 @@ RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const vo
         configured = true;
     }
     dim3 grid(n_tiles, Hq);
-    attn_prefill_kernel<<<grid, 128, smem, st>>>((const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, tiles,
-                                                 cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
-                                                 Hq, Hkv, scale * LOG2E, window);
-    return rb_launch_status();
+    return rb_launch_pdl(attn_prefill_kernel, grid, dim3(128), smem, st, (const bf16*)q, ld, (const bf16*)kpool,
+                         (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
+                         Hq, Hkv, scale * LOG2E, window);
 }
 
 // Floats of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D], part_ml [n_dec, Hq, splits, 2].
@@ -608,14 +614,13 @@ RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const voi
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_dec * Hq * num_splits * D : nullptr;
     dim3 grid(n_dec, Hkv * m_tiles, num_splits);
-    attn_decode_kernel<<<grid, DC_WARPS * 32, smem, st>>>(
+    int rc = rb_launch_pdl(attn_decode_kernel, grid, dim3(DC_WARPS * 32), smem, st,
         (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
         bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits);
-    int rc = rb_launch_status();
     if (rc != 0 || num_splits == 1) return rc;
     dim3 cgrid(n_dec, Hq);
-    attn_combine_kernel<<<cgrid, 128, 0, st>>>(part_o, part_ml, dec_segs, cu_q, (bf16*)out, Hq, num_splits);
-    return rb_launch_status();
+    return rb_launch_pdl(attn_combine_kernel, cgrid, dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,
+                         dec_segs, cu_q, (bf16*)out, Hq, num_splits);
 }
 
 // ------------------------------------------------------------------ decode attention without allocation

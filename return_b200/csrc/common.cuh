@@ -76,3 +76,50 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int rb_launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  A kernel launched with rb_launch_pdl may begin while the kernel
+// before it in the stream is still draining: its CTAs are placed as soon as every CTA of the
+// predecessor has called pdl_launch_dependents() (or exited), and run up to pdl_wait(), which
+// returns once the predecessor has finished and its writes are visible.  The rule every such
+// kernel keeps: before pdl_wait() it touches nothing a predecessor could have written (it may read
+// weights, which no kernel writes) and writes nothing at all.  This hides launch and ramp-up
+// latency between the many short kernels of a decode step; it is captured into CUDA graphs as
+// programmatic dependency edges.
+//
+// RB_PDL_MODE: 0 launch attribute only (the successor starts when this kernel ends); 1 trigger at
+// the start of every kernel; 2 trigger when a kernel's main loop is done, so that only its
+// epilogue and tail overlap the successor's prologue; 3 plain launches.
+#ifndef RB_PDL_MODE
+#define RB_PDL_MODE 2
+#endif
+__device__ __forceinline__ void pdl_wait() {
+#if RB_PDL_MODE != 3
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_launch_dependents() {       // at the start of a kernel
+#if RB_PDL_MODE == 1
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_trigger_late() {            // after a kernel's main loop
+#if RB_PDL_MODE == 2
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+template <typename... KArgs, typename... Args>
+static inline int rb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = RB_PDL_MODE == 3 ? 0 : 1;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

@@ -28,6 +28,8 @@ template <typename TW>
 __global__ void embedding_vec_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                                      float* __restrict__ stream, int H, int V) {
     constexpr int E = 16 / sizeof(TW);
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = tokens[t];
     float* dst = stream + (size_t)t * H;
@@ -52,12 +54,12 @@ RB_EXPORT int rb_embedding(const void* table, int table_dtype, const int* tokens
     const bool aligned = ((uintptr_t)table % 16) == 0 && ((uintptr_t)stream % 16) == 0;
     if (table_dtype == RB_F32) {
         if (aligned && H % 4 == 0)
-            embedding_vec_kernel<float><<<T, threads, 0, st>>>((const float*)table, tokens, stream, H, V);
+            return rb_launch_pdl(embedding_vec_kernel<float>, dim3(T), dim3(threads), 0, st, (const float*)table, tokens, stream, H, V);
         else
             embedding_kernel<float><<<T, threads, 0, st>>>((const float*)table, tokens, stream, H, V);
     } else {
         if (aligned && H % 8 == 0)
-            embedding_vec_kernel<bf16><<<T, threads, 0, st>>>((const bf16*)table, tokens, stream, H, V);
+            return rb_launch_pdl(embedding_vec_kernel<bf16>, dim3(T), dim3(threads), 0, st, (const bf16*)table, tokens, stream, H, V);
         else
             embedding_kernel<bf16><<<T, threads, 0, st>>>((const bf16*)table, tokens, stream, H, V);
     }
@@ -124,12 +126,19 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ stream, const TA* __r
                                        const int* __restrict__ rows, const TW* __restrict__ w,
                                        float eps, float offset, TA* __restrict__ out, int H) {
     __shared__ float scratch[33];
+    pdl_launch_dependents();
     const int orow = blockIdx.x;
+    const int nvec = H >> 2;
+    float4 x[VPT], wv[VPT];
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {                      // the norm weight is nobody's output: read it early
+        const int i = threadIdx.x + v * blockDim.x;
+        wv[v] = i < nvec ? Vec4<TW>::load(w + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
     const int irow = rows ? rows[orow] : orow;
     float* s = stream + (size_t)irow * H;
     const TA* d = delta ? delta + (size_t)irow * H : nullptr;
-    const int nvec = H >> 2;
-    float4 x[VPT], wv[VPT];
 #pragma unroll
     for (int v = 0; v < VPT; ++v) {
         const int i = threadIdx.x + v * blockDim.x;
@@ -145,11 +154,6 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ stream, const TA* __r
             }
         }
     }
-#pragma unroll
-    for (int v = 0; v < VPT; ++v) {
-        const int i = threadIdx.x + v * blockDim.x;
-        wv[v] = i < nvec ? Vec4<TW>::load(w + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
     float ss = 0.f;
 #pragma unroll
     for (int v = 0; v < VPT; ++v) ss += x[v].x * x[v].x + x[v].y * x[v].y + x[v].z * x[v].z + x[v].w * x[v].w;
@@ -160,6 +164,7 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ stream, const TA* __r
             if (i < nvec) Vec4<float>::store(s + 4 * i, x[v]);
         }
     }
+    pdl_trigger_late();
     ss = block_sum(ss, scratch);
     const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
     TA* o = out + (size_t)orow * H;
@@ -179,11 +184,11 @@ static int launch_add_rmsnorm_vec(float* stream, const void* delta, const int* r
     int threads = 128;
     while (threads < 1024 && threads * 4 < nvec) threads <<= 1;
     if (threads >= nvec)
-        add_rmsnorm_vec_kernel<TA, TW, 1><<<n_rows, threads, 0, st>>>(stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
+        return rb_launch_pdl(add_rmsnorm_vec_kernel<TA, TW, 1>, dim3(n_rows), dim3(threads), 0, st, stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
     else if (threads * 2 >= nvec)
-        add_rmsnorm_vec_kernel<TA, TW, 2><<<n_rows, threads, 0, st>>>(stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
+        return rb_launch_pdl(add_rmsnorm_vec_kernel<TA, TW, 2>, dim3(n_rows), dim3(threads), 0, st, stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
     else
-        add_rmsnorm_vec_kernel<TA, TW, 4><<<n_rows, threads, 0, st>>>(stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
+        return rb_launch_pdl(add_rmsnorm_vec_kernel<TA, TW, 4>, dim3(n_rows), dim3(threads), 0, st, stream, (const TA*)delta, rows, (const TW*)w, eps, offset, (TA*)out, H);
     return rb_launch_status();
 }
 
@@ -263,6 +268,8 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
 
 // bfloat16 with I a multiple of 8: eight elements (16 bytes) per thread and iteration.
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int T, int I) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int I8 = I >> 3;
     const size_t total = (size_t)T * I8;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -290,8 +297,7 @@ RB_EXPORT int rb_swiglu(const void* gu, void* out, int act_dtype, int T, int I, 
         const size_t total = (size_t)T * (I >> 3);
         int blocks = (int)((total + threads - 1) / threads);
         if (blocks > 148 * 16) blocks = 148 * 16;
-        swiglu_bf16x8_kernel<<<blocks, threads, 0, st>>>((const bf16*)gu, (bf16*)out, T, I);
-        return rb_launch_status();
+        return rb_launch_pdl(swiglu_bf16x8_kernel, dim3(blocks), dim3(threads), 0, st, (const bf16*)gu, (bf16*)out, T, I);
     }
     const size_t total = (size_t)T * I;
     int blocks = (int)((total + threads - 1) / threads);

@@ -69,7 +69,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
     for (int mt = 0; mt < MT; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    auto load = [&](Regs<MT, U>& r, int kb) {            // blocks past the warp's slice load zeros
+    auto load_w = [&](Regs<MT, U>& r, int kb) {          // blocks past the warp's slice load zeros
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (kb + u) << 5;
@@ -77,6 +77,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
             r.a0[u] = (kin && ok0) ? ld_stream16(w0 + k) : zero;
             r.a1[u] = (kin && ok1) ? ld_stream16(w1 + k) : zero;
         }
+    };
+    auto load_x = [&](Regs<MT, U>& r, int kb) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (kb + u) << 5;
@@ -96,14 +98,19 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
             }
         }
     };
+    auto load = [&](Regs<MT, U>& r, int kb) { load_w(r, kb); load_x(r, kb); };
     Regs<MT, U> ra, rb;
-    load(ra, kb_begin);
+    pdl_launch_dependents();
+    load_w(ra, kb_begin);                                // weights are nobody's output: stream them at once
+    pdl_wait();                                          // the tokens come from the kernel before
+    load_x(ra, kb_begin);
     for (int kb = kb_begin; kb < kb_end; kb += 2 * U) {  // the next buffer is in flight while one is used
         load(rb, kb + U);
         compute(ra);
         load(ra, kb + 2 * U);
         compute(rb);
     }
+    pdl_trigger_late();
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
         red[warp][g][mt * 8 + 2 * t4] = acc[mt][0];
@@ -128,10 +135,8 @@ int launch(const bf16* x, const bf16* w, void* out, int out_f32, int M, int N, i
            cudaStream_t st) {
     const int grid = (N + SK_ROWS - 1) / SK_ROWS;
     if (out_f32)
-        gemm_skinny_kernel<MT, float><<<grid, SK_WARPS * 32, 0, st>>>(x, w, (float*)out, M, N, K, ldx, ldw, ldo);
-    else
-        gemm_skinny_kernel<MT, bf16><<<grid, SK_WARPS * 32, 0, st>>>(x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
-    return rb_launch_status();
+        return rb_launch_pdl(gemm_skinny_kernel<MT, float>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (float*)out, M, N, K, ldx, ldw, ldo);
+    return rb_launch_pdl(gemm_skinny_kernel<MT, bf16>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
 }
 
 }  // namespace

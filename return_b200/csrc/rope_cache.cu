@@ -25,6 +25,8 @@ __global__ void qk_norm_rope_write_kernel(
         const int* __restrict__ block_table, int bt_stride, int page_size,
         TA* __restrict__ kpool, TA* __restrict__ vpool,
         int Hq, int Hkv, int D, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int warp = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);      // one warp per head
@@ -91,12 +93,10 @@ RB_EXPORT int rb_qk_norm_rope_write(
     const int heads = write_kv ? Hq + 2 * Hkv : Hq + Hkv;
     const dim3 grid(T, (heads + 3) / 4);
     if (act_dtype == RB_F32)
-        qk_norm_rope_write_kernel<float><<<grid, threads, 0, st>>>(
+        return rb_launch_pdl(qk_norm_rope_write_kernel<float>, grid, dim3(threads), 0, st,
             (float*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
             block_table, bt_stride, page_size, (float*)kpool, (float*)vpool, Hq, Hkv, D, write_kv);
-    else
-        qk_norm_rope_write_kernel<bf16><<<grid, threads, 0, st>>>(
+    return rb_launch_pdl(qk_norm_rope_write_kernel<bf16>, grid, dim3(threads), 0, st,
             (bf16*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
             block_table, bt_stride, page_size, (bf16*)kpool, (bf16*)vpool, Hq, Hkv, D, write_kv);
-    return rb_launch_status();
 }

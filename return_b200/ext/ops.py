@@ -54,6 +54,10 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
         raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
+# How kernels of a step overlap through programmatic dependent launch (csrc/common.cuh); a build option.
+import os as _os
+PDL_MODE = int(_os.environ.get("RETURN_B200_PDL_MODE", "2"))
+
 _core = None
 
 _CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemm_skinny.cu", "rope_cache.cu", "attention_simt.cu", "sampling.cu"]
@@ -63,7 +67,7 @@ def core() -> ctypes.CDLL:
     """The library of kernels that need no specialisation."""
     global _core
     if _core is None:
-        lib = build.load("return_core", _CORE_SOURCES)
+        lib = build.load("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})
         P, I, F = c_void_p, c_int, c_float
         lib.rb_embedding.argtypes = [P, I, P, P, I, I, I, P]
         lib.rb_add_rmsnorm.argtypes = [P, P, P, P, I, F, F, P, I, I, I, P]
@@ -89,9 +93,9 @@ PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 
 def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
-    paths = [build.library_path("return_core", _CORE_SOURCES)]
+    paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
     for d in PREBUILT_HEAD_DIMS:
-        paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], {"HEAD_DIM": d}))
+        paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], {"HEAD_DIM": d, "RB_PDL_MODE": PDL_MODE}))
     return paths
 
 
@@ -236,7 +240,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
     if lib is None:
         if head_dim % 16 or not (16 <= head_dim <= 256):
             raise KernelError(f"head_dim={head_dim}: the attention kernels take multiples of 16 from 16 to 256")
-        lib = build.load(f"return_attn_d{head_dim}", ["attention_mma.cu"], {"HEAD_DIM": head_dim})
+        lib = build.load(f"return_attn_d{head_dim}", ["attention_mma.cu"], {"HEAD_DIM": head_dim, "RB_PDL_MODE": PDL_MODE})
         P, I, F = c_void_p, c_int, c_float
         lib.rb_attn_prefill.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P]
         lib.rb_attn_decode.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P]

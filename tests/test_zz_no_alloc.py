@@ -21,8 +21,9 @@ HQ, HKV, D, P = 8, 2, 64, 16
 
 
 def _library():
-    from return_b200.ext import build
-    lib = ctypes.CDLL(build.library_path(f"return_attn_d{D}", ["attention_mma.cu"], {"HEAD_DIM": D}))
+    from return_b200.ext import build, ops
+    lib = ctypes.CDLL(build.library_path(f"return_attn_d{D}", ["attention_mma.cu"],
+                                         {"HEAD_DIM": D, "RB_PDL_MODE": ops.PDL_MODE}))
     Ptr, I = c_void_p, c_int
     lib.rb_attn_decode_static.argtypes = [Ptr, I, Ptr, Ptr, Ptr, I, Ptr, Ptr, Ptr, I, I, Ptr, I, I, c_float, I, I, Ptr]
     lib.rb_attn_decode_static.restype = c_int
