@@ -253,21 +253,25 @@ RB_EXPORT int rb_rmsnorm_rows(const void* x, const void* w, int w_dtype, float e
 }
 
 // ---------------------------------------------------------------- SwiGLU
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i];  gu is [T, 2I] with gate columns first.
+// out[t, i] = silu(gate) * up.  gu is [T, 2I].  block == 0: gate columns [0, I), up columns [I, 2I)
+// (the reference's concatenation, rollout/monkey_patch/qwen3.py:99-105).  block == 8: columns come in
+// blocks of 8 gate then 8 up (the layout that lets a matrix product's epilogue do this step).
 template <typename TA>
-__global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int T, int I) {
+__global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int T, int I, int block) {
     const size_t total = (size_t)T * I;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I, i = idx - t * I;
-        const float g = to_f32(gu[t * 2 * I + i]);
-        const float u = to_f32(gu[t * 2 * I + I + i]);
+        const size_t gi = block ? (i / block) * 2 * block + i % block : i;
+        const size_t ui = block ? gi + block : I + i;
+        const float g = to_f32(gu[t * 2 * I + gi]);
+        const float u = to_f32(gu[t * 2 * I + ui]);
         out[idx] = from_f32<TA>(g / (1.0f + expf(-g)) * u);
     }
 }
 
 // bfloat16 with I a multiple of 8: eight elements (16 bytes) per thread and iteration.
-__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int T, int I) {
+__global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int T, int I, int block) {
     pdl_launch_dependents();
     pdl_wait();
     const int I8 = I >> 3;
@@ -275,8 +279,8 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I8, i = (idx - t * I8) << 3;
-        const uint4 gv = *(const uint4*)(gu + t * 2 * I + i);
-        const uint4 uv = *(const uint4*)(gu + t * 2 * I + I + i);
+        const uint4 gv = *(const uint4*)(gu + t * 2 * I + (block ? 2 * i : i));
+        const uint4 uv = *(const uint4*)(gu + t * 2 * I + (block ? 2 * i + 8 : I + i));
         const bf16* g = (const bf16*)&gv;
         const bf16* u = (const bf16*)&uv;
         uint4 ov;
@@ -290,21 +294,22 @@ __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restri
     }
 }
 
-RB_EXPORT int rb_swiglu(const void* gu, void* out, int act_dtype, int T, int I, cudaStream_t st) {
+RB_EXPORT int rb_swiglu(const void* gu, void* out, int act_dtype, int T, int I, int block, cudaStream_t st) {
     if (T <= 0) return 0;
+    if (block != 0 && (block != 8 || I % 8)) return (int)cudaErrorInvalidValue;
     const int threads = 256;
     if (act_dtype == RB_BF16 && (I % 8) == 0 && ((uintptr_t)gu % 16) == 0 && ((uintptr_t)out % 16) == 0) {
         const size_t total = (size_t)T * (I >> 3);
         int blocks = (int)((total + threads - 1) / threads);
         if (blocks > 148 * 16) blocks = 148 * 16;
-        return rb_launch_pdl(swiglu_bf16x8_kernel, dim3(blocks), dim3(threads), 0, st, (const bf16*)gu, (bf16*)out, T, I);
+        return rb_launch_pdl(swiglu_bf16x8_kernel, dim3(blocks), dim3(threads), 0, st, (const bf16*)gu, (bf16*)out, T, I, block);
     }
     const size_t total = (size_t)T * I;
     int blocks = (int)((total + threads - 1) / threads);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (act_dtype == RB_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, st>>>((const float*)gu, (float*)out, T, I);
+        swiglu_kernel<float><<<blocks, threads, 0, st>>>((const float*)gu, (float*)out, T, I, block);
     else
-        swiglu_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)gu, (bf16*)out, T, I);
+        swiglu_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)gu, (bf16*)out, T, I, block);
     return rb_launch_status();
 }

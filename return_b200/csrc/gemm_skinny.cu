@@ -40,7 +40,9 @@ struct Regs {                         // one buffer: U blocks of 32 k of the wei
     uint4 a0[U], a1[U], b[U][MT];
 };
 
-template <int MT, typename TOut>
+// GATED: the 16 weight rows of a CTA are 8 gate rows followed by their 8 up rows (the feed-forward's
+// interleaved layout); the epilogue writes silu(gate) * up, 8 values per token, into out[M, N / 2].
+template <int MT, typename TOut, bool GATED>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ out,
                    int M, int N, int K, int ldx, int ldw, int ldo) {
@@ -119,38 +121,55 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
         red[warp][g + 8][mt * 8 + 2 * t4 + 1] = acc[mt][3];
     }
     __syncthreads();
-    for (int idx = tid; idx < SK_ROWS * 8 * MT; idx += SK_WARPS * 32) {
-        const int n = idx & (SK_ROWS - 1), m = idx >> 4;
-        if (m < M && n0 + n < N) {
-            float s = 0.f;
+    if constexpr (GATED) {
+        for (int idx = tid; idx < 8 * 8 * MT; idx += SK_WARPS * 32) {
+            const int j = idx & 7, m = idx >> 3;
+            if (m < M && n0 + 8 + j < N) {
+                float gate = 0.f, up = 0.f;
 #pragma unroll
-            for (int wi = 0; wi < SK_WARPS; ++wi) s += red[wi][n][m];
-            store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
+                for (int wi = 0; wi < SK_WARPS; ++wi) { gate += red[wi][j][m]; up += red[wi][8 + j][m]; }
+                store_out<TOut>(out + (size_t)m * ldo + (n0 >> 1) + j, gate / (1.0f + expf(-gate)) * up);
+            }
+        }
+    } else {
+        for (int idx = tid; idx < SK_ROWS * 8 * MT; idx += SK_WARPS * 32) {
+            const int n = idx & (SK_ROWS - 1), m = idx >> 4;
+            if (m < M && n0 + n < N) {
+                float s = 0.f;
+#pragma unroll
+                for (int wi = 0; wi < SK_WARPS; ++wi) s += red[wi][n][m];
+                store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
+            }
         }
     }
 }
 
 template <int MT>
-int launch(const bf16* x, const bf16* w, void* out, int out_f32, int M, int N, int K, int ldx, int ldw, int ldo,
-           cudaStream_t st) {
+int launch(const bf16* x, const bf16* w, void* out, int out_f32, int gated, int M, int N, int K, int ldx, int ldw,
+           int ldo, cudaStream_t st) {
     const int grid = (N + SK_ROWS - 1) / SK_ROWS;
+    if (gated)
+        return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, true>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
     if (out_f32)
-        return rb_launch_pdl(gemm_skinny_kernel<MT, float>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (float*)out, M, N, K, ldx, ldw, ldo);
-    return rb_launch_pdl(gemm_skinny_kernel<MT, bf16>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
+        return rb_launch_pdl(gemm_skinny_kernel<MT, float, false>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (float*)out, M, N, K, ldx, ldw, ldo);
+    return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, false>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
 }
 
 }  // namespace
 
 RB_EXPORT int rb_gemm_skinny_max_rows() { return 32; }
 
-RB_EXPORT int rb_gemm_skinny(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+// gated = 1: w holds gate and up rows interleaved in blocks of 8 (N % 16 == 0) and out is
+// bfloat16 [M, N / 2] = silu(gate) * up.
+RB_EXPORT int rb_gemm_skinny(const void* x, const void* w, void* out, int out_f32, int gated, int M, int N, int K,
                              int ldx, int ldw, int ldo, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 32 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16))
         return (int)cudaErrorInvalidValue;
+    if (gated && (N % 16 || out_f32)) return (int)cudaErrorInvalidValue;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)w;
-    if (M <= 8) return launch<1>(xp, wp, out, out_f32, M, N, K, ldx, ldw, ldo, st);
-    if (M <= 16) return launch<2>(xp, wp, out, out_f32, M, N, K, ldx, ldw, ldo, st);
-    return launch<4>(xp, wp, out, out_f32, M, N, K, ldx, ldw, ldo, st);
+    if (M <= 8) return launch<1>(xp, wp, out, out_f32, gated, M, N, K, ldx, ldw, ldo, st);
+    if (M <= 16) return launch<2>(xp, wp, out, out_f32, gated, M, N, K, ldx, ldw, ldo, st);
+    return launch<4>(xp, wp, out, out_f32, gated, M, N, K, ldx, ldw, ldo, st);
 }

@@ -72,9 +72,9 @@ def core() -> ctypes.CDLL:
         lib.rb_embedding.argtypes = [P, I, P, P, I, I, I, P]
         lib.rb_add_rmsnorm.argtypes = [P, P, P, P, I, F, F, P, I, I, I, P]
         lib.rb_rmsnorm_rows.argtypes = [P, P, I, F, F, P, I, I, I, P]
-        lib.rb_swiglu.argtypes = [P, P, I, I, I, P]
+        lib.rb_swiglu.argtypes = [P, P, I, I, I, I, P]
         lib.rb_gemm_f32.argtypes = [P, P, P, I, I, I, I, I, I, P]
-        lib.rb_gemm_skinny.argtypes = [P, P, P, I, I, I, I, I, I, I, P]
+        lib.rb_gemm_skinny.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P]
         lib.rb_gemm_skinny.restype = c_int
         lib.rb_qk_norm_rope_write.argtypes = [P, I, P, P, I, F, F, P, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P]
         lib.rb_attention_simt.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, P]
@@ -138,12 +138,12 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.T
                                   dtype_code(x.dtype), x.numel() // N, N, _stream()), "rmsnorm_rows")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> None:
+    """out = silu(gate) * up.  ``interleave`` 0: gate_up[t] = [gate | up]; 8: blocks of 8 gate then 8 up."""
     T, I2 = gate_up.shape
     assert out.shape == (T, I2 // 2) and gate_up.is_contiguous() and out.is_contiguous()
-    assert out.dtype == gate_up.dtype
-    _check(core().rb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, _stream()), "swiglu")
+    assert out.dtype == gate_up.dtype and interleave in (0, 8)
+    _check(core().rb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I2 // 2, interleave, _stream()), "swiglu")
 
 
 # ------------------------------------------------------------------------------- matrix products
@@ -162,15 +162,35 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 SKINNY_MAX_ROWS = 32
 
 
-def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 32 in bfloat16: the weight-streaming kernel of decode steps."""
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 32 in bfloat16: the weight-streaming kernel of decode steps.
+    ``gated``: w holds gate and up rows interleaved in blocks of 8; out[M, N/2] = silu(gate) * up."""
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
-    assert w.shape[1] == K and out.shape == (M, N) and M <= SKINNY_MAX_ROWS
+    assert w.shape[1] == K and out.shape == (M, N // 2 if gated else N) and M <= SKINNY_MAX_ROWS
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
-    _check(core().rb_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0, M, N, K,
-                                 x.stride(0), w.stride(0), out.stride(0), _stream()), "gemm_skinny")
+    _check(core().rb_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                                 1 if gated else 0, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()),
+           "gemm_skinny")
+
+
+def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the weight-streaming kernel takes this product (few rows, 16-byte aligned rows)."""
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, interleave: int) -> None:
+    """out[T, I] = silu(x @ gate^T) * (x @ up^T) for the fused weight ``w`` [2I, K] of a gated
+    feed-forward.  With the interleaved layout and few rows the product's epilogue does the
+    gating; otherwise a product into a [T, 2I] buffer is followed by the SwiGLU kernel."""
+    if interleave == 8 and skinny_ok(x, w):
+        gemm_skinny(x, w, out, gated=True)
+        return
+    gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
+    linear(x, w, gu)
+    swiglu(gu, out, interleave)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -183,8 +203,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     if not x.is_cuda:
         raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-    if (x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+    if skinny_ok(x, w):
         gemm_skinny(x, w, out)
         return
     if out.dtype == torch.float32:

@@ -4,8 +4,9 @@ parts' parameters.
 Layer order and formulas: rollout/monkey_patch/qwen3.py:59-81.  Tensor names are those of a
 Hugging Face ``Qwen3ForCausalLM`` checkpoint, which the reference loads
 (rollout/engine_actor.py:14-21).  Fusions at load: q, k and v projections into one ``qkv``
-matrix (rows q, then k, then v), gate and up projections into ``gate_up`` (gate rows first,
-as the reference concatenates them, rollout/monkey_patch/qwen3.py:99-105).
+matrix (rows q, then k, then v), gate and up projections into ``gate_up`` (the reference
+concatenates them, rollout/monkey_patch/qwen3.py:99-105; here their rows are interleaved in blocks
+of 8 when the intermediate size allows, see ``SwiGLUSpec``).
 """
 from __future__ import annotations
 
@@ -17,13 +18,18 @@ from ..parts.spec import (AttentionSpec, BlockSpec, DecoderSpec, NormSpec, RopeS
 from ..weights.loader import Source
 
 
+def _gate_up_interleave(cfg: Qwen3Config) -> int:
+    return 8 if cfg.intermediate_size % 8 == 0 else 0
+
+
 def decoder_spec(cfg: Qwen3Config, max_positions: Optional[int] = None) -> DecoderSpec:
     D = cfg.head_dim
     rope = RopeSpec(rotary_dim=D, theta=cfg.rope_theta,
                     max_positions=max_positions or cfg.max_position_embeddings)
     head_norm = NormSpec(size=D, eps=cfg.rms_norm_eps)
     stream_norm = NormSpec(size=cfg.hidden_size, eps=cfg.rms_norm_eps)
-    ffn = SwiGLUSpec(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size)
+    ffn = SwiGLUSpec(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size,
+                     interleave=_gate_up_interleave(cfg))
     layers = []
     for i in range(cfg.num_hidden_layers):
         mixer = AttentionSpec(hidden_size=cfg.hidden_size, num_heads=cfg.num_attention_heads,
@@ -50,7 +56,8 @@ def weight_sources(cfg: Qwen3Config) -> Dict[str, Source]:
         m[dst + "mixer.o"] = Source((src + "self_attn.o_proj.weight",))
         m[dst + "mixer.q_norm.weight"] = Source((src + "self_attn.q_norm.weight",))
         m[dst + "mixer.k_norm.weight"] = Source((src + "self_attn.k_norm.weight",))
-        m[dst + "feed_forward.gate_up"] = Source((src + "mlp.gate_proj.weight", src + "mlp.up_proj.weight"))
+        m[dst + "feed_forward.gate_up"] = Source((src + "mlp.gate_proj.weight", src + "mlp.up_proj.weight"),
+                                                 interleave=_gate_up_interleave(cfg))
         m[dst + "feed_forward.down"] = Source((src + "mlp.down_proj.weight",))
         m[dst + "mixer_norm.weight"] = Source((src + "input_layernorm.weight",))
         m[dst + "feed_forward_norm.weight"] = Source((src + "post_attention_layernorm.weight",))

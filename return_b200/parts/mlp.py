@@ -9,8 +9,14 @@ from .base import FEED_FORWARDS, FeedForward, ParamSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    """y = down( silu(g) * u ) with [g, u] = x @ gate_up^T, gate rows first, as the reference
-    concatenates them."""
+    """y = down( silu(g) * u ) with [g, u] = x @ gate_up^T.  The reference concatenates gate rows
+    and up rows; ``spec.interleave`` may instead ask for blocks of 8 gate rows and 8 up rows, so that
+    the product's epilogue applies the gate when a step has few rows."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.interleave not in (0, 8) or (spec.interleave and spec.intermediate_size % spec.interleave):
+            raise ValueError("interleave is 0, or 8 with intermediate_size a multiple of 8")
 
     def params(self):
         s = self.spec
@@ -20,10 +26,8 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx):
         s = self.spec
         T = x.shape[0]
-        gu = torch.empty((T, 2 * s.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.linear(x, self.p_gate_up, gu)
         act = torch.empty((T, s.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.swiglu(gu, act)
+        ops.gated_linear(x, self.p_gate_up, act, s.interleave)
         y = torch.empty((T, s.hidden_size), dtype=x.dtype, device=x.device)
         ops.linear(act, self.p_down, y)
         return y

@@ -49,9 +49,12 @@ class AttentionSpec:
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """down( silu(gate(x)) * up(x) ), dense."""
+    """down( silu(gate(x)) * up(x) ), dense.  ``interleave``: row layout of the fused gate_up weight:
+    0 = all gate rows then all up rows; 8 = blocks of 8 gate rows then their 8 up rows, which lets
+    the product's epilogue apply the gate (needs intermediate_size % 8 == 0)."""
     hidden_size: int
     intermediate_size: int
+    interleave: int = 0
     kind: str = "swiglu"
 
 

@@ -29,8 +29,10 @@ from .safetensors_io import ModelFiles, write_safetensors
 
 @dataclass(frozen=True)
 class Source:
-    """Checkpoint tensors that make up one parameter, concatenated along dim 0."""
+    """Checkpoint tensors that make up one parameter: concatenated along dim 0, or, with
+    ``interleave`` = b, woven in blocks of b rows (b rows of the first, b of the second, ...)."""
     names: Tuple[str, ...]
+    interleave: int = 0
 
 
 class WeightError(ValueError):
@@ -87,13 +89,19 @@ def load_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source],
             stored = files.dtype(names[0])
             dt = _target_dtype(stored, spec.role, act_dtype)
             dst = torch.empty(spec.shape, dtype=dt, device=device)
-            row = 0
-            for n in names:
-                t = files.tensor(n)
-                k = t.shape[0] if t.dim() else 1
-                view = dst[row:row + k] if t.dim() else dst
-                view.copy_(t)
-                row += k
+            b = sources[pname].interleave
+            if b:
+                woven = dst.view(-1, len(names), b, *dst.shape[1:])       # [blocks, source, b rows, ...]
+                for i, n in enumerate(names):
+                    woven[:, i].copy_(files.tensor(n).view(-1, b, *dst.shape[1:]))
+            else:
+                row = 0
+                for n in names:
+                    t = files.tensor(n)
+                    k = t.shape[0] if t.dim() else 1
+                    view = dst[row:row + k] if t.dim() else dst
+                    view.copy_(t)
+                    row += k
             out[pname] = dst
         return out
     finally:
@@ -175,7 +183,7 @@ def random_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source]
     for pname, spec in params.items():
         dt = act_dtype
         dst = torch.empty(spec.shape, dtype=dt, device=device)
-        row = 0
+        row = 0                       # random numbers have no order to keep: an interleaved layout is filled the same way
         for n in sources[pname].names:
             shp, init = shapes[n]
             k = shp[0]

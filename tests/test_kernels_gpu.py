@@ -89,6 +89,11 @@ def test_swiglu(act, I):
     ops.swiglu(gu, out)
     g, u = gu.float()[:, :I], gu.float()[:, I:]
     assert torch.allclose(out.float(), g * torch.sigmoid(g) * u, **_tol(act))
+    if I % 8 == 0:                       # the woven layout: blocks of 8 gate columns then 8 up columns
+        woven = torch.stack([gu[:, :I].reshape(13, -1, 8), gu[:, I:].reshape(13, -1, 8)], dim=2).reshape(13, 2 * I).contiguous()
+        out2 = torch.empty_like(out)
+        ops.swiglu(woven, out2, interleave=8)
+        assert torch.equal(out2, out)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 257), (65, 64, 16), (100, 200, 96), (2, 384, 96)])
@@ -131,6 +136,26 @@ def test_gemm_skinny(M, N, K, out_dtype):
     out2 = torch.empty_like(out)
     ops.gemm_skinny(big[:, :K], w, out2)
     assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 32, 50])
+@pytest.mark.parametrize("I,K", [(8, 32), (104, 40), (224, 96), (3072, 1024)])
+def test_gated_linear(M, I, K):
+    """The gated product (SwiGLU in the epilogue for few rows, product + kernel otherwise) against plain math."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    gate = (torch.randn(I, K, generator=g) / K ** 0.5).bfloat16()
+    up = (torch.randn(I, K, generator=g) / K ** 0.5).bfloat16()
+    woven = torch.stack([gate.view(-1, 8, K), up.view(-1, 8, K)], dim=1).reshape(2 * I, K).contiguous().to(DEV)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gated_linear(x, woven, out, 8)
+    gg, uu = x.float().cpu() @ gate.float().T, x.float().cpu() @ up.float().T
+    assert torch.allclose(out.float().cpu(), gg * torch.sigmoid(gg) * uu, atol=2e-2, rtol=3e-2)
+    plain_layout = torch.cat([gate, up]).to(DEV)
+    out2 = torch.empty_like(out)
+    ops.gated_linear(x, plain_layout, out2, 0)
+    assert torch.allclose(out2.float(), out.float(), atol=2e-2, rtol=3e-2)
 
 
 def test_linear_bf16_float32_out():

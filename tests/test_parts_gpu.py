@@ -48,15 +48,19 @@ def test_rope_part_tables():
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_feed_forward_part(dtype):
     from return_b200.parts import FEED_FORWARDS, SwiGLUSpec
-    ff = FEED_FORWARDS.build(SwiGLUSpec(hidden_size=40, intermediate_size=104), _env(dtype))
-    assert {k: v.shape for k, v in ff.params().items()} == {"gate_up": (208, 40), "down": (40, 104)}
     g, u, d = (0.2 * torch.randn(104, 40), 0.2 * torch.randn(104, 40), 0.2 * torch.randn(40, 104))
     rd = lambda t: t.to(dtype).float()
-    ff.bind({"gate_up": torch.cat([g, u]).to(dtype).to(DEV), "down": d.to(dtype).to(DEV)})
-    x = torch.randn(9, 40).to(dtype)
-    y = ff.forward(x.to(DEV), None)
     w = {"mlp.gate_proj.weight": rd(g), "mlp.up_proj.weight": rd(u), "mlp.down_proj.weight": rd(d)}
-    assert torch.allclose(y.float().cpu(), plain.swiglu_mlp(w, "", x.float()), **_tol(dtype))
+    for interleave in (0, 8):
+        ff = FEED_FORWARDS.build(SwiGLUSpec(hidden_size=40, intermediate_size=104, interleave=interleave), _env(dtype))
+        assert {k: v.shape for k, v in ff.params().items()} == {"gate_up": (208, 40), "down": (40, 104)}
+        gate_up = torch.cat([g, u]) if interleave == 0 else \
+            torch.stack([g.view(-1, 8, 40), u.view(-1, 8, 40)], dim=1).reshape(208, 40)
+        ff.bind({"gate_up": gate_up.to(dtype).to(DEV), "down": d.to(dtype).to(DEV)})
+        for rows in (9, 40):                 # few rows and many rows take different kernels on the bfloat16 path
+            x = torch.randn(rows, 40).to(dtype)
+            y = ff.forward(x.to(DEV), None)
+            assert torch.allclose(y.float().cpu(), plain.swiglu_mlp(w, "", x.float()), **_tol(dtype))
 
 
 def _runner_for(spec, params, dtype, page_size=8, max_token=512, max_reside=4):

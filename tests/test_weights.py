@@ -54,8 +54,11 @@ def test_fused_parameters_are_concatenations(tmp_path):
     p = "model.layers.1."
     qkv = torch.cat([f.tensor(p + f"self_attn.{x}_proj.weight") for x in "qkv"])
     assert torch.equal(params["layers.1.mixer.qkv"], qkv)
-    gu = torch.cat([f.tensor(p + "mlp.gate_proj.weight"), f.tensor(p + "mlp.up_proj.weight")])
+    # gate and up rows are woven in blocks of 8: [g0..g7, u0..u7, g8..g15, u8..u15, ...]
+    g, u = f.tensor(p + "mlp.gate_proj.weight"), f.tensor(p + "mlp.up_proj.weight")
+    gu = torch.stack([g.view(-1, 8, 96), u.view(-1, 8, 96)], dim=1).reshape(-1, 96)
     assert torch.equal(params["layers.1.feed_forward.gate_up"], gu)
+    assert torch.equal(gu[:8], g[:8]) and torch.equal(gu[8:16], u[:8]) and torch.equal(gu[16:24], g[8:16])
 
 
 def test_dtype_rule(tmp_path):
