@@ -198,3 +198,30 @@ def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0) -> Dict[str,
     ms = _time_kernels(fns, iters, warmup)
     return {"kernel": "linear", "M": M, "N": N, "K": K, "ms": ms, "GBps": N * K * 2 / ms / 1e6,
             "TFLOPs": 2.0 * M * N * K / ms / 1e9}
+
+
+def probe_mma_rate(iters=2000) -> Dict[str, object]:
+    """Cycles per mma.sync.m16n8k16 per warp, with one dependent chain (latency) and with eight
+    independent ones (issue rate), for 1 to 16 warps on every SM."""
+    import ctypes
+    from .ext import build
+    lib = build.load("return_probes", ["probes.cu"])
+    lib.rb_probe_mma_rate.argtypes = [ctypes.c_int] * 4 + [ctypes.c_void_p] * 3
+    lib.rb_probe_mma_rate.restype = ctypes.c_int
+    dev = torch.device("cuda:0")
+    sink = torch.zeros(4, device=dev)
+    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
+    rows = []
+    for warps in (1, 2, 4, 8, 16):
+        row = {"warps_per_sm": warps}
+        for chains in (1, 8):
+            rc = lib.rb_probe_mma_rate(148, warps, chains, iters, ctypes.c_void_p(sink.data_ptr()),
+                                       ctypes.c_void_p(cyc.data_ptr()),
+                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            assert rc == 0
+            per = float(cyc.item()) / (iters * chains)
+            row[f"cycles_per_mma_{chains}chain"] = round(per, 1)
+            if chains == 8:
+                row["fma_per_cycle_per_sm"] = round(warps * 2048.0 / per)
+        rows.append(row)
+    return {"probe": "mma_rate", "rows": rows}
