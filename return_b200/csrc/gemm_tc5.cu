@@ -1,0 +1,316 @@
+// out[M, N] = x[M, K] * W[N, K]^T in bfloat16 on the fifth-generation tensor cores (tcgen05), float32
+// accumulation in tensor memory, operands brought in by TMA.
+//
+//   rb_tc5_gemm          the product path for many rows: one CTA per 128 x BN output tile; a producer
+//                        thread streams 64-wide K blocks of both operands through a ring of
+//                        shared-memory stages with cp.async.bulk.tensor (128-byte swizzle), an MMA
+//                        thread issues tcgen05.mma (M = 128, N = BN, K = 16) into TMEM and frees each
+//                        stage with tcgen05.commit, four epilogue warps read the accumulator with
+//                        tcgen05.ld and store it.  Optional epilogue: SwiGLU over gate/up columns
+//                        woven in blocks of 8 (see SwiGLUSpec).
+//   rb_tc5_gemm_simple   the same tile computed with plain loads and one stage: the small twin that
+//                        pins the descriptor encodings down in tests.
+//
+// Every mbarrier wait is bounded; a wait that gives up raises *status and the kernel still frees its
+// TMEM and returns.
+#include <cuda.h>
+
+#include "tc5.cuh"
+
+namespace {
+
+using namespace tc5;
+
+constexpr int BM = 128;
+constexpr int BK = 64;                    // bf16 elements: one 128-byte swizzle row
+
+__device__ __forceinline__ void store_row_chunk(float* dst, const unsigned (&r)[32], int n_valid) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+        if (j < n_valid) dst[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void store_row_chunk(bf16* dst, const unsigned (&r)[32], int n_valid) {
+    if (n_valid == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+            v.x = *reinterpret_cast<unsigned*>(&p0); v.y = *reinterpret_cast<unsigned*>(&p1);
+            v.z = *reinterpret_cast<unsigned*>(&p2); v.w = *reinterpret_cast<unsigned*>(&p3);
+            *reinterpret_cast<uint4*>(dst + j) = v;
+        }
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+        if (j < n_valid) dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+}
+
+// ------------------------------------------------------------------------------------ the small twin
+template <int BN, typename TOut>
+__global__ void __launch_bounds__(128)
+tc5_gemm_simple_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ out,
+                       int M, int N, int K, int ldx, int ldw, int ldo, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sA = base;                             // 128 rows x 128 B
+    unsigned char* sB = base + BM * 128;                  // BN rows x 128 B
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ unsigned tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const unsigned bar = smem_u32(&bar_storage);
+    constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    if (tid == 0) { mbar_init(bar, 1); mbar_init_fence(); }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const unsigned tacc = tmem_slot;
+    const unsigned idesc = instr_desc_bf16(BM, BN);
+    unsigned phase = 0;
+    bool ok = true;
+
+    const int nkb = (K + BK - 1) / BK;
+    for (int kb = 0; kb < nkb; ++kb) {
+        for (int c = tid; c < BM * 8; c += 128) {
+            const int r = c >> 3, ch = c & 7, m = m0 + r, k = kb * BK + ch * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (m < M && k < K) v = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k);
+            *reinterpret_cast<uint4*>(sA + sw128_offset(r, ch)) = v;
+        }
+        for (int c = tid; c < BN * 8; c += 128) {
+            const int r = c >> 3, ch = c & 7, n = n0 + r, k = kb * BK + ch * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (n < N && k < K) v = *reinterpret_cast<const uint4*>(w + (size_t)n * ldw + k);
+            *reinterpret_cast<uint4*>(sB + sw128_offset(r, ch)) = v;
+        }
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+            fence_after_sync();
+#pragma unroll
+            for (int k16 = 0; k16 < BK / 16; ++k16)
+                mma_ss(tacc, smem_desc_sw128(smem_u32(sA), k16 * 32), smem_desc_sw128(smem_u32(sB), k16 * 32), idesc,
+                       kb > 0 || k16 > 0);
+            mma_commit(bar);
+        }
+        ok = mbar_wait(bar, phase) && ok;                   // the MMAs have read this stage: it may be refilled
+        phase ^= 1;
+        __syncthreads();
+    }
+    if (!ok && lane == 0) atomicExch(status, 1);
+    fence_after_sync();
+    const int m = m0 + warp * 32 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        unsigned r[32];
+        tmem_ld32(tacc + ((unsigned)(warp * 32) << 16) + c0, r);
+        tmem_ld_wait();
+        if (m < M && n0 + c0 < N) store_row_chunk(out + (size_t)m * ldo + n0 + c0, r, min(32, N - n0 - c0));
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tacc, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------ the product kernel
+__device__ __forceinline__ void tma_load_2d(unsigned smem_dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+constexpr int TC5_THREADS = 192;          // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
+
+template <int BN, int STAGES, typename TOut, bool GATED>
+__global__ void __launch_bounds__(TC5_THREADS)
+tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                TOut* __restrict__ out, int M, int N, int K, int ldo, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr unsigned A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ unsigned tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+    const int nkb = (K + BK - 1) / BK;
+
+    if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    if (tid == 0) {
+        tma_prefetch_desc(&map_x);
+        tma_prefetch_desc(&map_w);
+#pragma unroll
+        for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        mbar_init(smem_u32(&acc_bar), 1);
+        mbar_init_fence();
+    }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    pdl_wait();                                             // the tokens come from the kernel before
+    const unsigned tacc = tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {                                    // ---- producer
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES) ok = mbar_wait(smem_u32(&empty_bar[s]), ((kb / STAGES) - 1) & 1) && ok;
+                const unsigned full = smem_u32(&full_bar[s]);
+                mbar_arrive_expect_tx(full, STAGE_BYTES);
+                const unsigned dst = smem_u32(base + (size_t)s * STAGE_BYTES);
+                tma_load_2d(dst, &map_x, kb * BK, m0, full);
+                tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                                    // ---- MMA issuer
+            const unsigned idesc = instr_desc_bf16(BM, BN);
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(smem_u32(&full_bar[s]), (kb / STAGES) & 1) && ok;
+                fence_after_sync();
+                const unsigned a = smem_u32(base + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+                for (int k16 = 0; k16 < BK / 16; ++k16)
+                    mma_ss(tacc, smem_desc_sw128(a, k16 * 32), smem_desc_sw128(b, k16 * 32), idesc, kb > 0 || k16 > 0);
+                mma_commit(smem_u32(&empty_bar[s]));        // the stage is free once these MMAs have read it
+            }
+            mma_commit(smem_u32(&acc_bar));                 // the accumulator is complete
+        }
+    } else {                                                // ---- epilogue: TMEM lanes by warp % 4
+        ok = mbar_wait(smem_u32(&acc_bar), 0) && ok;
+        pdl_trigger_late();
+        fence_after_sync();
+        const int q = warp & 3;
+        const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            unsigned r[32];
+            tmem_ld32(tacc + ((unsigned)(q * 32) << 16) + c0, r);
+            tmem_ld_wait();
+            if (m >= M || n0 + c0 >= N) continue;
+            if (GATED) {
+                // columns come in blocks of 8 gate values and their 8 up values: 32 columns give 16 outputs
+                unsigned g[32];
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float gate = __uint_as_float(r[b * 16 + j]), up = __uint_as_float(r[b * 16 + 8 + j]);
+                        g[b * 8 + j] = __float_as_uint(gate / (1.0f + expf(-gate)) * up);
+                    }
+#pragma unroll
+                for (int j = 16; j < 32; ++j) g[j] = 0u;
+                TOut* dst = out + (size_t)m * ldo + ((n0 + c0) >> 1);
+                const int valid = min(16, (N - n0 - c0) >> 1);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (j < valid) dst[j] = from_f32<TOut>(__uint_as_float(g[j]));
+            } else {
+                store_row_chunk(out + (size_t)m * ldo + n0 + c0, r, min(32, N - n0 - c0));
+            }
+        }
+    }
+    if (!ok) atomicExch(status, 1);
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tacc, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A row-major [rows, cols] bf16 matrix with row stride ld (elements): boxes of box_rows x 64 columns.
+bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, typename TOut, bool GATED>
+int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo, int* status,
+               cudaStream_t st) {
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)STAGES * (BM + BN) * BK * 2 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN, STAGES, TOut, GATED>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    return rb_launch_pdl(tc5_gemm_kernel<BN, STAGES, TOut, GATED>, grid, dim3(TC5_THREADS), smem, st, mx, mw,
+                         (TOut*)out, M, N, K, ldo, status);
+}
+
+}  // namespace
+
+// out dtype: 0 bfloat16, 1 float32.  gated: SwiGLU epilogue over woven gate/up columns (out is [M, N/2]).
+// status: one int in device memory, set to 1 if a wait inside the kernel gave up (zero it beforehand).
+RB_EXPORT int rb_tc5_gemm(const void* x, const void* w, void* out, int out_f32, int gated, int M, int N, int K,
+                          int ldx, int ldw, int ldo, int* status, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return (int)cudaErrorInvalidValue;
+    if (gated) {
+        if (out_f32 || N % 16) return (int)cudaErrorInvalidValue;
+        return launch_tc5<256, 4, bf16, true>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    }
+    if (out_f32) return launch_tc5<256, 4, float, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    return launch_tc5<256, 4, bf16, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+}
+
+RB_EXPORT int rb_tc5_gemm_simple(const void* x, const void* w, void* out, int out_f32, int bn, int M, int N, int K,
+                                 int ldx, int ldw, int ldo, int* status, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K % 8 || ldx % 8 || ldw % 8) return (int)cudaErrorInvalidValue;
+    dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM);
+    const size_t smem = (size_t)(BM + bn) * 128 + 1024;
+#define RB_SIMPLE(BN_, T_)                                                                                           \
+    {                                                                                                                \
+        cudaFuncSetAttribute(tc5_gemm_simple_kernel<BN_, T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        tc5_gemm_simple_kernel<BN_, T_><<<grid, 128, smem, st>>>((const bf16*)x, (const bf16*)w, (T_*)out, M, N, K,  \
+                                                                 ldx, ldw, ldo, status);                             \
+        return rb_launch_status();                                                                                   \
+    }
+    if (bn == 64 && out_f32) RB_SIMPLE(64, float)
+    if (bn == 64) RB_SIMPLE(64, bf16)
+    if (bn == 128 && out_f32) RB_SIMPLE(128, float)
+    if (bn == 128) RB_SIMPLE(128, bf16)
+    if (bn == 256 && out_f32) RB_SIMPLE(256, float)
+    if (bn == 256) RB_SIMPLE(256, bf16)
+#undef RB_SIMPLE
+    return (int)cudaErrorInvalidValue;
+}

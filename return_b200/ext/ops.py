@@ -94,6 +94,7 @@ PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
+    paths.append(build.library_path("return_tc5", ["gemm_tc5.cu"], {"RB_PDL_MODE": PDL_MODE}))
     for d in PREBUILT_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], {"HEAD_DIM": d, "RB_PDL_MODE": PDL_MODE}))
     return paths
@@ -191,6 +192,53 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, interleave
     gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
     linear(x, w, gu)
     swiglu(gu, out, interleave)
+
+
+_tc5 = None
+
+
+def tc5_lib() -> ctypes.CDLL:
+    """The tcgen05 / TMA matrix-product library."""
+    global _tc5
+    if _tc5 is None:
+        lib = build.load("return_tc5", ["gemm_tc5.cu"], {"RB_PDL_MODE": PDL_MODE})
+        P, I = c_void_p, c_int
+        lib.rb_tc5_gemm.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, P]
+        lib.rb_tc5_gemm_simple.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, P]
+        lib.rb_tc5_gemm.restype = lib.rb_tc5_gemm_simple.restype = c_int
+        _tc5 = lib
+    return _tc5
+
+
+_tc5_status = {}
+
+
+def tc5_status(device) -> torch.Tensor:
+    """One int per device that a tcgen05 kernel raises when one of its bounded waits gave up."""
+    t = _tc5_status.get(device)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _tc5_status[device] = t
+    return t
+
+
+def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False, simple_bn: int = 0) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T on the tcgen05 tensor cores (TMA-fed).  ``gated``: SwiGLU epilogue over
+    woven gate/up rows of w, out [M, N/2].  ``simple_bn``: run the one-stage twin with that tile width."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+    assert w.shape[1] == K and out.shape == (M, N // 2 if gated else N)
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    status = tc5_status(x.device)
+    f32 = 1 if out.dtype == torch.float32 else 0
+    if simple_bn:
+        rc = tc5_lib().rb_tc5_gemm_simple(_ptr(x), _ptr(w), _ptr(out), f32, simple_bn, M, N, K, x.stride(0),
+                                          w.stride(0), out.stride(0), _ptr(status), _stream())
+    else:
+        rc = tc5_lib().rb_tc5_gemm(_ptr(x), _ptr(w), _ptr(out), f32, 1 if gated else 0, M, N, K, x.stride(0),
+                                   w.stride(0), out.stride(0), _ptr(status), _stream())
+    _check(rc, "gemm_tc5")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -1,0 +1,66 @@
+"""The tcgen05 / TMA matrix product against plain math: first the one-stage twin that pins the
+descriptor encodings down, then the pipelined kernel, at sizes with tails in every dimension."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ops():
+    from return_b200.ext import ops
+    return ops
+
+
+def _case(M, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).bfloat16().to(DEV)
+    return x, w, x.double() @ w.double().T
+
+
+def _status_clear(ops):
+    st = ops.tc5_status(torch.device(DEV))
+    torch.cuda.synchronize()
+    flag = int(st.item())
+    st.zero_()
+    return flag
+
+
+@pytest.mark.parametrize("bn", [64, 128, 256])
+@pytest.mark.parametrize("M,N,K", [(128, 64, 64), (128, 256, 128), (100, 200, 72), (300, 520, 1000)])
+def test_one_stage_twin(bn, M, N, K):
+    ops = _ops()
+    x, w, want = _case(M, N, K, M + N + K)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_tc5(x, w, out, simple_bn=bn)
+    assert _status_clear(ops) == 0, "a bounded wait inside the kernel gave up"
+    assert (out.double() - want).abs().max() < 2e-3
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (33, 40, 72), (300, 520, 1000), (2048, 1024, 4096),
+                                   (129, 257 * 8, 264)])
+def test_pipelined_product(M, N, K, out_dtype):
+    ops = _ops()
+    x, w, want = _case(M, N, K, M * 3 + N + K)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_tc5(x, w, out)
+    assert _status_clear(ops) == 0, "a bounded wait inside the kernel gave up"
+    tol = 2e-3 if out_dtype == torch.float32 else 3e-2
+    assert (out.double() - want).abs().max() < tol
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (200, 104, 136), (512, 3072, 1024)])
+def test_pipelined_product_with_swiglu_epilogue(M, I, K):
+    ops = _ops()
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    gate = (torch.randn(I, K, generator=g) / K ** 0.5).bfloat16()
+    up = (torch.randn(I, K, generator=g) / K ** 0.5).bfloat16()
+    woven = torch.stack([gate.view(-1, 8, K), up.view(-1, 8, K)], dim=1).reshape(2 * I, K).contiguous().to(DEV)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc5(x, woven, out, gated=True)
+    assert _status_clear(ops) == 0
+    gg, uu = x.float().cpu() @ gate.float().T, x.float().cpu() @ up.float().T
+    assert torch.allclose(out.float().cpu(), gg * torch.sigmoid(gg) * uu, atol=2e-2, rtol=3e-2)
