@@ -130,6 +130,10 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
 
 constexpr int TC5_THREADS = 192;          // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
 
+// Persistent: a CTA walks output tiles tile = blockIdx.x, + gridDim.x, ...; tiles that share a block
+// of W are neighbours (the M tile index runs fastest), so W is read from HBM once and X stays in L2.
+// The accumulator is double-buffered in TMEM (2 x BN columns): the epilogue warps drain tile i while
+// the MMA thread fills tile i + 1.  The ring of operand stages runs on across tiles.
 template <int BN, int STAGES, typename TOut, bool GATED>
 __global__ void __launch_bounds__(TC5_THREADS)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -137,12 +141,13 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     constexpr unsigned A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_bar;
+    __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-    constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+    constexpr unsigned TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
     const int nkb = (K + BK - 1) / BK;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, tiles = m_tiles * n_tiles;
 
     if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
     if (tid == 0) {
@@ -150,7 +155,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         tma_prefetch_desc(&map_w);
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        mbar_init(smem_u32(&acc_bar), 1);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&acc_full[b]), 1); mbar_init(smem_u32(&acc_empty[b]), 4); }
         mbar_init_fence();
     }
     fence_before_sync();
@@ -162,63 +168,76 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     if (warp == 0) {
         if (lane == 0) {                                    // ---- producer
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES) ok = mbar_wait(smem_u32(&empty_bar[s]), ((kb / STAGES) - 1) & 1) && ok;
-                const unsigned full = smem_u32(&full_bar[s]);
-                mbar_arrive_expect_tx(full, STAGE_BYTES);
-                const unsigned dst = smem_u32(base + (size_t)s * STAGE_BYTES);
-                tma_load_2d(dst, &map_x, kb * BK, m0, full);
-                tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full);
+            int it = 0;                                     // k blocks issued so far, over all tiles
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES) ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / STAGES) - 1) & 1) && ok;
+                    const unsigned full = smem_u32(&full_bar[s]);
+                    mbar_arrive_expect_tx(full, STAGE_BYTES);
+                    const unsigned dst = smem_u32(base + (size_t)s * STAGE_BYTES);
+                    tma_load_2d(dst, &map_x, kb * BK, m0, full);
+                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full);
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {                                    // ---- MMA issuer
             const unsigned idesc = instr_desc_bf16(BM, BN);
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % STAGES;
-                ok = mbar_wait(smem_u32(&full_bar[s]), (kb / STAGES) & 1) && ok;
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (local >= 2) ok = mbar_wait(smem_u32(&acc_empty[buf]), ((local >> 1) - 1) & 1) && ok;
                 fence_after_sync();
-                const unsigned a = smem_u32(base + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
+                const unsigned d = tacc + buf * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1) && ok;
+                    fence_after_sync();
+                    const unsigned a = smem_u32(base + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
 #pragma unroll
-                for (int k16 = 0; k16 < BK / 16; ++k16)
-                    mma_ss(tacc, smem_desc_sw128(a, k16 * 32), smem_desc_sw128(b, k16 * 32), idesc, kb > 0 || k16 > 0);
-                mma_commit(smem_u32(&empty_bar[s]));        // the stage is free once these MMAs have read it
+                    for (int k16 = 0; k16 < BK / 16; ++k16)
+                        mma_ss(d, smem_desc_sw128(a, k16 * 32), smem_desc_sw128(b, k16 * 32), idesc, kb > 0 || k16 > 0);
+                    mma_commit(smem_u32(&empty_bar[s]));    // the stage is free once these MMAs have read it
+                }
+                mma_commit(smem_u32(&acc_full[buf]));       // this tile's accumulator is complete
             }
-            mma_commit(smem_u32(&acc_bar));                 // the accumulator is complete
         }
     } else {                                                // ---- epilogue: TMEM lanes by warp % 4
-        ok = mbar_wait(smem_u32(&acc_bar), 0) && ok;
-        pdl_trigger_late();
-        fence_after_sync();
         const int q = warp & 3;
-        const int m = m0 + q * 32 + lane;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            const int buf = local & 1;
+            ok = mbar_wait(smem_u32(&acc_full[buf]), (local >> 1) & 1) && ok;
+            if (tile + (int)gridDim.x >= tiles) pdl_trigger_late();        // the last tile of this CTA
+            fence_after_sync();
+            const int m = m0 + q * 32 + lane;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-            unsigned r[32];
-            tmem_ld32(tacc + ((unsigned)(q * 32) << 16) + c0, r);
-            tmem_ld_wait();
-            if (m >= M || n0 + c0 >= N) continue;
-            if (GATED) {
-                // columns come in blocks of 8 gate values and their 8 up values: 32 columns give 16 outputs
-                unsigned g[32];
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                unsigned r[32];
+                tmem_ld32(tacc + ((unsigned)(q * 32) << 16) + buf * BN + c0, r);
+                tmem_ld_wait();
+                if (m >= M || n0 + c0 >= N) continue;
+                if (GATED) {
+                    // columns come in blocks of 8 gate values and their 8 up values: 32 columns give 16 outputs
+                    TOut* dst = out + (size_t)m * ldo + ((n0 + c0) >> 1);
+                    const int valid = min(16, (N - n0 - c0) >> 1);
 #pragma unroll
-                for (int b = 0; b < 2; ++b)
+                    for (int b = 0; b < 2; ++b)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float gate = __uint_as_float(r[b * 16 + j]), up = __uint_as_float(r[b * 16 + 8 + j]);
-                        g[b * 8 + j] = __float_as_uint(gate / (1.0f + expf(-gate)) * up);
-                    }
-#pragma unroll
-                for (int j = 16; j < 32; ++j) g[j] = 0u;
-                TOut* dst = out + (size_t)m * ldo + ((n0 + c0) >> 1);
-                const int valid = min(16, (N - n0 - c0) >> 1);
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (j < valid) dst[j] = from_f32<TOut>(__uint_as_float(g[j]));
-            } else {
-                store_row_chunk(out + (size_t)m * ldo + n0 + c0, r, min(32, N - n0 - c0));
+                        for (int j = 0; j < 8; ++j) {
+                            const float gate = __uint_as_float(r[b * 16 + j]), up = __uint_as_float(r[b * 16 + 8 + j]);
+                            if (b * 8 + j < valid) dst[b * 8 + j] = from_f32<TOut>(gate / (1.0f + expf(-gate)) * up);
+                        }
+                } else {
+                    store_row_chunk(out + (size_t)m * ldo + n0 + c0, r, min(32, N - n0 - c0));
+                }
             }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));         // this warp has drained its quarter
         }
     }
     if (!ok) atomicExch(status, 1);
@@ -271,7 +290,14 @@ int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    static int num_sms = 0;
+    if (num_sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    dim3 grid(tiles < num_sms ? tiles : num_sms);
     return rb_launch_pdl(tc5_gemm_kernel<BN, STAGES, TOut, GATED>, grid, dim3(TC5_THREADS), smem, st, mx, mw,
                          (TOut*)out, M, N, K, ldo, status);
 }
