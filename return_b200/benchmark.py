@@ -170,18 +170,21 @@ def kernel_attention_decode(batch=64, ctx=2048, heads=32, kv_heads=8, head_dim=1
 
 
 def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8, head_dim=128, page=16,
-                             iters=10, warmup=3) -> Dict[str, float]:
-    """The prefill attention kernel alone: device time and causal TFLOP/s."""
+                             iters=10, warmup=3, impl=0) -> Dict[str, float]:
+    """The prefill attention kernel alone: device time and causal TFLOP/s.
+    ``impl`` 0: the tcgen05 kernel (head sizes 64 and 128); 1: the mma.sync kernel."""
     from .ext import ops
     dev = torch.device("cuda:0")
     qkv, k_pool, v_pool, bt, cu_q, seg_pos0, _ = _paged_case(batch, ctx, q_len, heads, kv_heads, head_dim, page, dev)
     out = torch.empty((batch * q_len, heads * head_dim), dtype=torch.bfloat16, device=dev)
-    tiles = torch.tensor([(i, r) for i in range(batch) for r in range(0, q_len, 64)], dtype=torch.int32, device=dev)
-    fn = lambda: ops.attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, bt, page, out, heads,
-                                           kv_heads, head_dim, head_dim ** -0.5, 0)
+    rows = 64 if impl else 128
+    tiles = torch.tensor([(i, r) for i in range(batch) for r in range(0, q_len, rows)], dtype=torch.int32, device=dev)
+    kernel = ops.attention_prefill_mma if impl else ops.attention_prefill_tc5
+    fn = lambda: kernel(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, bt, page, out, heads,
+                        kv_heads, head_dim, head_dim ** -0.5, 0)
     ms = _time_kernels([fn], iters, warmup)
     flops = 4.0 * batch * heads * head_dim * (q_len * (ctx - q_len) + q_len * q_len / 2.0)
-    return {"kernel": "attention_prefill", "batch": batch, "ctx": ctx, "q_len": q_len, "ms": ms,
+    return {"kernel": "attention_prefill_mma" if impl else "attention_prefill_tc5", "batch": batch, "ctx": ctx, "q_len": q_len, "ms": ms,
             "TFLOPs": flops / ms / 1e9}
 
 

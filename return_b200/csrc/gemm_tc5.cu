@@ -118,6 +118,75 @@ tc5_gemm_simple_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, T
     if (warp == 0) tmem_dealloc(tacc, TMEM_COLS);
 }
 
+// The twin with B given as [K, N] row-major (N contiguous): an MN-major B operand, as the values of
+// an attention tile are.  One 128 x BN tile per CTA, K a multiple of 64.  The descriptor's leading
+// offset (8192 B) steps over blocks of 64 columns of N, its stride offset (1024 B) over groups of 8 k-rows.
+template <int BN>
+__global__ void __launch_bounds__(128)
+tc5_gemm_bmn_kernel(const bf16* __restrict__ x, const bf16* __restrict__ bmat, float* __restrict__ out,
+                    int M, int N, int K, int ldx, int ldb, int ldo, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* sA = base;                             // 128 rows x 128 B
+    unsigned char* sB = base + BM * 128;                  // BN / 64 slabs of 64 k-rows x 128 B
+    __shared__ __align__(8) unsigned long long bar_storage;
+    __shared__ unsigned tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const unsigned bar = smem_u32(&bar_storage);
+    constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+    if (warp == 0) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    if (tid == 0) { mbar_init(bar, 1); mbar_init_fence(); }
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const unsigned tacc = tmem_slot;
+    const unsigned idesc = instr_desc_bf16(BM, BN, true);
+    unsigned phase = 0;
+    bool ok = true;
+    for (int kb = 0; kb < K / BK; ++kb) {
+        for (int c = tid; c < BM * 8; c += 128) {
+            const int r = c >> 3, ch = c & 7, m = m0 + r, k = kb * BK + ch * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (m < M) v = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k);
+            *reinterpret_cast<uint4*>(sA + sw128_offset(r, ch)) = v;
+        }
+        for (int c = tid; c < BK * (BN / 8); c += 128) {      // 64 k-rows, BN / 8 chunks of 8 n
+            const int kr = c / (BN / 8), nc = c % (BN / 8), n = n0 + nc * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (n < N) v = *reinterpret_cast<const uint4*>(bmat + (size_t)(kb * BK + kr) * ldb + n);
+            *reinterpret_cast<uint4*>(sB + (nc >> 3) * 8192 + sw128_offset(kr, nc & 7)) = v;
+        }
+        fence_proxy_async();
+        __syncthreads();
+        if (tid == 0) {
+            fence_after_sync();
+#pragma unroll
+            for (int k16 = 0; k16 < BK / 16; ++k16) {
+                mma_ss(tacc, smem_desc_sw128(smem_u32(sA), k16 * 32),
+                       smem_desc_sw128_mn(smem_u32(sB) + k16 * 2048, 8192u, 1024u), idesc, kb > 0 || k16 > 0);
+            }
+            mma_commit(bar);
+        }
+        ok = mbar_wait(bar, phase) && ok;
+        phase ^= 1;
+        __syncthreads();
+    }
+    if (!ok && lane == 0) atomicExch(status, 1);
+    fence_after_sync();
+    const int m = m0 + warp * 32 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        unsigned r[32];
+        tmem_ld32(tacc + ((unsigned)(warp * 32) << 16) + c0, r);
+        tmem_ld_wait();
+        if (m < M && n0 + c0 < N) store_row_chunk(out + (size_t)m * ldo + n0 + c0, r, min(32, N - n0 - c0));
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tacc, TMEM_COLS);
+}
+
 // ------------------------------------------------------------------------------------ the product kernel
 __device__ __forceinline__ void tma_load_2d(unsigned smem_dst, const CUtensorMap* map, int x, int y, unsigned bar) {
     asm volatile(
@@ -338,5 +407,26 @@ RB_EXPORT int rb_tc5_gemm_simple(const void* x, const void* w, void* out, int ou
     if (bn == 256 && out_f32) RB_SIMPLE(256, float)
     if (bn == 256) RB_SIMPLE(256, bf16)
 #undef RB_SIMPLE
+    return (int)cudaErrorInvalidValue;
+}
+
+// out[M, N] (float32) = x[M, K] * b[K, N] with b row-major: the MN-major-B twin.  bn in {64, 128, 256}, K % 64 == 0, N % 8 == 0.
+RB_EXPORT int rb_tc5_gemm_bmn(const void* x, const void* b, float* out, int bn, int M, int N, int K, int ldx, int ldb,
+                              int ldo, int* status, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K % 64 || N % 8 || ldx % 8 || ldb % 8) return (int)cudaErrorInvalidValue;
+    dim3 grid((N + bn - 1) / bn, (M + BM - 1) / BM);
+    const size_t smem = (size_t)BM * 128 + (size_t)bn * 128 + 1024;
+#define RB_BMN(BN_)                                                                                                   \
+    {                                                                                                                 \
+        cudaFuncSetAttribute(tc5_gemm_bmn_kernel<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+        tc5_gemm_bmn_kernel<BN_><<<grid, 128, smem, st>>>((const bf16*)x, (const bf16*)b, out, M, N, K, ldx, ldb, ldo, \
+                                                          status);                                              \
+        return rb_launch_status();                                                                                    \
+    }
+    if (bn == 64) RB_BMN(64)
+    if (bn == 128) RB_BMN(128)
+    if (bn == 256) RB_BMN(256)
+#undef RB_BMN
     return (int)cudaErrorInvalidValue;
 }

@@ -99,12 +99,27 @@ __device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned tile_smem
     return d;
 }
 
-// Instruction descriptor for kind::f16: bf16 x bf16 -> f32, both operands K-major, tile M x N.
-__device__ __forceinline__ unsigned instr_desc_bf16(int M, int N) {
+// The same tile read as an MN-major operand (the 128-byte rows run along M or N, successive rows
+// along K): `lead` bytes between blocks of 64 elements along M/N, `stride` bytes between groups of
+// 8 rows along K.
+__device__ __forceinline__ unsigned long long smem_desc_sw128_mn(unsigned start_smem_addr, unsigned lead, unsigned stride) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((start_smem_addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)((lead >> 4) & 0x3FFFu) << 16;
+    d |= (unsigned long long)((stride >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;
+    d |= 2ull << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: bf16 x bf16 -> f32, tile M x N.  A is K-major; B is K-major,
+// or MN-major (its rows run along N) with b_mn_major.
+__device__ __forceinline__ unsigned instr_desc_bf16(int M, int N, bool b_mn_major = false) {
     unsigned d = 0;
     d |= 1u << 4;                       // accumulator format: f32
     d |= 1u << 7;                       // A format: bf16
     d |= 1u << 10;                      // B format: bf16
+    d |= (b_mn_major ? 1u : 0u) << 16;  // B major: 0 K, 1 MN
     d |= (unsigned)(N >> 3) << 17;      // N / 8
     d |= (unsigned)(M >> 4) << 24;      // M / 16
     return d;

@@ -42,11 +42,13 @@ class HostBatch:
     want_rows: np.ndarray     # [n_want] token rows whose logits are wanted
     decode_segs: np.ndarray   # segments of one token
     prefill_tiles: np.ndarray  # [n_tiles, 2]: (segment, first row within it) for segments of several tokens
+    prefill_tiles128: np.ndarray = None   # the same in blocks of 128 rows (the tcgen05 attention kernel's tile)
     block_tables: List[np.ndarray] = field(default_factory=list)   # per group [n, blocks]
     rids: List[Hashable] = field(default_factory=list)
 
 
 PREFILL_TILE_ROWS = 64
+PREFILL_TILE_ROWS_TC5 = 128
 
 
 def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional[int] = None,
@@ -72,6 +74,7 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
     want_rows: List[int] = []
     decode_segs: List[int] = []
     tiles: List[tuple] = []
+    tiles128: List[tuple] = []
     row = 0
     for i, e in enumerate(entries):
         L = lens[i]
@@ -92,6 +95,7 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
             decode_segs.append(i)
         else:
             tiles.extend((i, r0) for r0 in range(0, L, PREFILL_TILE_ROWS))
+            tiles128.extend((i, r0) for r0 in range(0, L, PREFILL_TILE_ROWS_TC5))
         row += L
     if vocab_size is not None and (tokens.min() < 0 or tokens.max() >= vocab_size):
         raise ValueError(f"token ids must lie in [0, {vocab_size})")
@@ -110,14 +114,15 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
         num_tokens=T, num_segments=n, num_want=len(want_rows), tokens=tokens, pos=pos, tok_seg=tok_seg,
         seg_slot=seg_slot, cu_q=cu_q, seg_pos0=seg_pos0, seg_kv_len=seg_kv_len,
         want_rows=np.asarray(want_rows, np.int32), decode_segs=np.asarray(decode_segs, np.int32),
-        prefill_tiles=np.asarray(tiles, np.int32).reshape(-1, 2), block_tables=tables, rids=rids)
+        prefill_tiles=np.asarray(tiles, np.int32).reshape(-1, 2),
+        prefill_tiles128=np.asarray(tiles128, np.int32).reshape(-1, 2), block_tables=tables, rids=rids)
 
 
 class StepBatch:
     """The tables on the device, as views of one int32 buffer."""
 
     _FIELDS = ("tokens", "pos", "tok_seg", "seg_slot", "cu_q", "seg_pos0", "seg_kv_len", "want_rows",
-               "decode_segs", "prefill_tiles")
+               "decode_segs", "prefill_tiles", "prefill_tiles128")
 
     def __init__(self, host: HostBatch, device, staging: "BatchStaging"):
         self.host = host
@@ -139,6 +144,7 @@ class StepBatch:
         for f, v in zip(self._FIELDS, views):
             setattr(self, f, v)
         self.prefill_tiles = self.prefill_tiles.view(-1, 2)
+        self.prefill_tiles128 = self.prefill_tiles128.view(-1, 2)
         self.block_tables = [v.view(bt.shape) for v, bt in zip(views[len(self._FIELDS):], host.block_tables)]
 
 
@@ -183,6 +189,7 @@ class _StaticHost:
         self.num_tokens = self.num_segments = self.num_want = n
         self.decode_segs = np.arange(n, dtype=np.int32)
         self.prefill_tiles = np.zeros((0, 2), np.int32)
+        self.prefill_tiles128 = np.zeros((0, 2), np.int32)
         self.cu_q = np.arange(n + 1, dtype=np.int32)
         self.seg_slot = np.zeros(n, np.int32)
         self.seg_kv_len = np.ones(n, np.int32)
@@ -218,6 +225,7 @@ class StaticDecodeBatch:
             self._h_bt.append(hv[off:off + n * b].reshape(n, b))
             self.block_tables.append(self._dev[off:off + n * b].view(n, b))
         self.prefill_tiles = torch.zeros((0, 2), dtype=torch.int32, device=device)
+        self.prefill_tiles128 = torch.zeros((0, 2), dtype=torch.int32, device=device)
         self._h["tok_seg"][:] = np.arange(n)
         self._h["cu_q"][:] = np.arange(n + 1)
         self._h["want_rows"][:] = np.arange(n)

@@ -95,6 +95,8 @@ def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
     paths.append(build.library_path("return_tc5", ["gemm_tc5.cu"], {"RB_PDL_MODE": PDL_MODE}))
+    for d in TC5_ATTENTION_HEAD_DIMS:
+        paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], {"HEAD_DIM": d}))
     for d in PREBUILT_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], {"HEAD_DIM": d, "RB_PDL_MODE": PDL_MODE}))
     return paths
@@ -205,7 +207,8 @@ def tc5_lib() -> ctypes.CDLL:
         P, I = c_void_p, c_int
         lib.rb_tc5_gemm.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, P]
         lib.rb_tc5_gemm_simple.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, P]
-        lib.rb_tc5_gemm.restype = lib.rb_tc5_gemm_simple.restype = c_int
+        lib.rb_tc5_gemm_bmn.argtypes = [P, P, P, I, I, I, I, I, I, I, P, P]
+        lib.rb_tc5_gemm.restype = lib.rb_tc5_gemm_simple.restype = lib.rb_tc5_gemm_bmn.restype = c_int
         _tc5 = lib
     return _tc5
 
@@ -239,6 +242,15 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = 
         rc = tc5_lib().rb_tc5_gemm(_ptr(x), _ptr(w), _ptr(out), f32, 1 if gated else 0, M, N, K, x.stride(0),
                                    w.stride(0), out.stride(0), _ptr(status), _stream())
     _check(rc, "gemm_tc5")
+
+
+def gemm_tc5_bmn(x: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int = 128) -> None:
+    """out[M, N] (float32) = x[M, K] @ b[K, N], b row-major: the tcgen05 twin with an MN-major B operand."""
+    M, K = x.shape
+    N = b.shape[1]
+    assert x.dtype == b.dtype == torch.bfloat16 and out.dtype == torch.float32 and b.shape[0] == K
+    _check(tc5_lib().rb_tc5_gemm_bmn(_ptr(x), _ptr(b), _ptr(out), bn, M, N, K, x.stride(0), b.stride(0), out.stride(0),
+                                     _ptr(tc5_status(x.device)), _stream()), "gemm_tc5_bmn")
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -320,6 +332,36 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
     return lib
 
 
+_attn_tc5_libs = {}
+TC5_ATTENTION_HEAD_DIMS = (64, 128)
+
+
+def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
+    """The tcgen05 prefill attention kernel, compiled for this head size (64 or 128) on first use."""
+    lib = _attn_tc5_libs.get(head_dim)
+    if lib is None:
+        if head_dim not in TC5_ATTENTION_HEAD_DIMS:
+            raise KernelError(f"head_dim={head_dim}: the tcgen05 attention kernel takes {TC5_ATTENTION_HEAD_DIMS}")
+        lib = build.load(f"return_attn_tc5_d{head_dim}", ["attention_tc5.cu"], {"HEAD_DIM": head_dim})
+        P, I, F = c_void_p, c_int, c_float
+        lib.rb_attn_prefill_tc5.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P, P]
+        lib.rb_attn_prefill_tc5.restype = c_int
+        _attn_tc5_libs[head_dim] = lib
+    return lib
+
+
+def attention_prefill_tc5(qkv, k_pool, v_pool, tiles128, cu_q, seg_pos0, block_table, page_size, out, num_heads,
+                          num_kv_heads, head_dim, scale, window=0) -> None:
+    """tcgen05 attention for the listed (segment, first row) tiles of up to 128 query rows."""
+    assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
+    assert tiles128.dtype == torch.int32 and tiles128.is_contiguous()
+    lib = attention_tc5_lib(head_dim)
+    _check(lib.rb_attn_prefill_tc5(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles128),
+                                   tiles128.shape[0], _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table),
+                                   block_table.stride(0), page_size, _ptr(out), num_heads, num_kv_heads, scale,
+                                   int(window or 0), _ptr(tc5_status(qkv.device)), _stream()), "attention_prefill_tc5")
+
+
 NUM_SMS = 148
 
 
@@ -385,8 +427,12 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
         return
     host = batch.host
     if host.prefill_tiles.shape[0]:
-        attention_prefill_mma(qkv, k_pool, v_pool, batch.prefill_tiles, batch.cu_q, batch.seg_pos0, block_table,
-                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
+        if head_dim in TC5_ATTENTION_HEAD_DIMS:
+            attention_prefill_tc5(qkv, k_pool, v_pool, batch.prefill_tiles128, batch.cu_q, batch.seg_pos0, block_table,
+                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
+        else:
+            attention_prefill_mma(qkv, k_pool, v_pool, batch.prefill_tiles, batch.cu_q, batch.seg_pos0, block_table,
+                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
     n_dec = host.decode_segs.shape[0]
     if n_dec:
         group = num_heads // num_kv_heads

@@ -260,6 +260,27 @@ def test_attention_prefill_mma(Hq, Hkv, D, P, window):
     assert torch.allclose(out.float().cpu(), pg.reference(scale, window), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,P", [(8, 8, 64, 4), (32, 8, 128, 16), (6, 2, 128, 8), (20, 1, 64, 16), (4, 4, 128, 64)])
+@pytest.mark.parametrize("window", [None, 37, 100])
+def test_attention_prefill_tc5(Hq, Hkv, D, P, window):
+    """The tcgen05 prefill kernel: tiles of 128 rows, tails, earlier keys in the cache, windows."""
+    ops = _ops()
+    kv_lens, q_lens = [2, 70, 200, 128, 129, 300, 640], [2, 70, 3, 128, 65, 130, 300]
+    pg = Paged(kv_lens, q_lens, Hq, Hkv, D, P, torch.bfloat16, seed=D + 5)
+    tiles = [(i, r0) for i, ql in enumerate(q_lens) for r0 in range(0, ql, 128)]
+    tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    out = torch.full((sum(q_lens), Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 0.7 / math.sqrt(D)
+    ops.attention_prefill_tc5(pg.qkv, pg.kpool, pg.vpool, tiles, pg.cu_q, pg.seg_pos0, pg.bt, P, out, Hq, Hkv, D,
+                              scale, window or 0)
+    torch.cuda.synchronize()
+    st = ops.tc5_status(torch.device(DEV))
+    flag = int(st.item())
+    st.zero_()
+    assert flag == 0, "a bounded wait inside the kernel gave up"
+    assert torch.allclose(out.float().cpu(), pg.reference(scale, window), atol=3e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,P", ATT_SHAPES)
 @pytest.mark.parametrize("window", [None, 37])
 @pytest.mark.parametrize("splits", [1, 3, 8])
