@@ -234,3 +234,28 @@ def probe_mma_rate(iters=2000) -> Dict[str, object]:
                 row["fma_per_cycle_per_sm"] = round(warps * 2048.0 / per)
         rows.append(row)
     return {"probe": "mma_rate", "rows": rows}
+
+
+def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[str, float]:
+    """The gated feed-forward product out = silu(x Wg^T) * (x Wu^T) alone.  ``impl`` 0: the engine's
+    choice (``ops.gated_linear``); 1: the tcgen05 kernel with the SwiGLU epilogue; 2: cuBLAS + the SwiGLU kernel."""
+    from .ext import ops
+    dev = torch.device("cuda:0")
+    fns = []
+    for _ in range(_copies_beyond_l2(2 * I * K * 2)):
+        x = torch.randn((M, K), device=dev).bfloat16()
+        w = torch.randn((2 * I, K), device=dev).bfloat16()
+        out = torch.empty((M, I), dtype=torch.bfloat16, device=dev)
+        gu = torch.empty((M, 2 * I), dtype=torch.bfloat16, device=dev)
+        if impl == 1:
+            fns.append(lambda a=(x, w, out): ops.gemm_tc5(a[0], a[1], a[2], gated=True))
+        elif impl == 2:
+            def two(a=(x, w, out, gu)):
+                torch.mm(a[0], a[1].t(), out=a[3])
+                ops.swiglu(a[3], a[2], 8)
+            fns.append(two)
+        else:
+            fns.append(lambda a=(x, w, out): ops.gated_linear(a[0], a[1], a[2], 8))
+    ms = _time_kernels(fns, iters, warmup)
+    return {"kernel": ("gated_linear", "gemm_tc5_gated", "cublas+swiglu")[impl], "M": M, "I": I, "K": K, "ms": ms,
+            "TFLOPs": 4.0 * M * I * K / ms / 1e9}

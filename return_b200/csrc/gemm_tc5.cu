@@ -293,13 +293,29 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     // columns come in blocks of 8 gate values and their 8 up values: 32 columns give 16 outputs
                     TOut* dst = out + (size_t)m * ldo + ((n0 + c0) >> 1);
                     const int valid = min(16, (N - n0 - c0) >> 1);
+                    float g[16];
 #pragma unroll
                     for (int b = 0; b < 2; ++b)
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float gate = __uint_as_float(r[b * 16 + j]), up = __uint_as_float(r[b * 16 + 8 + j]);
-                            if (b * 8 + j < valid) dst[b * 8 + j] = from_f32<TOut>(gate / (1.0f + expf(-gate)) * up);
+                            g[b * 8 + j] = gate / (1.0f + __expf(-gate)) * up;
                         }
+                    if (valid == 16 && sizeof(TOut) == 2 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(g[j], g[j + 1]), p1 = __floats2bfloat162_rn(g[j + 2], g[j + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(g[j + 4], g[j + 5]), p3 = __floats2bfloat162_rn(g[j + 6], g[j + 7]);
+                            v.x = *reinterpret_cast<unsigned*>(&p0); v.y = *reinterpret_cast<unsigned*>(&p1);
+                            v.z = *reinterpret_cast<unsigned*>(&p2); v.w = *reinterpret_cast<unsigned*>(&p3);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < valid) dst[j] = from_f32<TOut>(g[j]);
+                    }
                 } else {
                     store_row_chunk(out + (size_t)m * ldo + n0 + c0, r, min(32, N - n0 - c0));
                 }
