@@ -3,7 +3,7 @@
 //
 // The weight matrix is the A operand of mma.sync.m16n8k16 (16 weight rows per warp), the tokens are
 // the B operand (8 tokens per instruction), so a product with few tokens wastes no tensor-core rows.
-// A CTA owns 16 weight rows; its 8 warps split K and add their partial sums through shared memory.
+// A group is 16 weight rows; the 8 warps of a CTA split K and add their partial sums through shared memory.
 // Every lane reads 16 contiguous bytes of a weight row and of a token row straight into registers:
 // within a block of 32 k the four 16-byte pieces of a row are handed to the MMA in a permuted
 // order, the same for both operands, which leaves the dot product unchanged and makes all loads
@@ -14,8 +14,17 @@
 
 namespace {
 
+#ifdef RB_SK_WARPS                 // tuning builds may fix the shape
+constexpr int SK_WARPS = RB_SK_WARPS;
+#else
 constexpr int SK_WARPS = 8;
-constexpr int SK_ROWS = 16;       // weight rows per CTA
+#endif
+constexpr int SK_ROWS = 16;       // weight rows per group
+#ifdef RB_SK_CTAS
+constexpr int SK_CTAS_PER_SM = RB_SK_CTAS;
+#else
+constexpr int SK_CTAS_PER_SM = 2;
+#endif
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {       // read once: do not keep in L1
     uint4 v;
@@ -40,21 +49,26 @@ struct Regs {                         // one buffer: U blocks of 32 k of the wei
     uint4 a0[U], a1[U], b[U][MT];
 };
 
-// GATED: the 16 weight rows of a CTA are 8 gate rows followed by their 8 up rows (the feed-forward's
+// GATED: the 16 weight rows of a group are 8 gate rows followed by their 8 up rows (the feed-forward's
 // interleaved layout); the epilogue writes silu(gate) * up, 8 values per token, into out[M, N / 2].
+//
+// Persistent: a CTA walks groups of 16 weight rows (group = blockIdx.x, + gridDim.x, ...).  Each
+// warp owns one slice of K, cut into buffers of U blocks of 32; the buffers of all its groups form
+// one sequence, and the loads of buffer i + 1 are in flight while buffer i is multiplied, also
+// across the boundary between two groups, so the weight stream never drains while a group's
+// partial sums are added up and stored.
 template <int MT, typename TOut, bool GATED>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ out,
                    int M, int N, int K, int ldx, int ldw, int ldo) {
+#ifdef RB_SK_U1
+    constexpr int U = MT == 1 ? RB_SK_U1 : 2;
+#else
     constexpr int U = MT == 1 ? 4 : 2;                    // k32 blocks per buffer; two buffers in flight
+#endif
     __shared__ float red[SK_WARPS][SK_ROWS][8 * MT + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
-    const int n0 = blockIdx.x * SK_ROWS;
-    const int r0 = n0 + g, r1 = r0 + 8;
-    const bool ok0 = r0 < N, ok1 = r1 < N;
-    const bf16* w0 = w + (size_t)(ok0 ? r0 : 0) * ldw + 8 * t4;
-    const bf16* w1 = w + (size_t)(ok1 ? r1 : 0) * ldw + 8 * t4;
     const bf16* xr[MT];
     bool xok[MT];
 #pragma unroll
@@ -66,12 +80,23 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
     const int nkb = (K + 31) >> 5;
     const int per = (nkb + SK_WARPS - 1) / SK_WARPS;
     const int kb_begin = warp * per, kb_end = min(nkb, kb_begin + per);
+    const int nbuf = max(1, (per + U - 1) / U);          // buffers per group (the same for every warp)
+    const int n_groups = (N + SK_ROWS - 1) / SK_ROWS;
+    const int my_groups = (int)blockIdx.x < n_groups ? (n_groups - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int total = my_groups * nbuf;                  // buffers this warp walks
     float acc[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) { acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f; }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
-    auto load_w = [&](Regs<MT, U>& r, int kb) {          // blocks past the warp's slice load zeros
+    // buffer i of this warp: group (i / nbuf) of this CTA, blocks kb_begin + (i % nbuf) * U ...
+    auto load_w = [&](Regs<MT, U>& r, int i) {           // blocks past the slice, or past the last group, load zeros
+        const int gi = i / nbuf, kb = kb_begin + (i - gi * nbuf) * U;
+        const int n0 = ((int)blockIdx.x + gi * (int)gridDim.x) * SK_ROWS;
+        const int r0 = n0 + g, r1 = r0 + 8;
+        const bool ok0 = i < total && r0 < N, ok1 = i < total && r1 < N;
+        const bf16* w0 = w + (size_t)(ok0 ? r0 : 0) * ldw + 8 * t4;
+        const bf16* w1 = w + (size_t)(ok1 ? r1 : 0) * ldw + 8 * t4;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (kb + u) << 5;
@@ -80,11 +105,12 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
             r.a1[u] = (kin && ok1) ? ld_stream16(w1 + k) : zero;
         }
     };
-    auto load_x = [&](Regs<MT, U>& r, int kb) {
+    auto load_x = [&](Regs<MT, U>& r, int i) {
+        const int kb = kb_begin + (i % nbuf) * U;
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = (kb + u) << 5;
-            const bool kin = kb + u < kb_end && k + 8 * t4 < K;
+            const bool kin = i < total && kb + u < kb_end && k + 8 * t4 < K;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt)
                 r.b[u][mt] = (kin && xok[mt]) ? __ldg(reinterpret_cast<const uint4*>(xr[mt] + k)) : zero;
@@ -100,46 +126,58 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
             }
         }
     };
-    auto load = [&](Regs<MT, U>& r, int kb) { load_w(r, kb); load_x(r, kb); };
-    Regs<MT, U> ra, rb;
-    pdl_launch_dependents();
-    load_w(ra, kb_begin);                                // weights are nobody's output: stream them at once
-    pdl_wait();                                          // the tokens come from the kernel before
-    load_x(ra, kb_begin);
-    for (int kb = kb_begin; kb < kb_end; kb += 2 * U) {  // the next buffer is in flight while one is used
-        load(rb, kb + U);
-        compute(ra);
-        load(ra, kb + 2 * U);
-        compute(rb);
-    }
-    pdl_trigger_late();
+    // after the last buffer of a group: the warps' partial sums meet in shared memory and are stored
+    auto finish_group = [&](int i) {
+        const int n0 = ((int)blockIdx.x + (i / nbuf) * (int)gridDim.x) * SK_ROWS;
+        if (i + 1 >= total) pdl_trigger_late();
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-        red[warp][g][mt * 8 + 2 * t4] = acc[mt][0];
-        red[warp][g][mt * 8 + 2 * t4 + 1] = acc[mt][1];
-        red[warp][g + 8][mt * 8 + 2 * t4] = acc[mt][2];
-        red[warp][g + 8][mt * 8 + 2 * t4 + 1] = acc[mt][3];
-    }
-    __syncthreads();
-    if constexpr (GATED) {
-        for (int idx = tid; idx < 8 * 8 * MT; idx += SK_WARPS * 32) {
-            const int j = idx & 7, m = idx >> 3;
-            if (m < M && n0 + 8 + j < N) {
-                float gate = 0.f, up = 0.f;
+        for (int mt = 0; mt < MT; ++mt) {
+            red[warp][g][mt * 8 + 2 * t4] = acc[mt][0];
+            red[warp][g][mt * 8 + 2 * t4 + 1] = acc[mt][1];
+            red[warp][g + 8][mt * 8 + 2 * t4] = acc[mt][2];
+            red[warp][g + 8][mt * 8 + 2 * t4 + 1] = acc[mt][3];
+            acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.f;
+        }
+        __syncthreads();
+        if constexpr (GATED) {
+            for (int idx = tid; idx < 8 * 8 * MT; idx += SK_WARPS * 32) {
+                const int j = idx & 7, m = idx >> 3;
+                if (m < M && n0 + 8 + j < N) {
+                    float gate = 0.f, up = 0.f;
 #pragma unroll
-                for (int wi = 0; wi < SK_WARPS; ++wi) { gate += red[wi][j][m]; up += red[wi][8 + j][m]; }
-                store_out<TOut>(out + (size_t)m * ldo + (n0 >> 1) + j, gate / (1.0f + expf(-gate)) * up);
+                    for (int wi = 0; wi < SK_WARPS; ++wi) { gate += red[wi][j][m]; up += red[wi][8 + j][m]; }
+                    store_out<TOut>(out + (size_t)m * ldo + (n0 >> 1) + j, gate / (1.0f + expf(-gate)) * up);
+                }
+            }
+        } else {
+            for (int idx = tid; idx < SK_ROWS * 8 * MT; idx += SK_WARPS * 32) {
+                const int n = idx & (SK_ROWS - 1), m = idx >> 4;
+                if (m < M && n0 + n < N) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int wi = 0; wi < SK_WARPS; ++wi) s += red[wi][n][m];
+                    store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
+                }
             }
         }
-    } else {
-        for (int idx = tid; idx < SK_ROWS * 8 * MT; idx += SK_WARPS * 32) {
-            const int n = idx & (SK_ROWS - 1), m = idx >> 4;
-            if (m < M && n0 + n < N) {
-                float s = 0.f;
-#pragma unroll
-                for (int wi = 0; wi < SK_WARPS; ++wi) s += red[wi][n][m];
-                store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
-            }
+        __syncthreads();                                 // red is free for the next group
+    };
+
+    Regs<MT, U> ra, rb;
+    pdl_launch_dependents();
+    load_w(ra, 0);                                       // weights are nobody's output: stream them at once
+    pdl_wait();                                          // the tokens come from the kernel before
+    load_x(ra, 0);
+    for (int i = 0; i < total; i += 2) {                 // buffer i + 1 is in flight while buffer i is used
+        load_w(rb, i + 1);
+        load_x(rb, i + 1);
+        compute(ra);
+        if ((i + 1) % nbuf == 0) finish_group(i);
+        load_w(ra, i + 2);
+        load_x(ra, i + 2);
+        if (i + 1 < total) {
+            compute(rb);
+            if ((i + 2) % nbuf == 0) finish_group(i + 1);
         }
     }
 }
@@ -147,7 +185,15 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
 template <int MT>
 int launch(const bf16* x, const bf16* w, void* out, int out_f32, int gated, int M, int N, int K, int ldx, int ldw,
            int ldo, cudaStream_t st) {
-    const int grid = (N + SK_ROWS - 1) / SK_ROWS;
+    static int resident = 0;                              // CTAs that fit the GPU at once
+    if (resident == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        resident = sms * SK_CTAS_PER_SM;
+    }
+    const int groups = (N + SK_ROWS - 1) / SK_ROWS;
+    const int grid = groups < resident ? groups : resident;
     if (gated)
         return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, true>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
     if (out_f32)

@@ -365,16 +365,17 @@ def attention_prefill_tc5(qkv, k_pool, v_pool, tiles128, cu_q, seg_pos0, block_t
 NUM_SMS = 148
 
 
-def decode_splits(n_ctas_base: int, max_kv_len: int) -> int:
-    """How many ways the keys of a decoded token are split.  One CTA runs per SM, so the time of
-    the launch goes with (waves of CTAs) x (keys per CTA); the split count that makes this
-    smallest wins, with at least 128 keys per CTA and the smaller count on a tie."""
+def decode_splits(n_ctas_base: int, max_kv_len: int, ctas_per_sm: int = 2) -> int:
+    """How many ways the keys of a decoded token are split.  Two CTAs share an SM (head sizes up to
+    128), so the time of the launch goes with (waves of CTAs) x (keys per CTA); the split count that
+    makes this smallest wins, with at least 128 keys per CTA and the smaller count on a tie."""
     tiles = max(1, (max_kv_len + 15) // 16)
+    slots = NUM_SMS * ctas_per_sm
     best, best_cost = 1, None
     for s in range(1, 65):
         if s > 1 and (max_kv_len + s - 1) // s < 128:
             break
-        waves = (n_ctas_base * s + NUM_SMS - 1) // NUM_SMS
+        waves = (n_ctas_base * s + slots - 1) // slots
         cost = waves * ((tiles + s - 1) // s + 4)          # + a few tiles' worth of fixed work per CTA
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
