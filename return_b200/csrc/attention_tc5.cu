@@ -9,14 +9,17 @@
 //                 (tcgen05.ld / st) only when a row's maximum moved;
 //   O += P V      tcgen05.mma, M = 128, N = head dim, V as it lies in the cache (rows = keys): an
 //                 MN-major B operand.
-// One thread issues the MMAs; completion comes back through mbarriers (tcgen05.commit).  K and V
-// tiles are gathered page by page with cp.async into the 128-byte-swizzled layout the MMA reads
-// (keys outside the visible range, or on a page that was given back, are zero-filled, never read).
-// 100 KB of shared memory and 256 TMEM columns a CTA: two CTAs share an SM, so one's softmax
-// overlaps the other's MMAs.  Same contract as the reference's prefill kernel
-// (rollout/attention.py:45-142) and as attention_mma.cu; keys arrive rotated, tiles are aligned to
-// absolute positions, a sliding window bounds the keys from below.
-// Every wait is bounded (tc5.cuh); *status is raised if one gave up.
+// Seven warps with fixed roles, tied together by mbarriers (every wait bounded, tc5.cuh):
+//   warps 0-3  the softmax rows;
+//   warp 4     one thread issues every MMA; S is double-buffered in TMEM, so S(t+1) is computed
+//              while the rows work on S(t);
+//   warp 5     gathers K tiles, warp 6 V tiles, page by page with cp.async into the
+//              128-byte-swizzled layout the MMA reads (two buffers each; keys outside the visible
+//              range, or on a page that was given back, are zero-filled, never read).
+// 112 KB of shared memory and 256 TMEM columns a CTA: two CTAs share an SM.  Same contract as the
+// reference's prefill kernel (rollout/attention.py:45-142) and as attention_mma.cu; keys arrive
+// rotated, tiles are aligned to absolute positions, a sliding window bounds the keys from below.
+// *status is raised if a wait gave up.
 #include "tc5.cuh"
 
 #ifndef HEAD_DIM
@@ -32,12 +35,11 @@ constexpr int D = HEAD_DIM;
 constexpr int DS = D / 64;                    // 64-wide slabs of the head dim
 constexpr int QM = 128;                       // query rows per CTA
 constexpr int KN = 64;                        // keys per tile
-constexpr int BT_CAP = 1024;                  // block-table entries staged in shared memory
-constexpr int THREADS = 160;                  // warps 0..3: one query row per thread; warp 4: MMA issuer
+constexpr int THREADS = 224;                  // warps 0..3: one query row per thread; 4: MMA; 5: K loader; 6: V loader
 constexpr unsigned Q_BYTES = DS * QM * 128, K_BYTES = DS * KN * 128, P_BYTES = QM * 128;
-constexpr unsigned SMEM_BYTES = Q_BYTES + K_BYTES + 2 * K_BYTES + P_BYTES + BT_CAP * 4 + 1024;
-constexpr unsigned TMEM_COLS = 256;           // S: 64 columns, O: HEAD_DIM columns
-constexpr unsigned S_COL = 0, O_COL = 64;
+constexpr unsigned SMEM_BYTES = Q_BYTES + 2 * K_BYTES + 2 * K_BYTES + P_BYTES + 256;   // two CTAs must fit 228 KB
+constexpr unsigned TMEM_COLS = 256;           // S: 2 x 64 columns, O: HEAD_DIM columns
+constexpr unsigned S_COL = 0, O_COL = 128;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -64,22 +66,27 @@ struct Paging {
     __device__ __forceinline__ int row(int j) const { return shift >= 0 ? j & (page_size - 1) : j % page_size; }
 };
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
                         const bf16* __restrict__ vpool, const int* __restrict__ tiles,
                         const int* __restrict__ cu_q, const int* __restrict__ seg_pos0,
                         const int* __restrict__ block_table, int bt_stride, int page_size,
                         bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
                         int* __restrict__ status) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* sQ = base;
-    unsigned char* sK = sQ + Q_BYTES;
-    unsigned char* sV = sK + K_BYTES;                     // two buffers
+    // The swizzled tiles need 1024-byte alignment.  The kernel has no static shared memory, so the
+    // dynamic window starts at the CTA's shared base; should it ever not be aligned, the kernel
+    // reports it and does nothing.
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    if ((smem_u32(smem_raw) & 1023u) != 0u) {
+        if (threadIdx.x == 0) atomicExch(status, 2);
+        return;
+    }
+    unsigned char* sQ = smem_raw;
+    unsigned char* sK = sQ + Q_BYTES;                     // two buffers
+    unsigned char* sV = sK + 2 * K_BYTES;                 // two buffers
     unsigned char* sP = sV + 2 * K_BYTES;
-    int* sBT = reinterpret_cast<int*>(sP + P_BYTES);
-    __shared__ __align__(8) unsigned long long bar_s_full, bar_p_ready, bar_pv_done;
-    __shared__ unsigned tmem_slot;
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + P_BYTES);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 16);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y, kvh = h / (Hq / Hkv);
@@ -92,21 +99,28 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     const int jt_begin = lo_min / KN, n_tiles = p_last / KN - jt_begin + 1;
     const int* bt_row = block_table + (size_t)seg * bt_stride;
     const Paging pg(page_size);
-    const unsigned s_full = smem_u32(&bar_s_full), p_ready = smem_u32(&bar_p_ready), pv_done = smem_u32(&bar_pv_done);
+    // barriers: [0,1] S buffer full, [2,3] K buffer loaded, [4,5] V buffer loaded, 6 P ready, 7 PV done, 8 Q ready,
+    // [9,10] V buffer free.  Each barrier's next phase needs its waiter to have passed the current one, so a
+    // parity wait can never fall two phases behind (the V loader has its own barrier for that reason: PV_DONE
+    // moves on without it).
+    const unsigned bar0 = smem_u32(bars);
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+    constexpr int S_FULL = 0, K_READY = 2, V_READY = 4, P_READY = 6, PV_DONE = 7, Q_READY = 8, V_FREE = 9;
 
-    if (warp == 4) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+    if (warp == 4) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     if (tid == 0) {
-        mbar_init(s_full, 1);
-        mbar_init(p_ready, 128);
-        mbar_init(pv_done, 1);
+        for (int i = 0; i < 6; ++i) mbar_init(bar(i), 1);
+        mbar_init(bar(P_READY), 128);
+        mbar_init(bar(PV_DONE), 1);
+        mbar_init(bar(Q_READY), 128);
+        mbar_init(bar(V_FREE), 1);
+        mbar_init(bar(V_FREE + 1), 1);
         mbar_init_fence();
     }
-    const int bt_first = pg.block(lo_min), bt_count = min(BT_CAP, pg.block(p_last) - bt_first + 1);
-    for (int i = tid; i < bt_count; i += THREADS) sBT[i] = bt_row[bt_first + i];
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
-    const unsigned tmem = tmem_slot;
+    const unsigned tmem = *tmem_slot;
     bool ok = true;
 
     if (warp < 4) {
@@ -114,26 +128,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         const int r = tid;
         const int pos_r = p0 + r;
         const bool row_valid = r < m_rows;
-        // K/V gather: two threads a key row, each half of the row's 16-byte chunks
-        constexpr int CPT = D / 16;                       // chunks per thread
-        const int krow = tid >> 1, c_first = (tid & 1) * CPT;
-        auto issue_kv = [&](unsigned tile_smem, const bf16* pool, int jt) {
-            const int j = jt * KN + krow;
-            bool pred = j >= lo_min && j <= p_last;
-            const bf16* src = pool;
-            if (pred) {
-                const int blk = pg.block(j), i = blk - bt_first;
-                const int page = i < bt_count ? sBT[i] : bt_row[blk];
-                pred = page >= 0;
-                if (pred) src = pool + (((size_t)page * Hkv + kvh) * pg.page_size + pg.row(j)) * D;
-            }
-#pragma unroll
-            for (int c = 0; c < CPT; ++c) {
-                const int cc = c_first + c;
-                cp_async16(tile_smem + (cc >> 3) * (KN * 128) + sw128_offset(krow, cc & 7), pred ? src + cc * 8 : pool, pred);
-            }
-        };
-        // ---- prologue: this row of Q, the first K and V tiles
         {
             const bf16* qrow = q + (size_t)(q_begin + row0 + r) * ld + (size_t)h * D;
 #pragma unroll
@@ -143,109 +137,106 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 *reinterpret_cast<uint4*>(sQ + (c >> 3) * (QM * 128) + sw128_offset(r, c & 7)) = v;
             }
         }
-        issue_kv(smem_u32(sK), kpool, jt_begin);
-        cp_async_commit();
-        issue_kv(smem_u32(sV), vpool, jt_begin);
-        cp_async_commit();
-        cp_async_wait<0>();
         fence_proxy_async();
-        mbar_arrive(p_ready);                             // phase 0: the operands of the first tile are in place
+        mbar_arrive(bar(Q_READY));
 
         float m_run = -INFINITY, l_run = 0.f;
+        const unsigned lane_addr = tmem + ((unsigned)(warp * 32) << 16);
         for (int t = 0; t < n_tiles; ++t) {
-            const int jt = jt_begin + t;
-            ok = mbar_wait(s_full, t & 1) && ok;          // S(t) is complete, so the K buffer is free
+            const int j_base = (jt_begin + t) * KN;
+            const unsigned s_addr = lane_addr + S_COL + (t & 1) * KN;
+            ok = mbar_wait(bar(S_FULL + (t & 1)), (t >> 1) & 1) && ok;
             fence_after_sync();
-            if (t + 1 < n_tiles) issue_kv(smem_u32(sK), kpool, jt + 1);
-            cp_async_commit();
-
-            unsigned sr[64];
-            {
-                unsigned a[32], b[32];
-                tmem_ld32(tmem + ((unsigned)(warp * 32) << 16) + S_COL, a);
-                tmem_ld32(tmem + ((unsigned)(warp * 32) << 16) + S_COL + 32, b);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) { sr[i] = a[i]; sr[32 + i] = b[i]; }
-            }
-            const int j_base = jt * KN;
-            float mx = -INFINITY;
             const bool all_visible = j_base + KN - 1 <= p0 && (window <= 0 || j_base > p_last - window) && m_rows == QM;
-            if (all_visible) {
+            // pass 1: the row's maximum over the tile (two halves of 32 keys)
+            float mx = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const float v = __uint_as_float(sr[i]) * scale_log2;
-                    sr[i] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
-            } else {
+            for (int half = 0; half < 2; ++half) {
+                unsigned a[32];
+                tmem_ld32(s_addr + half * 32, a);
+                tmem_ld_wait();
+                if (all_visible) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const int j = j_base + i;
-                    const bool vis = row_valid && j <= pos_r && (window <= 0 || j > pos_r - window);
-                    const float v = vis ? __uint_as_float(sr[i]) * scale_log2 : -INFINITY;
-                    sr[i] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(a[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int j = j_base + half * 32 + i;
+                        const bool vis = row_valid && j <= pos_r && (window <= 0 || j > pos_r - window);
+                        if (vis) mx = fmaxf(mx, __uint_as_float(a[i]));
+                    }
                 }
             }
+            mx *= scale_log2;                              // the scale is positive: max(scale * s) = scale * max(s)
             const float m_new = fmaxf(m_run, mx);
             const float mu = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = fast_exp2(m_run - mu);
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float p = fast_exp2(__uint_as_float(sr[i]) - mu);
-                sr[i] = __float_as_uint(p);
-                sum += p;
-            }
-            l_run = l_run * alpha + sum;
             const bool moved = m_new != m_run;
             m_run = m_new;
 
-            if (t > 0) ok = mbar_wait(pv_done, (t - 1) & 1) && ok;    // O, P and the other V buffer are free
+            if (t > 0) ok = mbar_wait(bar(PV_DONE), (t - 1) & 1) && ok;     // O and the P buffer are free
             fence_after_sync();
-            if (t + 1 < n_tiles) issue_kv(smem_u32(sV) + ((t + 1) & 1) * K_BYTES, vpool, jt + 1);
-            cp_async_commit();
-
-            if (t > 0 && __any_sync(0xffffffffu, moved)) {            // rescale this row of O in tensor memory
+            if (t > 0 && __any_sync(0xffffffffu, moved)) {                  // rescale this row of O in tensor memory
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     unsigned o[32];
-                    const unsigned addr = tmem + ((unsigned)(warp * 32) << 16) + O_COL + c0;
-                    tmem_ld32(addr, o);
+                    tmem_ld32(lane_addr + O_COL + c0, o);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st32(addr, o);
+                    tmem_st32(lane_addr + O_COL + c0, o);
                 }
                 tmem_st_wait();
             }
-            // P, rounded to bfloat16, as the A operand of the next MMA: this thread's row, 8 chunks of 8 keys
+            // pass 2: p = 2^(scale * s - m), summed in float32, rounded to bfloat16 into the A operand of P V
+            float sum = 0.f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint4 v;
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(sr[8 * c]), __uint_as_float(sr[8 * c + 1]));
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(sr[8 * c + 2]), __uint_as_float(sr[8 * c + 3]));
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(sr[8 * c + 4]), __uint_as_float(sr[8 * c + 5]));
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(sr[8 * c + 6]), __uint_as_float(sr[8 * c + 7]));
-                v.x = *reinterpret_cast<unsigned*>(&p0); v.y = *reinterpret_cast<unsigned*>(&p1);
-                v.z = *reinterpret_cast<unsigned*>(&p2); v.w = *reinterpret_cast<unsigned*>(&p3);
-                *reinterpret_cast<uint4*>(sP + sw128_offset(r, c)) = v;
+            for (int half = 0; half < 2; ++half) {
+                unsigned a[32];
+                tmem_ld32(s_addr + half * 32, a);
+                tmem_ld_wait();
+                if (all_visible) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float p = fast_exp2(fmaf(__uint_as_float(a[i]), scale_log2, -mu));
+                        sum += p;
+                        a[i] = __float_as_uint(p);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int j = j_base + half * 32 + i;
+                        const bool vis = row_valid && j <= pos_r && (window <= 0 || j > pos_r - window);
+                        const float p = vis ? fast_exp2(fmaf(__uint_as_float(a[i]), scale_log2, -mu)) : 0.f;
+                        sum += p;
+                        a[i] = __float_as_uint(p);
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint4 v;
+                    __nv_bfloat162 q0 = __floats2bfloat162_rn(__uint_as_float(a[8 * c]), __uint_as_float(a[8 * c + 1]));
+                    __nv_bfloat162 q1 = __floats2bfloat162_rn(__uint_as_float(a[8 * c + 2]), __uint_as_float(a[8 * c + 3]));
+                    __nv_bfloat162 q2 = __floats2bfloat162_rn(__uint_as_float(a[8 * c + 4]), __uint_as_float(a[8 * c + 5]));
+                    __nv_bfloat162 q3 = __floats2bfloat162_rn(__uint_as_float(a[8 * c + 6]), __uint_as_float(a[8 * c + 7]));
+                    v.x = *reinterpret_cast<unsigned*>(&q0); v.y = *reinterpret_cast<unsigned*>(&q1);
+                    v.z = *reinterpret_cast<unsigned*>(&q2); v.w = *reinterpret_cast<unsigned*>(&q3);
+                    *reinterpret_cast<uint4*>(sP + sw128_offset(r, half * 4 + c)) = v;
+                }
             }
-            cp_async_wait<1>();                            // K(t+1) and V(t) have landed; V(t+1) may still fly
+            l_run = l_run * alpha + sum;
             fence_proxy_async();
             fence_before_sync();
-            mbar_arrive(p_ready);                          // phase t+1
+            mbar_arrive(bar(P_READY));                     // S(t) is read, O is rescaled, P(t) is written
         }
-        ok = mbar_wait(pv_done, (n_tiles - 1) & 1) && ok;
+        ok = mbar_wait(bar(PV_DONE), (n_tiles - 1) & 1) && ok;
         fence_after_sync();
-        cp_async_wait<0>();
         const float inv = 1.f / l_run;
         bf16* orow = out + (size_t)(q_begin + row0 + r) * ((size_t)Hq * D) + (size_t)h * D;
 #pragma unroll 1
         for (int c0 = 0; c0 < D; c0 += 32) {
             unsigned o[32];
-            tmem_ld32(tmem + ((unsigned)(warp * 32) << 16) + O_COL + c0, o);
+            tmem_ld32(lane_addr + O_COL + c0, o);
             tmem_ld_wait();
             if (row_valid) {
 #pragma unroll
@@ -261,31 +252,73 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 }
             }
         }
-    } else if (lane == 0) {
-        // ================================================================== the MMA issuer
-        const unsigned idesc_s = instr_desc_bf16(QM, KN, false);
-        const unsigned idesc_o = instr_desc_bf16(QM, D, true);
-        const unsigned aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
-        auto issue_s = [&]() {
+    } else if (warp == 4) {
+        if (lane == 0) {
+            // ============================================================== the MMA issuer
+            const unsigned idesc_s = instr_desc_bf16(QM, KN, false);
+            const unsigned idesc_o = instr_desc_bf16(QM, D, true);
+            const unsigned aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP);
+            auto issue_s = [&](int t) {                    // S(t) = Q K(t)^T into S buffer t & 1
+                ok = mbar_wait(bar(K_READY + (t & 1)), (t >> 1) & 1) && ok;
+                fence_after_sync();
+                const unsigned k_tile = aK + (t & 1) * K_BYTES;
 #pragma unroll
-            for (int d16 = 0; d16 < D / 16; ++d16)
-                mma_ss(tmem + S_COL, smem_desc_sw128(aQ + (d16 >> 2) * (QM * 128), (d16 & 3) * 32),
-                       smem_desc_sw128(aK + (d16 >> 2) * (KN * 128), (d16 & 3) * 32), idesc_s, d16 > 0);
-            mma_commit(s_full);
-        };
-        ok = mbar_wait(p_ready, 0) && ok;                  // Q, K(0), V(0) are in shared memory
-        fence_after_sync();
-        issue_s();
-        for (int t = 0; t < n_tiles; ++t) {
-            ok = mbar_wait(p_ready, (t + 1) & 1) && ok;    // P(t) written, O rescaled, V(t) and K(t+1) landed
+                for (int d16 = 0; d16 < D / 16; ++d16)
+                    mma_ss(tmem + S_COL + (t & 1) * KN, smem_desc_sw128(aQ + (d16 >> 2) * (QM * 128), (d16 & 3) * 32),
+                           smem_desc_sw128(k_tile + (d16 >> 2) * (KN * 128), (d16 & 3) * 32), idesc_s, d16 > 0);
+                mma_commit(bar(S_FULL + (t & 1)));
+            };
+            ok = mbar_wait(bar(Q_READY), 0) && ok;
             fence_after_sync();
-            const unsigned v_tile = aV + (t & 1) * K_BYTES;
+            issue_s(0);
+            if (n_tiles > 1) issue_s(1);
+            for (int t = 0; t < n_tiles; ++t) {
+                ok = mbar_wait(bar(P_READY), t & 1) && ok;
+                ok = mbar_wait(bar(V_READY + (t & 1)), (t >> 1) & 1) && ok;
+                fence_after_sync();
+                const unsigned v_tile = aV + (t & 1) * K_BYTES;
 #pragma unroll
-            for (int k16 = 0; k16 < KN / 16; ++k16)
-                mma_ss(tmem + O_COL, smem_desc_sw128(aP, k16 * 32),
-                       smem_desc_sw128_mn(v_tile + k16 * 2048, KN * 128, 1024u), idesc_o, t > 0 || k16 > 0);
-            mma_commit(pv_done);
-            if (t + 1 < n_tiles) issue_s();
+                for (int k16 = 0; k16 < KN / 16; ++k16)
+                    mma_ss(tmem + O_COL, smem_desc_sw128(aP, k16 * 32),
+                           smem_desc_sw128_mn(v_tile + k16 * 2048, KN * 128, 1024u), idesc_o, t > 0 || k16 > 0);
+                mma_commit(bar(PV_DONE));
+                mma_commit(bar(V_FREE + (t & 1)));
+                if (t + 2 < n_tiles) issue_s(t + 2);       // its S buffer was read by the rows before P_READY(t)
+            }
+        }
+    } else {
+        // ================================================================== the loaders: warp 5 K, warp 6 V
+        const bool is_k = warp == 5;
+        const bf16* pool = is_k ? kpool : vpool;
+        unsigned char* bufs = is_k ? sK : sV;
+        for (int t = 0; t < n_tiles; ++t) {
+            if (t >= 2) {
+                // buffer t & 1 is free once S(t-2) (for K) or the P V product of tile t-2 (for V) is complete
+                if (is_k) ok = mbar_wait(bar(S_FULL + (t & 1)), ((t - 2) >> 1) & 1) && ok;
+                else ok = mbar_wait(bar(V_FREE + (t & 1)), ((t - 2) >> 1) & 1) && ok;
+            }
+            const unsigned tile_smem = smem_u32(bufs) + (t & 1) * K_BYTES;
+            const int jt = jt_begin + t;
+#pragma unroll 1
+            for (int rr = 0; rr < KN; rr += 32) {          // a lane gathers the whole row of two keys
+                const int krow = rr + lane;
+                const int j = jt * KN + krow;
+                bool pred = j >= lo_min && j <= p_last;
+                const bf16* src = pool;
+                if (pred) {
+                    const int page = bt_row[pg.block(j)];
+                    pred = page >= 0;
+                    if (pred) src = pool + (((size_t)page * Hkv + kvh) * pg.page_size + pg.row(j)) * D;
+                }
+#pragma unroll
+                for (int cc = 0; cc < D / 8; ++cc)
+                    cp_async16(tile_smem + (cc >> 3) * (KN * 128) + sw128_offset(krow, cc & 7), pred ? src + cc * 8 : pool, pred);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar((is_k ? K_READY : V_READY) + (t & 1)));
         }
     }
     if (!ok) atomicExch(status, 1);

@@ -281,6 +281,39 @@ def test_attention_prefill_tc5(Hq, Hkv, D, P, window):
     assert torch.allclose(out.float().cpu(), pg.reference(scale, window), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_attention_prefill_tc5_long(D):
+    """Dozens of key tiles per query tile with every SM busy: the loaders, the issuing thread and the
+    softmax rows drift apart in time, which is where a barrier that is waited on out of step shows.
+    One far key is made to stand out for one late query, so a lost or misplaced tile shows too."""
+    ops = _ops()
+    Hq, Hkv, P, L = 4, 1, 16, 5000
+    pg = Paged([L, 700], [L, 300], Hq, Hkv, D, P, torch.bfloat16, seed=11)
+    far, late = 37, L - 3
+    page, off = int(pg.bt[0, far // P]), far % P
+    pg.k[0][far] *= 6.0
+    pg.kpool[page, :, off] = pg.k[0][far].to(torch.bfloat16).to(DEV)
+    pg.q[0][late] = pg.k[0][far, 0].repeat(Hq, 1) * 0.5
+    pg.qkv[late, :Hq * D] = pg.q[0][late].reshape(-1).to(torch.bfloat16).to(DEV)
+    tiles = [(i, r0) for i, ql in enumerate(pg.q_lens) for r0 in range(0, ql, 128)]
+    tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    out = torch.full((sum(pg.q_lens), Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    for _ in range(3):
+        ops.attention_prefill_tc5(pg.qkv, pg.kpool, pg.vpool, tiles, pg.cu_q, pg.seg_pos0, pg.bt, P, out, Hq, Hkv, D,
+                                  scale, 0)
+    torch.cuda.synchronize()
+    st = ops.tc5_status(torch.device(DEV))
+    flag = int(st.item())
+    st.zero_()
+    assert flag == 0, "a bounded wait inside the kernel gave up"
+    ref = pg.reference(scale, None)
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+    # the late query's output is the far key's value, almost alone
+    assert torch.allclose(out[late].float().cpu().reshape(Hq, D), pg.v[0][far, 0].to(torch.bfloat16).float().expand(Hq, D),
+                          atol=5e-2, rtol=5e-2)
+
+
 @pytest.mark.parametrize("Hq,Hkv,D,P", ATT_SHAPES)
 @pytest.mark.parametrize("window", [None, 37])
 @pytest.mark.parametrize("splits", [1, 3, 8])
