@@ -190,7 +190,8 @@ def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8
 
 def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> Dict[str, float]:
     """A bfloat16 matrix product alone: device time, weight bandwidth and TFLOP/s.
-    ``impl`` 0: ``ops.linear`` (the engine's choice); 1: the tcgen05 kernel; 2: cuBLAS (``torch.mm``)."""
+    ``impl`` 0: ``ops.linear`` (the engine's choice); 1: the tcgen05 kernel; 2: cuBLAS (``torch.mm``);
+    3: the tcgen05 weight-streaming kernel; 4: the mma.sync weight-streaming kernel."""
     from .ext import ops
     dev = torch.device("cuda:0")
     fns = []
@@ -202,10 +203,14 @@ def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> D
             fns.append(lambda a=(x, w, out): ops.gemm_tc5(*a))
         elif impl == 2:
             fns.append(lambda a=(x, w, out): torch.mm(a[0], a[1].t(), out=a[2]))
+        elif impl == 3:
+            fns.append(lambda a=(x, w, out): ops.gemm_stream(*a))
+        elif impl == 4:
+            fns.append(lambda a=(x, w, out): ops.gemm_skinny(*a))
         else:
             fns.append(lambda a=(x, w, out): ops.linear(*a))
     ms = _time_kernels(fns, iters, warmup)
-    return {"kernel": ("linear", "gemm_tc5", "cublas")[impl], "M": M, "N": N, "K": K, "ms": ms, "GBps": N * K * 2 / ms / 1e6,
+    return {"kernel": ("linear", "gemm_tc5", "cublas", "gemm_stream", "gemm_skinny")[impl], "M": M, "N": N, "K": K, "ms": ms, "GBps": N * K * 2 / ms / 1e6,
             "TFLOPs": 2.0 * M * N * K / ms / 1e9}
 
 

@@ -16,6 +16,7 @@
 #include <cuda.h>
 
 #include "tc5.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -188,15 +189,6 @@ tc5_gemm_bmn_kernel(const bf16* __restrict__ x, const bf16* __restrict__ bmat, f
 }
 
 // ------------------------------------------------------------------------------------ the product kernel
-__device__ __forceinline__ void tma_load_2d(unsigned smem_dst, const CUtensorMap* map, int x, int y, unsigned bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
 constexpr int TC5_THREADS = 192;          // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
 
 // Persistent: a CTA walks output tiles tile = blockIdx.x, + gridDim.x, ...; tiles that share a block
@@ -220,8 +212,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 
     if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
     if (tid == 0) {
-        tma_prefetch_desc(&map_x);
-        tma_prefetch_desc(&map_w);
+        tma::prefetch_desc(&map_x);
+        tma::prefetch_desc(&map_w);
 #pragma unroll
         for (int s = 0; s < STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
 #pragma unroll
@@ -246,8 +238,8 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const unsigned full = smem_u32(&full_bar[s]);
                     mbar_arrive_expect_tx(full, STAGE_BYTES);
                     const unsigned dst = smem_u32(base + (size_t)s * STAGE_BYTES);
-                    tma_load_2d(dst, &map_x, kb * BK, m0, full);
-                    tma_load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full);
+                    tma::load_2d(dst, &map_x, kb * BK, m0, full);
+                    tma::load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full);
                 }
             }
         }
@@ -332,41 +324,11 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return nullptr;
-        fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// A row-major [rows, cols] bf16 matrix with row stride ld (elements): boxes of box_rows x 64 columns.
-bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return false;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int BN, int STAGES, typename TOut, bool GATED>
 int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo, int* status,
                cudaStream_t st) {
     CUtensorMap mx, mw;
-    if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
+    if (!tma::make_map_bf16(&mx, x, M, K, ldx, BM) || !tma::make_map_bf16(&mw, w, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)STAGES * (BM + BN) * BK * 2 + 1024;
     static bool configured = false;
     if (!configured) {

@@ -1,0 +1,70 @@
+// Tensor-memory-accelerator helpers: tiled bulk loads into 128-byte-swizzled shared-memory tiles,
+// and the host side that encodes a tensor map for a row-major bfloat16 matrix.  The driver's
+// encoder is looked up through the runtime (cudaGetDriverEntryPoint), so nothing links libcuda.
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef RB_TMA_PROMO
+#define RB_TMA_PROMO 2      // CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+#endif
+
+namespace tma {
+
+// One box of the tensor behind `map`, whose innermost coordinate is x (elements; x * 2 bytes must be
+// a multiple of 16) and second coordinate y, lands at smem_dst; its bytes are counted on `bar`.
+__device__ __forceinline__ void load_2d(unsigned smem_dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+// The same with an L2 cache policy (createpolicy): evict-first for data that is read once.
+__device__ __forceinline__ void load_2d_hint(unsigned smem_dst, const CUtensorMap* map, int x, int y, unsigned bar,
+                                             unsigned long long policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar), "l"(policy) : "memory");
+}
+__device__ __forceinline__ unsigned long long policy_evict_first() {
+    unsigned long long p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static inline EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// A row-major [rows, cols] bf16 matrix with row stride ld (elements, a multiple of 8; base 16-byte
+// aligned): boxes of box_rows x 64 columns, 128-byte swizzle; what lies outside reads as zero.
+static inline bool make_map_bf16(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, (CUtensorMapL2promotion)RB_TMA_PROMO,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace tma

@@ -94,7 +94,7 @@ PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
-    paths.append(build.library_path("return_tc5", ["gemm_tc5.cu"], {"RB_PDL_MODE": PDL_MODE}))
+    paths.append(build.library_path("return_tc5", _TC5_SOURCES, _tc5_defines()))
     for d in TC5_ATTENTION_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], {"HEAD_DIM": d}))
     for d in PREBUILT_HEAD_DIMS:
@@ -197,14 +197,28 @@ def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, interleave
 
 
 _tc5 = None
+_TC5_SOURCES = ["gemm_tc5.cu", "gemm_stream.cu"]
+
+
+def _tc5_defines():
+    """Build options of the tcgen05 library; RETURN_B200_TC5_DEFS="NAME=1,OTHER=2" adds tuning macros."""
+    defs = {"RB_PDL_MODE": PDL_MODE}
+    for item in filter(None, _os.environ.get("RETURN_B200_TC5_DEFS", "").split(",")):
+        k, _, v = item.partition("=")
+        defs[k.strip()] = v.strip() or "1"
+    return defs
 
 
 def tc5_lib() -> ctypes.CDLL:
     """The tcgen05 / TMA matrix-product library."""
     global _tc5
     if _tc5 is None:
-        lib = build.load("return_tc5", ["gemm_tc5.cu"], {"RB_PDL_MODE": PDL_MODE})
+        lib = build.load("return_tc5", _TC5_SOURCES, _tc5_defines())
         P, I = c_void_p, c_int
+        lib.rb_gemm_stream.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, P]
+        lib.rb_gemm_stream.restype = c_int
+        lib.rb_gemm_stream_plan.argtypes = [I, I, I, I, P]
+        lib.rb_gemm_stream_plan.restype = None
         lib.rb_tc5_gemm.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, P]
         lib.rb_tc5_gemm_simple.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, P]
         lib.rb_tc5_gemm_bmn.argtypes = [P, P, P, I, I, I, I, I, I, I, P, P]
@@ -242,6 +256,37 @@ def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = 
         rc = tc5_lib().rb_tc5_gemm(_ptr(x), _ptr(w), _ptr(out), f32, 1 if gated else 0, M, N, K, x.stride(0),
                                    w.stride(0), out.stride(0), _ptr(status), _stream())
     _check(rc, "gemm_tc5")
+
+
+STREAM_MAX_ROWS = 128
+
+
+def stream_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tcgen05 weight-streaming kernel takes this product."""
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= STREAM_MAX_ROWS and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_stream(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 128 in bfloat16: weights streamed by TMA through tcgen05 with the
+    operand roles exchanged (weight rows on the 128 tensor-memory lanes, tokens as columns), the rows dealt out
+    evenly to one CTA per SM.  ``gated``: w holds gate and up rows woven in blocks of 8; out[M, N/2] = silu(gate) * up."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
+    assert w.shape[1] == K and out.shape == (M, N // 2 if gated else N) and M <= STREAM_MAX_ROWS
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(tc5_lib().rb_gemm_stream(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                                    1 if gated else 0, M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                                    _ptr(tc5_status(x.device)), _stream()), "gemm_stream")
+
+
+def gemm_stream_plan(M: int, N: int, K: int, gated: bool = False):
+    """(rows of the largest range, chunks per CTA, rows of the tallest chunk, parts of K side by side on the lanes)
+    on the current device."""
+    buf = (c_int * 4)()
+    tc5_lib().rb_gemm_stream_plan(M, N, K, 1 if gated else 0, buf)
+    return tuple(buf)
 
 
 def gemm_tc5_bmn(x: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int = 128) -> None:

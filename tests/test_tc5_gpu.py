@@ -64,3 +64,63 @@ def test_pipelined_product_with_swiglu_epilogue(M, I, K):
     assert _status_clear(ops) == 0
     gg, uu = x.float().cpu() @ gate.float().T, x.float().cpu() @ up.float().T
     assert torch.allclose(out.float().cpu(), gg * torch.sigmoid(gg) * uu, atol=2e-2, rtol=3e-2)
+
+
+# ------------------------------------------------------------------------------- the weight-streaming kernel
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 32, 50, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(16, 32), (100, 72), (384, 96), (1000, 4096), (4104, 1544)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_stream(M, N, K, out_dtype):
+    ops = _ops()
+    x, w, want = _case(M, N, K, M * 1000 + N)
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    ops.gemm_stream(x, w, out)
+    assert _status_clear(ops) == 0, "a bounded wait inside the kernel gave up"
+    tol = 2e-3 if out_dtype == torch.float32 else 2e-2
+    assert (out.double() - want).abs().max() < tol
+    # a second call gives the same bits
+    out2 = torch.full_like(out, float("nan"))
+    ops.gemm_stream(x, w, out2)
+    assert _status_clear(ops) == 0
+    assert torch.equal(out2, out)
+    # a view with a row stride (the q part of a qkv buffer) works too
+    big = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    big[:, :K] = x
+    out3 = torch.empty_like(out)
+    ops.gemm_stream(big[:, :K], w, out3)
+    assert torch.equal(out3, out)
+
+
+@pytest.mark.parametrize("M", [2, 20, 70])
+@pytest.mark.parametrize("rows_per_sm", [1, 15, 20, 40, 64, 127, 128, 129, 300])
+def test_gemm_stream_ranges_and_chunks(M, rows_per_sm):
+    """Ranges of rows_per_sm or one more row a CTA: one chunk, exactly 128 rows, and several chunks of
+    unequal height."""
+    ops = _ops()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    N, K = sms * rows_per_sm + 5, 200
+    most, nchunk, tallest, parts = ops.gemm_stream_plan(M, N, K)
+    assert most == rows_per_sm + 1 and tallest == -(-most // nchunk)
+    assert (nchunk == (most + 127) // 128 and parts == 1) if most > 64 else (nchunk == 1 and parts > 1)
+    x, w, want = _case(M, N, K, M)
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_stream(x, w, out)
+    assert _status_clear(ops) == 0
+    assert (out.double() - want).abs().max() < 2e-3
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 32, 50, 128])
+@pytest.mark.parametrize("I,K", [(8, 32), (104, 40), (224, 96), (3072, 1024), (12288, 264)])
+def test_gemm_stream_gated(M, I, K):
+    ops = _ops()
+    g = torch.Generator().manual_seed(M + I)
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    gate = (torch.randn(I, K, generator=g) / K ** 0.5).bfloat16()
+    up = (torch.randn(I, K, generator=g) / K ** 0.5).bfloat16()
+    woven = torch.stack([gate.view(-1, 8, K), up.view(-1, 8, K)], dim=1).reshape(2 * I, K).contiguous().to(DEV)
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_stream(x, woven, out, gated=True)
+    assert _status_clear(ops) == 0
+    gg, uu = x.float().cpu() @ gate.float().T, x.float().cpu() @ up.float().T
+    assert torch.allclose(out.float().cpu(), gg * torch.sigmoid(gg) * uu, atol=2e-2, rtol=3e-2)
