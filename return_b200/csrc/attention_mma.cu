@@ -314,13 +314,94 @@ constexpr int DC_STAGES = (D <= 128) ? 3 : 2;   // pipeline depth per warp, boun
 #endif
 constexpr int DC_N = 16;      // keys per warp tile
 
+// The decode kernel can do the work of the q/k norm + rotation + cache-write kernel for its own
+// token: its query heads go normed and rotated straight into shared memory, and the CTA whose key
+// range ends at the new token writes that token's key (normed, rotated) and value into the cache
+// before it reads them back with everything else.  The arithmetic is that of rope_cache.cu.
+struct FusedRope {
+    const void* qw;            // per-head norm weights of q and k, or null: no norm
+    const void* kw;
+    int w_dtype;
+    float eps, offset;
+    const float* cos_t;        // [positions, rot_dim / 2] each
+    const float* sin_t;
+    int rot_dim;
+    bf16* kpool;               // the pools again, to write to
+    bf16* vpool;
+    int write_kv;
+};
+
+__device__ __forceinline__ float2 ld_pair(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void st_pair(bf16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y); }
+
+// One warp norms and rotates one head x[0..D) at position p; dst(i) is where elements i, i + 1 go.
+template <typename DstFn>
+__device__ __forceinline__ void warp_norm_rope(const bf16* __restrict__ x, const void* __restrict__ w, int w_dtype,
+                                               float eps, float offset, const float* __restrict__ cos_t,
+                                               const float* __restrict__ sin_t, int rot_dim, int p, int lane, DstFn dst) {
+    const int half = rot_dim >> 1;
+    const float* cs = cos_t + (size_t)p * half;
+    const float* sn = sin_t + (size_t)p * half;
+    // every load is issued before the first use: the head, its norm weights and its angles arrive together
+    float2 a[2], b[2], wa[2], wb[2], c[2], sv[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = 2 * lane + 64 * j;
+        if (i < half) {
+            a[j] = ld_pair(x + i);
+            b[j] = ld_pair(x + i + half);
+            c[j] = *reinterpret_cast<const float2*>(cs + i);
+            sv[j] = *reinterpret_cast<const float2*>(sn + i);
+            wa[j] = wb[j] = make_float2(1.f, 1.f);
+            if (w) {
+                wa[j] = make_float2(offset + load_as_f32(w, w_dtype, i), offset + load_as_f32(w, w_dtype, i + 1));
+                wb[j] = make_float2(offset + load_as_f32(w, w_dtype, i + half), offset + load_as_f32(w, w_dtype, i + half + 1));
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+        if (2 * lane + 64 * j < half)
+            ss += a[j].x * a[j].x + a[j].y * a[j].y + b[j].x * b[j].x + b[j].y * b[j].y;
+    for (int i = rot_dim + 2 * lane; i < D; i += 64) {
+        const float2 v = ld_pair(x + i);
+        ss += v.x * v.x + v.y * v.y;
+    }
+    float rstd = 1.f;
+    if (w) {
+        ss = warp_sum(ss);
+        rstd = 1.0f / sqrtf(ss / (float)D + eps);
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int i = 2 * lane + 64 * j;
+        if (i < half) {
+            float2 x1 = make_float2(a[j].x * rstd, a[j].y * rstd), x2 = make_float2(b[j].x * rstd, b[j].y * rstd);
+            if (w) {
+                x1.x *= wa[j].x; x1.y *= wa[j].y;
+                x2.x *= wb[j].x; x2.y *= wb[j].y;
+            }
+            st_pair(dst(i), make_float2(x1.x * c[j].x - x2.x * sv[j].x, x1.y * c[j].y - x2.y * sv[j].y));
+            st_pair(dst(i + half), make_float2(x2.x * c[j].x + x1.x * sv[j].x, x2.y * c[j].y + x1.y * sv[j].y));
+        }
+    }
+    for (int i = rot_dim + 2 * lane; i < D; i += 64) {
+        float2 v = ld_pair(x + i);
+        v.x *= rstd; v.y *= rstd;
+        if (w) { v.x *= offset + load_as_f32(w, w_dtype, i); v.y *= offset + load_as_f32(w, w_dtype, i + 1); }
+        st_pair(dst(i), v);
+    }
+}
+
+template <bool FUSED>
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
                    const bf16* __restrict__ vpool, const int* __restrict__ dec_segs,
                    const int* __restrict__ cu_q, const int* __restrict__ seg_kv_len,
                    const int* __restrict__ block_table, int bt_stride, int page_size,
                    float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
-                   int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits) {
+                   int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits, FusedRope fr) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                    // 16 x D
     int* sBT = reinterpret_cast<int*>(sQ + 16 * D);                  // the block-table entries this CTA walks
@@ -347,22 +428,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
     const StagedTable bt = stage_table(sBT, block_table + (size_t)seg * bt_stride, pg.block(max(lo, t_begin * DC_N)),
                                        pg.block(min(hi, t_end * DC_N - 1)), tid, DC_WARPS * 32);
 
-    for (int c = tid; c < 16 * CHUNKS; c += DC_WARPS * 32) {
-        const int r = c / CHUNKS, ch = c - r * CHUNKS;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < rows_valid) v = *reinterpret_cast<const uint4*>(q + (size_t)tok_row * ld + (size_t)(h0 + r) * D + ch * 8);
-        *reinterpret_cast<uint4*>(sQ + soff(r, ch)) = v;
-    }
-    __syncthreads();
-    unsigned qf[KSTEPS][4];
-#pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk)
-        ldsm_x4(qf[kk], sQ + soff((lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
-
-    float o[DTILES][4];
-#pragma unroll
-    for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    __syncthreads();                                              // the staged block table
 
     // Everything that depends on the lane only is worked out once: byte offsets of the ldmatrix
     // rows inside a stage, and of the 16-byte chunks this lane copies.
@@ -405,11 +471,73 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
 #pragma unroll
         for (int c = 0; c < CPT; ++c) cp_async16_u(st + TILE_BYTES + doff[c], vs + c * 16, pred);
     };
+    // The first tiles are requested before anything else is done; only when this CTA is about to write
+    // the new token into the cache and that token's tile is among the first, the requests wait for
+    // the write.
+    const bool writes_new = FUSED && fr.write_kv && hi / DC_N >= t_begin && hi / DC_N < t_end;
+    const bool early = !writes_new || hi / DC_N - t_begin >= DC_WARPS * (DC_STAGES - 1);
+    if (early) {
 #pragma unroll
-    for (int s = 0; s < DC_STAGES - 1; ++s) {
-        if (s < n_my) issue(s, s);
-        cp_async_commit();
+        for (int s = 0; s < DC_STAGES - 1; ++s) {
+            if (s < n_my) issue(s, s);
+            cp_async_commit();
+        }
     }
+
+    if (FUSED) {
+        const bf16* tok = q + (size_t)tok_row * ld;                  // the raw projections of this token
+        // the CTA whose keys end at the new token puts that token into the cache; the barrier below
+        // orders these stores before the asynchronous copies that read them back
+        if (writes_new && warp < 2) {
+            const int page = block_table[(size_t)seg * bt_stride + pg.block(hi)];
+            if (page >= 0) {
+                const size_t slot = (((size_t)page * Hkv + kvh) * pg.page_size + pg.row(hi)) * D;
+                if (warp == 0) {
+                    bf16* kd = fr.kpool + slot;
+                    warp_norm_rope(tok + (size_t)(Hq + kvh) * D, fr.kw, fr.w_dtype, fr.eps, fr.offset, fr.cos_t, fr.sin_t,
+                                   fr.rot_dim, hi, lane, [&](int i) { return kd + i; });
+                } else {
+                    const bf16* vs = tok + (size_t)(Hq + Hkv + kvh) * D;
+                    for (int ch = lane; ch < CHUNKS; ch += 32)
+                        *reinterpret_cast<uint4*>(fr.vpool + slot + ch * 8) = *reinterpret_cast<const uint4*>(vs + ch * 8);
+                }
+            }
+        }
+        // the query heads, starting with the warps that had no key or value to write
+        for (int r = (warp + 2) % DC_WARPS; r < 16; r += DC_WARPS) {
+            if (r < rows_valid) {
+                warp_norm_rope(tok + (size_t)(h0 + r) * D, fr.qw, fr.w_dtype, fr.eps, fr.offset, fr.cos_t, fr.sin_t,
+                               fr.rot_dim, hi, lane, [&](int i) { return sQ + soff(r, i >> 3) + (i & 7); });
+            } else {
+                for (int ch = lane; ch < CHUNKS; ch += 32) *reinterpret_cast<uint4*>(sQ + soff(r, ch)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    } else {
+        for (int c = tid; c < 16 * CHUNKS; c += DC_WARPS * 32) {
+            const int r = c / CHUNKS, ch = c - r * CHUNKS;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < rows_valid) v = *reinterpret_cast<const uint4*>(q + (size_t)tok_row * ld + (size_t)(h0 + r) * D + ch * 8);
+            *reinterpret_cast<uint4*>(sQ + soff(r, ch)) = v;
+        }
+    }
+    __syncthreads();
+    if (!early) {
+#pragma unroll
+        for (int s = 0; s < DC_STAGES - 1; ++s) {
+            if (s < n_my) issue(s, s);
+            cp_async_commit();
+        }
+    }
+    unsigned qf[KSTEPS][4];
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk)
+        ldsm_x4(qf[kk], sQ + soff((lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4)));
+
+    float o[DTILES][4];
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
     int stage = 0, fill_stage = DC_STAGES - 1;
     for (int i = 0; i < n_my; ++i) {
         if (i + DC_STAGES - 1 < n_my) issue(i + DC_STAGES - 1, fill_stage);
@@ -595,10 +723,11 @@ RB_EXPORT long long rb_attn_decode_scratch_floats(int n_dec, int Hq, int num_spl
     return num_splits <= 1 ? 0 : (long long)n_dec * Hq * num_splits * (D + 2);
 }
 
-RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
-                             int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
-                             int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
-                             float scale, int window, int num_splits, cudaStream_t st) {
+namespace {
+int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
+                  int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
+                  int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
+                  float scale, int window, int num_splits, const FusedRope* fused, cudaStream_t st) {
     if (n_dec <= 0) return 0;
     if (num_splits < 1 || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
@@ -607,20 +736,54 @@ RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const voi
     const size_t smem = (size_t)16 * D * sizeof(bf16) + BT_CAP * sizeof(int) + (pipe > merge ? pipe : merge);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_dec * Hq * num_splits * D : nullptr;
     dim3 grid(n_dec, Hkv * m_tiles, num_splits);
-    int rc = rb_launch_pdl(attn_decode_kernel, grid, dim3(DC_WARPS * 32), smem, st,
-        (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
-        bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits);
+    FusedRope none = {};
+    int rc;
+    if (fused != nullptr)
+        rc = rb_launch_pdl(attn_decode_kernel<true>, grid, dim3(DC_WARPS * 32), smem, st,
+            (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused);
+    else
+        rc = rb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DC_WARPS * 32), smem, st,
+            (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none);
     if (rc != 0 || num_splits == 1) return rc;
     dim3 cgrid(n_dec, Hq);
     return rb_launch_pdl(attn_combine_kernel, cgrid, dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,
                          dec_segs, cu_q, (bf16*)out, Hq, num_splits);
+}
+}  // namespace
+
+RB_EXPORT int rb_attn_decode(const void* q, int ld, const void* kpool, const void* vpool, const int* dec_segs,
+                             int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
+                             int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
+                             float scale, int window, int num_splits, cudaStream_t st) {
+    return launch_decode(q, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
+                         scratch, out, Hq, Hkv, scale, window, num_splits, nullptr, st);
+}
+
+// The same for a step of single tokens only, with the q/k norm, the rotation and the cache write of
+// those tokens done inside (qkv holds the raw projections; nothing else has touched them).
+RB_EXPORT int rb_attn_decode_fused(const void* qkv, int ld, void* kpool, void* vpool, const int* dec_segs,
+                                   int n_dec, const int* cu_q, const int* seg_kv_len, const int* block_table,
+                                   int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
+                                   float scale, int window, int num_splits, const void* qw, const void* kw,
+                                   int w_dtype, float eps, float offset, const float* cos_t, const float* sin_t,
+                                   int rot_dim, int write_kv, cudaStream_t st) {
+    if (rot_dim > D || (rot_dim & 3) || rot_dim > 256) return (int)cudaErrorInvalidValue;
+    FusedRope fr;
+    fr.qw = qw; fr.kw = kw; fr.w_dtype = w_dtype; fr.eps = eps; fr.offset = offset;
+    fr.cos_t = cos_t; fr.sin_t = sin_t; fr.rot_dim = rot_dim;
+    fr.kpool = (bf16*)kpool; fr.vpool = (bf16*)vpool; fr.write_kv = write_kv;
+    return launch_decode(qkv, ld, kpool, vpool, dec_segs, n_dec, cu_q, seg_kv_len, block_table, bt_stride, page_size,
+                         scratch, out, Hq, Hkv, scale, window, num_splits, &fr, st);
 }
 
 // ------------------------------------------------------------------ decode attention without allocation

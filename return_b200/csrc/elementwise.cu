@@ -313,3 +313,4 @@ RB_EXPORT int rb_swiglu(const void* gu, void* out, int act_dtype, int T, int I, 
         swiglu_kernel<bf16><<<blocks, threads, 0, st>>>((const bf16*)gu, (bf16*)out, T, I, block);
     return rb_launch_status();
 }
+

@@ -37,7 +37,7 @@ class ModelRunner:
         self.storage.allocate()
         self.staging = BatchStaging(self.env.device)
         self.vocab_size = model.spec.vocab_size
-        self._graphs = {}                   # decode batch size -> (graph, static batch, static logits)
+        self._graphs = {}                   # (decode batch size, context span) -> (graph, static batch, static logits)
         self._graph_pool = None
         self.launches_per_replay = {}       # decode batch size -> kernels of this package in its graph
 
@@ -114,11 +114,15 @@ class ModelRunner:
     # ------------------------------------------------------------------ CUDA graphs for decode steps
     def _graphed_decode(self, host) -> torch.Tensor:
         """A step of single decoded tokens replays a graph captured for its batch size, as the
-        reference does (rollout/model.py:346-407); graphs are captured on first use."""
+        reference does (rollout/model.py:346-407); graphs are captured on first use.  A captured
+        launch cannot change its grid, so there is one graph per batch size and per span of context
+        lengths (the longest request's, rounded up to a power of two or one and a half): the span fixes how many ways
+        the decode attention splits the keys."""
         n = host.num_tokens
-        entry = self._graphs.get(n)
+        span = self._span(int(host.seg_kv_len.max()))
+        entry = self._graphs.get((n, span))
         if entry is None:
-            entry = self._capture(n)
+            entry = self._capture(n, span)
         graph, static, logits = entry
         static.fill(host)
         graph.replay()
@@ -126,10 +130,26 @@ class ModelRunner:
             return logits
         return logits.index_select(0, torch.as_tensor(host.want_rows, dtype=torch.int64).to(logits.device))
 
-    def _capture(self, n: int):
+    @staticmethod
+    def _span(longest: int) -> int:
+        span = 512
+        while span < longest:
+            span += span // 2 if span & (span - 1) == 0 else span // 3     # 512, 768, 1024, 1536, 2048, ...
+        return span
+
+    def _kv_groups(self) -> int:
+        """CTAs a decoded token gives the attention kernel per split, at most over the layers."""
+        most = 1
+        for layer in self.model.spec.layers:
+            heads, kv = getattr(layer.mixer, "num_heads", None), getattr(layer.mixer, "num_kv_heads", None)
+            if heads and kv:
+                most = max(most, kv * ((heads // kv + 15) // 16))
+        return most
+
+    def _capture(self, n: int, span: int):
         max_blocks = [(self.max_positions + g.page_size - 1) // g.page_size for g in self.manager.groups]
         # every mixer of a captured step sees the same fixed split count
-        static = StaticDecodeBatch(n, max_blocks, self.env.device, ops.decode_splits_for_graph(n))
+        static = StaticDecodeBatch(n, max_blocks, self.env.device, ops.decode_splits(n * self._kv_groups(), span))
         side = torch.cuda.Stream(device=self.env.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                      # warm-up outside the capture
@@ -143,11 +163,12 @@ class ModelRunner:
         self.launches_per_replay[n] = ops.launch_count - before
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        self._graphs[n] = (graph, static, logits)
-        return self._graphs[n]
+        self._graphs[(n, span)] = (graph, static, logits)
+        return self._graphs[(n, span)]
 
     def capture_decode_graphs(self, batch_sizes=None) -> None:
         """Captures the decode graphs ahead of the first request (the reference's ``build_graph``)."""
+        span = self._span(min(self.max_positions, 4096))
         for n in (batch_sizes or range(1, self.config.max_reside + 1)):
-            if n not in self._graphs:
-                self._capture(n)
+            if (n, span) not in self._graphs:
+                self._capture(n, span)

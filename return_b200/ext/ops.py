@@ -368,6 +368,8 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
         P, I, F = c_void_p, c_int, c_float
         lib.rb_attn_prefill.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P]
         lib.rb_attn_decode.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P]
+        lib.rb_attn_decode_fused.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P, P, I, F, F, P, P, I, I, P]
+        lib.rb_attn_decode_fused.restype = c_int
         lib.rb_attn_decode_scratch_floats.argtypes = [I, I, I]
         lib.rb_attn_decode_scratch_floats.restype = ctypes.c_longlong
         lib.rb_attn_prefill.restype = lib.rb_attn_decode.restype = lib.rb_attn_head_dim.restype = c_int
@@ -421,17 +423,10 @@ def decode_splits(n_ctas_base: int, max_kv_len: int, ctas_per_sm: int = 2) -> in
         if s > 1 and (max_kv_len + s - 1) // s < 128:
             break
         waves = (n_ctas_base * s + slots - 1) // slots
-        cost = waves * ((tiles + s - 1) // s + 4)          # + a few tiles' worth of fixed work per CTA
+        cost = waves * ((tiles + s - 1) // s + 16)         # + the fixed work of a CTA, about 16 tiles' worth (3 us)
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
-
-
-def decode_splits_for_graph(n_decode: int) -> int:
-    """The split count baked into a captured decode step of ``n_decode`` tokens.  It cannot follow
-    the lengths of the requests, so it is chosen to fill the GPU with eight kv-head groups a
-    request (more heads only add CTAs); splits that get no keys are neutral."""
-    return decode_splits(n_decode * 8, 4096)
 
 
 def attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
@@ -460,6 +455,57 @@ def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, blo
                               num_splits, _stream()), "attention_decode", 2 if num_splits > 1 else 1)
 
 
+def _decode_split_count(batch, num_heads, num_kv_heads, window) -> int:
+    host = batch.host
+    n_dec = host.decode_segs.shape[0]
+    group = num_heads // num_kv_heads
+    base = n_dec * num_kv_heads * ((group + 15) // 16)
+    longest = int(host.seg_kv_len[host.decode_segs].max())
+    if window:
+        longest = min(longest, int(window))
+    fixed = getattr(batch, "fixed_decode_splits", None)
+    return fixed or decode_splits(base, longest)
+
+
+def decode_only(batch, dtype, num_heads, num_kv_heads, window=None) -> bool:
+    """Whether the step holds single decoded tokens only, runs on the tensor-core path, and is small enough
+    that the decode attention kernel should norm, rotate and cache those tokens itself: the saved launch
+    pays while the kernel's CTAs fit on the GPU at once; with more, the work added to every CTA costs
+    more than the small kernel it replaces (measured: +1 % at 8 requests, -2 % at 64)."""
+    host = batch.host
+    if not (dtype == torch.bfloat16 and host.prefill_tiles.shape[0] == 0
+            and host.decode_segs.shape[0] == host.num_tokens and host.num_tokens > 0):
+        return False
+    group = num_heads // num_kv_heads
+    ctas = host.num_tokens * num_kv_heads * ((group + 15) // 16) * _decode_split_count(batch, num_heads, num_kv_heads, window)
+    return ctas <= 2 * NUM_SMS
+
+
+def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_dim, k_pool, v_pool, batch,
+                           block_table, page_size, out, num_heads, num_kv_heads, head_dim, scale, window=None,
+                           write_kv=True) -> None:
+    """A step of single tokens: per-head q/k norm, rotation, cache write and split-KV attention in one kernel
+    (plus the merge of the splits).  ``qkv`` holds the raw projections and is left as it is."""
+    assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
+    lib = attention_lib(head_dim)
+    n = batch.decode_segs.shape[0]
+    splits = _decode_split_count(batch, num_heads, num_kv_heads, window)
+    floats = lib.rb_attn_decode_scratch_floats(n, num_heads, splits)
+    scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device) if floats else None
+    if rot_dim:
+        assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] * 2 == rot_dim
+        assert cos.is_contiguous() and sin.is_contiguous()
+    else:
+        cos = sin = batch.cu_q          # never read: a rotary width of zero rotates nothing
+    wd = dtype_code(q_weight.dtype) if q_weight is not None else F32
+    _check(lib.rb_attn_decode_fused(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(batch.decode_segs), n,
+                                    _ptr(batch.cu_q), _ptr(batch.seg_kv_len), _ptr(block_table), block_table.stride(0),
+                                    page_size, _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale,
+                                    int(window or 0), splits, _ptr(q_weight), _ptr(k_weight), wd, eps, offset,
+                                    _ptr(cos), _ptr(sin), rot_dim, 1 if write_kv else 0, _stream()),
+           "attention_decode_fused", 2 if splits > 1 else 1)
+
+
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,
                     head_dim, scale, window=None) -> None:
     """Attention of every token of the step over its request's cached keys (its own included).
@@ -481,15 +527,9 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
     n_dec = host.decode_segs.shape[0]
     if n_dec:
-        group = num_heads // num_kv_heads
-        base = n_dec * num_kv_heads * ((group + 15) // 16)
-        longest = int(host.seg_kv_len[host.decode_segs].max())
-        if window:
-            longest = min(longest, int(window))
-        fixed = getattr(batch, "fixed_decode_splits", None)
         attention_decode_mma(qkv, k_pool, v_pool, batch.decode_segs, batch.cu_q, batch.seg_kv_len, block_table,
                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
-                             fixed or decode_splits(base, longest))
+                             _decode_split_count(batch, num_heads, num_kv_heads, window))
 
 
 # ------------------------------------------------------------------------------- sampling

@@ -2,7 +2,8 @@
 
 Projections q, k, v as one fused product (the reference runs three, :29-31; the fused weight is
 their row-wise concatenation), per-head RMSNorm of q and k before the rotation (:29-30),
-rotation and cache write in one kernel, attention over the block table, output projection
+rotation and cache write in one kernel (for a step of single tokens: inside the attention kernel),
+attention over the block table, output projection
 (:55-56).  Sizes, window, norm and position encoding come from the specification.
 """
 from __future__ import annotations
@@ -63,6 +64,16 @@ class PagedAttention(Mixer):
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         offset = s.qk_norm.offset if s.qk_norm is not None else 0.0
         tables = self.position.rotary_tables() if self.position is not None else None
+        o = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+        if (tables is not None or self.position is None) and ops.decode_only(b, x.dtype, s.num_heads, s.num_kv_heads, s.window):
+            # single decoded tokens only: norm, rotation, cache write and attention are one kernel
+            cos, sin, rot = tables if tables is not None else (None, None, 0)
+            ops.attention_decode_fused(qkv, qw, kw, eps, offset, cos, sin, rot, kv.k, kv.v, b, kv.block_table,
+                                       kv.page_size, o, s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
+                                       write_kv=ctx.write_cache)
+            y = torch.empty((T, s.hidden_size), dtype=x.dtype, device=x.device)
+            ops.linear(o, self.p_o, y)
+            return y
         if tables is not None or self.position is None:
             cos, sin, rot = tables if tables is not None else (None, None, 0)
             ops.qk_norm_rope_write(qkv, qw, kw, eps, cos, sin, rot, b.pos, b.tok_seg, kv.block_table,
@@ -80,7 +91,6 @@ class PagedAttention(Mixer):
                                        kv.page_size, kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim,
                                        write_kv=True)
 
-        o = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
         ops.paged_attention(qkv, kv.k, kv.v, b, kv.block_table, kv.page_size, o, s.num_heads,
                             s.num_kv_heads, s.head_dim, s.scale, s.window)
         y = torch.empty((T, s.hidden_size), dtype=x.dtype, device=x.device)

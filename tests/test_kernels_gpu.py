@@ -281,6 +281,52 @@ def test_attention_prefill_tc5(Hq, Hkv, D, P, window):
     assert torch.allclose(out.float().cpu(), pg.reference(scale, window), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,P", ATT_SHAPES)
+@pytest.mark.parametrize("window,rot_frac,norm", [(None, 1.0, True), (37, 0.5, True), (None, 1.0, False)])
+def test_attention_decode_fused(Hq, Hkv, D, P, window, rot_frac, norm):
+    """Norm, rotation, cache write and attention of single tokens in one kernel, against the two kernels
+    it stands for; the new token's key and value must land in the cache bit for bit."""
+    import types
+    ops = _ops()
+    kv_lens = [1, 70, 200, 16, 129, 511, 17, 64]
+    n = len(kv_lens)
+    pg = Paged(kv_lens, [1] * n, Hq, Hkv, D, P, torch.bfloat16, seed=D + 9)
+    g = torch.Generator().manual_seed(5)
+    raw = torch.randn(n, (Hq + 2 * Hkv) * D, generator=g).bfloat16().to(DEV)
+    rot = int(D * rot_frac) // 4 * 4
+    pos_max = max(kv_lens)
+    inv = 1.0 / (10000.0 ** (torch.arange(rot // 2, dtype=torch.float32) / max(rot // 2, 1)))
+    ang = torch.arange(pos_max, dtype=torch.float32)[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous().to(DEV), ang.sin().contiguous().to(DEV)
+    qw = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV) if norm else None
+    kw = (1 + 0.1 * torch.randn(D, generator=g)).to(DEV) if norm else None
+    scale = 0.7 / math.sqrt(D)
+    segs = torch.arange(n, dtype=torch.int32, device=DEV)
+    # the last token of every request is not in the cache yet: poison its slot
+    k0, v0 = pg.kpool.clone(), pg.vpool.clone()
+    for i, L in enumerate(kv_lens):
+        page, row = int(pg.bt[i, (L - 1) // P]), (L - 1) % P
+        k0[page, :, row] = float("nan")
+        v0[page, :, row] = float("nan")
+    # the two kernels
+    k1, v1, q1 = k0.clone(), v0.clone(), raw.clone()
+    ops.qk_norm_rope_write(q1, qw, kw, 1e-6, cos, sin, rot, pg.pos, pg.tok_seg, pg.bt, P, k1, v1, Hq, Hkv, D)
+    want = torch.empty(n, Hq * D, device=DEV, dtype=torch.bfloat16)
+    ops.attention_decode_mma(q1, k1, v1, segs, pg.cu_q, pg.seg_kv_len, pg.bt, P, want, Hq, Hkv, D, scale, window or 0,
+                             num_splits=3)
+    # the one kernel
+    host = types.SimpleNamespace(decode_segs=segs.cpu().numpy(), seg_kv_len=pg.seg_kv_len.cpu().numpy(), num_tokens=n,
+                                 prefill_tiles=torch.zeros(0, 2).numpy())
+    batch = types.SimpleNamespace(decode_segs=segs, cu_q=pg.cu_q, seg_kv_len=pg.seg_kv_len, host=host, fixed_decode_splits=3)
+    k2, v2, q2 = k0.clone(), v0.clone(), raw.clone()
+    got = torch.full_like(want, float("nan"))
+    ops.attention_decode_fused(q2, qw, kw, 1e-6, 0.0, cos, sin, rot, k2, v2, batch, pg.bt, P, got, Hq, Hkv, D, scale, window)
+    assert torch.equal(q2, raw)
+    assert torch.equal(torch.nan_to_num(k2, nan=7.0), torch.nan_to_num(k1, nan=7.0))
+    assert torch.equal(torch.nan_to_num(v2, nan=7.0), torch.nan_to_num(v1, nan=7.0))
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("D", [64, 128])
 def test_attention_prefill_tc5_long(D):
     """Dozens of key tiles per query tile with every SM busy: the loaders, the issuing thread and the
