@@ -272,3 +272,188 @@ def test_toy_mixer_with_state_of_its_own(tmp_path):
     finally:
         registry.unregister_architecture("ToyRunningMeanLM")
         MIXERS.unregister("running_mean")
+
+
+# ------------------------------------------------------------------------------- a second toy architecture:
+# the engine's attention with a position encoding of the test's own, and a feed-forward with routing
+
+@dataclass(frozen=True)
+class PairRotationSpec:
+    """Neighbouring pairs (2i, 2i + 1) of a head rotated by position * base^(-i / (D/2))."""
+    head_dim: int
+    base: float
+    kind: str = "pair_rotation"
+
+
+@dataclass(frozen=True)
+class RoutedSpec:
+    """Top-1 of ``experts`` small SwiGLU experts, weighted by the router's softmax probability."""
+    hidden_size: int
+    intermediate_size: int
+    experts: int
+    kind: str = "toy_routed"
+
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    vocab_size: int
+    hidden_size: int
+    intermediate_size: int
+    experts: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    base: float
+    eps: float
+    architectures: tuple = ("ToyRoutedLM",)
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(*(raw[k] for k in ("vocab_size", "hidden_size", "intermediate_size", "experts", "heads", "kv_heads",
+                                      "head_dim", "base", "eps")))
+
+    def to_dict(self):
+        d = dataclasses.asdict(self)
+        d["architectures"] = list(self.architectures)
+        d["model_type"] = "toy_routed"
+        return d
+
+
+def _pair_rotate(x, pos, base):
+    """x [T, heads, D] float32, pos [T]: the toy encoding, shared by the part and the reference."""
+    D = x.shape[-1]
+    inv = base ** (-torch.arange(D // 2, dtype=torch.float32, device=x.device) / (D // 2))
+    ang = pos.to(torch.float32)[:, None, None] * inv[None, None, :]
+    c, s = ang.cos(), ang.sin()
+    a, b = x[..., 0::2], x[..., 1::2]
+    return torch.stack([a * c - b * s, a * s + b * c], dim=-1).reshape(x.shape)
+
+
+def _register_routed():
+    from return_b200.config import registry
+    from return_b200.parts import (FEED_FORWARDS, POSITION_ENCODINGS, AttentionSpec, BlockSpec, DecoderSpec, FeedForward,
+                                   NormSpec, ParamSpec, PositionEncoding, SwiGLUSpec)
+    from return_b200.weights.loader import Source
+
+    class PairRotation(PositionEncoding):
+        def apply(self, qkv, batch, num_heads, num_kv_heads, head_dim):
+            T = qkv.shape[0]
+            n = (num_heads + num_kv_heads) * head_dim                 # q and k heads; v stays
+            x = qkv[:, :n].float().reshape(T, num_heads + num_kv_heads, head_dim)
+            qkv[:, :n] = _pair_rotate(x, batch.pos, self.spec.base).reshape(T, n).to(qkv.dtype)
+
+    class Routed(FeedForward):
+        def params(self):
+            s = self.spec
+            return {"router": ParamSpec((s.experts, s.hidden_size)),
+                    "w1": ParamSpec((s.experts * 2 * s.intermediate_size, s.hidden_size)),
+                    "w2": ParamSpec((s.experts * s.hidden_size, s.intermediate_size))}
+
+        def forward(self, x, ctx):
+            s = self.spec
+            logits = x.float() @ self.p_router.float().T              # router logits in 32-bit
+            prob, pick = torch.softmax(logits, dim=-1).max(dim=-1)
+            w1 = self.p_w1.float().reshape(s.experts, 2 * s.intermediate_size, s.hidden_size)
+            w2 = self.p_w2.float().reshape(s.experts, s.hidden_size, s.intermediate_size)
+            y = torch.zeros_like(x, dtype=torch.float32)
+            for e in range(s.experts):                                # every expert on every row, masked: no host sync
+                gu = x.float() @ w1[e].T
+                g, u = gu[:, :s.intermediate_size], gu[:, s.intermediate_size:]
+                y += ((g * torch.sigmoid(g) * u) @ w2[e].T) * (prob * (pick == e))[:, None]
+            return y.to(x.dtype)
+
+    POSITION_ENCODINGS.register("pair_rotation", PairRotation)
+    FEED_FORWARDS.register("toy_routed", Routed)
+
+    def decoder_spec(cfg, max_positions=None):
+        norm = NormSpec(cfg.hidden_size, cfg.eps)
+        att = lambda position: AttentionSpec(cfg.hidden_size, cfg.heads, cfg.kv_heads, cfg.head_dim, cfg.head_dim ** -0.5,
+                                             position=position)
+        routed = BlockSpec(att(PairRotationSpec(cfg.head_dim, cfg.base)),
+                           RoutedSpec(cfg.hidden_size, cfg.intermediate_size, cfg.experts), norm, norm)
+        dense = BlockSpec(att(None), SwiGLUSpec(cfg.hidden_size, cfg.intermediate_size), norm, norm)
+        return DecoderSpec(cfg.vocab_size, cfg.hidden_size, (routed, dense), DecoderSpec.in_order(2), norm,
+                           tie_embeddings=False)
+
+    def weight_sources(cfg):
+        m = {"embed": Source(("emb",)), "lm_head": Source(("head",)), "final_norm.weight": Source(("nf",))}
+        for i in range(2):
+            m[f"layers.{i}.mixer.qkv"] = Source((f"l{i}.q", f"l{i}.k", f"l{i}.v"))
+            m[f"layers.{i}.mixer.o"] = Source((f"l{i}.o",))
+            m[f"layers.{i}.mixer_norm.weight"] = Source((f"l{i}.n1",))
+            m[f"layers.{i}.feed_forward_norm.weight"] = Source((f"l{i}.n2",))
+        m["layers.0.feed_forward.router"] = Source(("l0.router",))
+        m["layers.0.feed_forward.w1"] = Source(("l0.w1",))
+        m["layers.0.feed_forward.w2"] = Source(("l0.w2",))
+        m["layers.1.feed_forward.gate_up"] = Source(("l1.gate", "l1.up"))
+        m["layers.1.feed_forward.down"] = Source(("l1.down",))
+        return m
+
+    def split_rows(cfg, pname):
+        if pname.endswith("mixer.qkv"):
+            return [cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim]
+        return None
+
+    registry.register_architecture(registry.Architecture(
+        name="ToyRoutedLM", model_type="toy_routed", config_cls=RoutedConfig,
+        decoder_spec=decoder_spec, weight_sources=weight_sources, split_rows=split_rows))
+
+
+def _routed_reference(model_dir, cfg, ids):
+    from safetensors.torch import load_file
+    w = {k: v.float() for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
+    T = len(ids)
+    pos = torch.arange(T)
+    x = w["emb"][torch.tensor(ids)]
+    for i in range(2):
+        a = plain.rms_norm(x, w[f"l{i}.n1"], cfg.eps)
+        q = (a @ w[f"l{i}.q"].T).reshape(T, cfg.heads, cfg.head_dim)
+        k = (a @ w[f"l{i}.k"].T).reshape(T, cfg.kv_heads, cfg.head_dim)
+        v = (a @ w[f"l{i}.v"].T).reshape(T, cfg.kv_heads, cfg.head_dim)
+        if i == 0:
+            q, k = _pair_rotate(q, pos, cfg.base), _pair_rotate(k, pos, cfg.base)
+        o = plain.attention_scores_softmax_pv(q, k, v, pos, pos, cfg.head_dim ** -0.5, None)
+        x = x + o.reshape(T, -1) @ w[f"l{i}.o"].T
+        b = plain.rms_norm(x, w[f"l{i}.n2"], cfg.eps)
+        if i == 0:
+            prob, pick = torch.softmax(b @ w["l0.router"].T, dim=-1).max(dim=-1)
+            w1 = w["l0.w1"].reshape(cfg.experts, 2 * cfg.intermediate_size, cfg.hidden_size)
+            w2 = w["l0.w2"].reshape(cfg.experts, cfg.hidden_size, cfg.intermediate_size)
+            y = torch.zeros_like(b)
+            for t in range(T):
+                e = int(pick[t])
+                gu = w1[e] @ b[t]
+                g, u = gu[:cfg.intermediate_size], gu[cfg.intermediate_size:]
+                y[t] = (w2[e] @ (g * torch.sigmoid(g) * u)) * prob[t]
+            x = x + y
+        else:
+            g, u = b @ w["l1.gate"].T, b @ w["l1.up"].T
+            x = x + (g * torch.sigmoid(g) * u) @ w["l1.down"].T
+    return plain.rms_norm(x, w["nf"], cfg.eps) @ w["head"].T
+
+
+def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
+    """An architecture registered from this file: the engine's paged attention with a position encoding
+    defined here (layer 0) and with none (layer 1), a routed feed-forward defined here (layer 0) beside
+    the engine's dense one (layer 1).  Replayed in portions and mixed batches against plain math."""
+    from return_b200.config import registry
+    from return_b200.engine.replay import TraceReplayer
+    from return_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS
+    from return_b200.weights import loader
+    _register_routed()
+    try:
+        cfg = RoutedConfig(vocab_size=70, hidden_size=32, intermediate_size=24, experts=3, heads=4, kv_heads=2,
+                           head_dim=16, base=50.0, eps=1e-5)
+        d = loader.write_random_model(os.path.join(str(tmp_path), "routed"), cfg, seed=3)
+        arch, read = registry.read_config(d)
+        assert arch.name == "ToyRoutedLM" and read == cfg
+        reqs = {f"t{i}": helpers.random_ids(70, n, 200 + i) for i, n in enumerate((33, 9, 21, 14))}
+        steps = helpers.mixed(reqs, max_live=3, portion=7, decode_tail=4, seed=9)
+        rp = TraceReplayer(d, "float32", helpers.pool_tokens(steps), page_size=16, max_reside=3)
+        got = helpers.collect(steps, [None if (lg := rp.run_step(s)) is None else lg.cpu() for s in steps])
+        for rid, ids in reqs.items():
+            assert (got[rid] - _routed_reference(d, cfg, ids)).abs().max() < 2e-4, rid
+    finally:
+        registry.unregister_architecture("ToyRoutedLM")
+        POSITION_ENCODINGS.unregister("pair_rotation")
+        FEED_FORWARDS.unregister("toy_routed")
