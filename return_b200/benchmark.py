@@ -177,7 +177,7 @@ def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8
     dev = torch.device("cuda:0")
     qkv, k_pool, v_pool, bt, cu_q, seg_pos0, _ = _paged_case(batch, ctx, q_len, heads, kv_heads, head_dim, page, dev)
     out = torch.empty((batch * q_len, heads * head_dim), dtype=torch.bfloat16, device=dev)
-    rows = 64 if impl else 128
+    rows = 64 if impl else ops.TC5_TILE_ROWS
     tiles = torch.tensor([(i, r) for i in range(batch) for r in range(0, q_len, rows)], dtype=torch.int32, device=dev)
     kernel = ops.attention_prefill_mma if impl else ops.attention_prefill_tc5
     fn = lambda: kernel(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, bt, page, out, heads,

@@ -42,13 +42,13 @@ class HostBatch:
     want_rows: np.ndarray     # [n_want] token rows whose logits are wanted
     decode_segs: np.ndarray   # segments of one token
     prefill_tiles: np.ndarray  # [n_tiles, 2]: (segment, first row within it) for segments of several tokens
-    prefill_tiles128: np.ndarray = None   # the same in blocks of 128 rows (the tcgen05 attention kernel's tile)
+    prefill_tiles_tc5: np.ndarray = None   # the same in blocks of 256 rows, the longest contexts first (the tcgen05 kernel's tiles)
     block_tables: List[np.ndarray] = field(default_factory=list)   # per group [n, blocks]
     rids: List[Hashable] = field(default_factory=list)
 
 
 PREFILL_TILE_ROWS = 64
-PREFILL_TILE_ROWS_TC5 = 128
+PREFILL_TILE_ROWS_TC5 = 256
 
 
 def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional[int] = None,
@@ -74,7 +74,7 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
     want_rows: List[int] = []
     decode_segs: List[int] = []
     tiles: List[tuple] = []
-    tiles128: List[tuple] = []
+    tiles_tc5: List[tuple] = []
     row = 0
     for i, e in enumerate(entries):
         L = lens[i]
@@ -95,12 +95,14 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
             decode_segs.append(i)
         else:
             tiles.extend((i, r0) for r0 in range(0, L, PREFILL_TILE_ROWS))
-            tiles128.extend((i, r0) for r0 in range(0, L, PREFILL_TILE_ROWS_TC5))
+            tiles_tc5.extend((i, r0) for r0 in range(0, L, PREFILL_TILE_ROWS_TC5))
         row += L
     if vocab_size is not None and (tokens.min() < 0 or tokens.max() >= vocab_size):
         raise ValueError(f"token ids must lie in [0, {vocab_size})")
     if max_positions is not None and int(seg_kv_len.max()) > max_positions:
         raise ValueError(f"a request would reach {int(seg_kv_len.max())} tokens; the engine was set up for {max_positions}")
+    # a tile's work grows with the position of its rows: the heaviest tiles are launched first
+    tiles_tc5.sort(key=lambda sr: -(int(seg_pos0[sr[0]]) + sr[1]))
     tables = []
     for g, spec in enumerate(manager.groups):
         blocks = max((int(seg_kv_len[i]) + spec.page_size - 1) // spec.page_size for i in range(n))
@@ -115,14 +117,14 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
         seg_slot=seg_slot, cu_q=cu_q, seg_pos0=seg_pos0, seg_kv_len=seg_kv_len,
         want_rows=np.asarray(want_rows, np.int32), decode_segs=np.asarray(decode_segs, np.int32),
         prefill_tiles=np.asarray(tiles, np.int32).reshape(-1, 2),
-        prefill_tiles128=np.asarray(tiles128, np.int32).reshape(-1, 2), block_tables=tables, rids=rids)
+        prefill_tiles_tc5=np.asarray(tiles_tc5, np.int32).reshape(-1, 2), block_tables=tables, rids=rids)
 
 
 class StepBatch:
     """The tables on the device, as views of one int32 buffer."""
 
     _FIELDS = ("tokens", "pos", "tok_seg", "seg_slot", "cu_q", "seg_pos0", "seg_kv_len", "want_rows",
-               "decode_segs", "prefill_tiles", "prefill_tiles128")
+               "decode_segs", "prefill_tiles", "prefill_tiles_tc5")
 
     def __init__(self, host: HostBatch, device, staging: "BatchStaging"):
         self.host = host
@@ -144,7 +146,7 @@ class StepBatch:
         for f, v in zip(self._FIELDS, views):
             setattr(self, f, v)
         self.prefill_tiles = self.prefill_tiles.view(-1, 2)
-        self.prefill_tiles128 = self.prefill_tiles128.view(-1, 2)
+        self.prefill_tiles_tc5 = self.prefill_tiles_tc5.view(-1, 2)
         self.block_tables = [v.view(bt.shape) for v, bt in zip(views[len(self._FIELDS):], host.block_tables)]
 
 
@@ -189,7 +191,7 @@ class _StaticHost:
         self.num_tokens = self.num_segments = self.num_want = n
         self.decode_segs = np.arange(n, dtype=np.int32)
         self.prefill_tiles = np.zeros((0, 2), np.int32)
-        self.prefill_tiles128 = np.zeros((0, 2), np.int32)
+        self.prefill_tiles_tc5 = np.zeros((0, 2), np.int32)
         self.cu_q = np.arange(n + 1, dtype=np.int32)
         self.seg_slot = np.zeros(n, np.int32)
         self.seg_kv_len = np.ones(n, np.int32)
@@ -225,7 +227,7 @@ class StaticDecodeBatch:
             self._h_bt.append(hv[off:off + n * b].reshape(n, b))
             self.block_tables.append(self._dev[off:off + n * b].view(n, b))
         self.prefill_tiles = torch.zeros((0, 2), dtype=torch.int32, device=device)
-        self.prefill_tiles128 = torch.zeros((0, 2), dtype=torch.int32, device=device)
+        self.prefill_tiles_tc5 = torch.zeros((0, 2), dtype=torch.int32, device=device)
         self._h["tok_seg"][:] = np.arange(n)
         self._h["cu_q"][:] = np.arange(n + 1)
         self._h["want_rows"][:] = np.arange(n)

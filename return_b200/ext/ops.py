@@ -381,6 +381,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
 
 _attn_tc5_libs = {}
 TC5_ATTENTION_HEAD_DIMS = (64, 128)
+TC5_TILE_ROWS = 256            # query rows of one CTA of the tcgen05 prefill attention kernel
 
 
 def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
@@ -397,14 +398,15 @@ def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
     return lib
 
 
-def attention_prefill_tc5(qkv, k_pool, v_pool, tiles128, cu_q, seg_pos0, block_table, page_size, out, num_heads,
+def attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
                           num_kv_heads, head_dim, scale, window=0) -> None:
-    """tcgen05 attention for the listed (segment, first row) tiles of up to 128 query rows."""
+    """tcgen05 attention for the listed (segment, first row) blocks of up to TC5_TILE_ROWS query rows
+    (the blocks with the longest contexts should come first: they take longest)."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
-    assert tiles128.dtype == torch.int32 and tiles128.is_contiguous()
+    assert tiles.dtype == torch.int32 and tiles.is_contiguous()
     lib = attention_tc5_lib(head_dim)
-    _check(lib.rb_attn_prefill_tc5(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles128),
-                                   tiles128.shape[0], _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table),
+    _check(lib.rb_attn_prefill_tc5(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles),
+                                   tiles.shape[0], _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table),
                                    block_table.stride(0), page_size, _ptr(out), num_heads, num_kv_heads, scale,
                                    int(window or 0), _ptr(tc5_status(qkv.device)), _stream()), "attention_prefill_tc5")
 
@@ -520,7 +522,7 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
     host = batch.host
     if host.prefill_tiles.shape[0]:
         if head_dim in TC5_ATTENTION_HEAD_DIMS:
-            attention_prefill_tc5(qkv, k_pool, v_pool, batch.prefill_tiles128, batch.cu_q, batch.seg_pos0, block_table,
+            attention_prefill_tc5(qkv, k_pool, v_pool, batch.prefill_tiles_tc5, batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
         else:
             attention_prefill_mma(qkv, k_pool, v_pool, batch.prefill_tiles, batch.cu_q, batch.seg_pos0, block_table,

@@ -150,7 +150,7 @@ def test_host_batch_tables():
     assert hb.cu_q.tolist() == [0, 1, 6, 8] and hb.seg_pos0.tolist() == [6, 0, 0] and hb.seg_kv_len.tolist() == [7, 5, 2]
     assert hb.want_rows.tolist() == [0, 5, 6, 7]
     assert hb.decode_segs.tolist() == [0] and hb.prefill_tiles.tolist() == [[1, 0], [2, 0]]
-    assert hb.prefill_tiles128.tolist() == [[1, 0], [2, 0]]
+    assert hb.prefill_tiles_tc5.tolist() == [[1, 0], [2, 0]]
     assert hb.block_tables[0].shape == (3, 2)
     assert hb.block_tables[0][0].tolist() == m.block_table("a", 0)
     assert hb.block_tables[0][2].tolist() == m.block_table("c", 0) + [-1]

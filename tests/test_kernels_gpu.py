@@ -263,11 +263,11 @@ def test_attention_prefill_mma(Hq, Hkv, D, P, window):
 @pytest.mark.parametrize("Hq,Hkv,D,P", [(8, 8, 64, 4), (32, 8, 128, 16), (6, 2, 128, 8), (20, 1, 64, 16), (4, 4, 128, 64)])
 @pytest.mark.parametrize("window", [None, 37, 100])
 def test_attention_prefill_tc5(Hq, Hkv, D, P, window):
-    """The tcgen05 prefill kernel: tiles of 128 rows, tails, earlier keys in the cache, windows."""
+    """The tcgen05 prefill kernel: blocks of 256 rows (two tiles of 128), tails, earlier keys in the cache, windows."""
     ops = _ops()
     kv_lens, q_lens = [2, 70, 200, 128, 129, 300, 640], [2, 70, 3, 128, 65, 130, 300]
     pg = Paged(kv_lens, q_lens, Hq, Hkv, D, P, torch.bfloat16, seed=D + 5)
-    tiles = [(i, r0) for i, ql in enumerate(q_lens) for r0 in range(0, ql, 128)]
+    tiles = [(i, r0) for i, ql in enumerate(q_lens) for r0 in range(0, ql, ops.TC5_TILE_ROWS)]
     tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
     out = torch.full((sum(q_lens), Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
     scale = 0.7 / math.sqrt(D)
@@ -341,7 +341,7 @@ def test_attention_prefill_tc5_long(D):
     pg.kpool[page, :, off] = pg.k[0][far].to(torch.bfloat16).to(DEV)
     pg.q[0][late] = pg.k[0][far, 0].repeat(Hq, 1) * 0.5
     pg.qkv[late, :Hq * D] = pg.q[0][late].reshape(-1).to(torch.bfloat16).to(DEV)
-    tiles = [(i, r0) for i, ql in enumerate(pg.q_lens) for r0 in range(0, ql, 128)]
+    tiles = [(i, r0) for i, ql in enumerate(pg.q_lens) for r0 in range(0, ql, ops.TC5_TILE_ROWS)]
     tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
     out = torch.full((sum(pg.q_lens), Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
     scale = 1.0 / math.sqrt(D)
