@@ -394,16 +394,7 @@ __device__ __forceinline__ void warp_norm_rope(const bf16* __restrict__ x, const
     }
 }
 
-// CLUSTER: the CTAs that share a token and a head group (the splits, along z) form a thread-block
-// cluster and merge their partial results through distributed shared memory, each CTA finishing a
-// slice of the heads' elements; otherwise partial results go to global memory and a second kernel
-// merges them.
-constexpr int DC_MAX_CLUSTER = 16;
-#ifndef RB_DECODE_CLUSTER
-#define RB_DECODE_CLUSTER 1                    // 0: always merge through global memory and a second kernel
-#endif            // 8 is portable; 16 needs the opt-in the launcher sets
-
-template <bool FUSED, bool CLUSTER>
+template <bool FUSED>
 __global__ void __launch_bounds__(DC_WARPS * 32)
 attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ kpool,
                    const bf16* __restrict__ vpool, const int* __restrict__ dec_segs,
@@ -655,8 +646,6 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         if (g + 8 < rows_valid) { obuf[(warp * 16 + g + 8) * D + d] = o[i][2]; obuf[(warp * 16 + g + 8) * D + d + 1] = o[i][3]; }
     }
     __syncthreads();
-    float* xo = obuf + DC_WARPS * 16 * D;                         // [16][D]: this CTA's merged accumulators
-    float* xml = xo + 16 * D;                                     // [16][2]: their maximum and sum
     for (int idx = tid; idx < rows_valid * D; idx += DC_WARPS * 32) {
         const int r = idx / D, d = idx - r * D;
         float mg = -INFINITY;
@@ -673,36 +662,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         const int h = h0 + r;
         if (num_splits == 1) {
             out[(size_t)tok_row * Hq * D + (size_t)h * D + d] = __float2bfloat16_rn(og / lg);
-        } else if (CLUSTER) {
-            xo[r * D + d] = og;
-            if (d == 0) { xml[r * 2] = mg; xml[r * 2 + 1] = lg; }
         } else {
             const size_t pidx = ((size_t)blockIdx.x * Hq + h) * num_splits + split;
             part_o[pidx * D + d] = og;
             if (d == 0) { part_ml[pidx * 2] = mg; part_ml[pidx * 2 + 1] = lg; }
         }
-    }
-    if (CLUSTER && num_splits > 1) {
-        cluster_sync_all();                                       // every split's xo / xml is written
-        const int total = rows_valid * D, per = (total + num_splits - 1) / num_splits;
-        const int end = min(total, (split + 1) * per);
-        const unsigned xo_u = smem_u32(xo), xml_u = smem_u32(xml);
-        for (int idx = split * per + tid; idx < end; idx += DC_WARPS * 32) {
-            const int r = idx / D, d = idx - r * D;
-            float mg = -INFINITY;
-            for (int sp = 0; sp < num_splits; ++sp) mg = fmaxf(mg, cluster_ld_f32(cluster_map_shared(xml_u + r * 8, sp)));
-            float lg = 0.f, acc = 0.f;
-            for (int sp = 0; sp < num_splits; ++sp) {             // in the order of the splits, whoever does it
-                const float ms = cluster_ld_f32(cluster_map_shared(xml_u + r * 8, sp));
-                if (ms != -INFINITY) {
-                    const float sc = exp2f(ms - mg);
-                    lg += cluster_ld_f32(cluster_map_shared(xml_u + r * 8 + 4, sp)) * sc;
-                    acc += cluster_ld_f32(cluster_map_shared(xo_u + (unsigned)(r * D + d) * 4, sp)) * sc;
-                }
-            }
-            out[(size_t)tok_row * Hq * D + (size_t)(h0 + r) * D + d] = __float2bfloat16_rn(acc / lg);
-        }
-        cluster_sync_all();                                       // nobody leaves while its memory is being read
     }
 }
 
@@ -754,11 +718,9 @@ RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const vo
                          Hq, Hkv, scale * LOG2E, window);
 }
 
-// Floats of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D], part_ml [n_dec, Hq, splits, 2];
-// none when the splits merge through their cluster's shared memory.
+// Floats of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D], part_ml [n_dec, Hq, splits, 2].
 RB_EXPORT long long rb_attn_decode_scratch_floats(int n_dec, int Hq, int num_splits) {
-    if (num_splits <= 1 || (RB_DECODE_CLUSTER && num_splits <= DC_MAX_CLUSTER)) return 0;    // merged inside the kernel
-    return (long long)n_dec * Hq * num_splits * (D + 2);
+    return num_splits <= 1 ? 0 : (long long)n_dec * Hq * num_splits * (D + 2);
 }
 
 namespace {
@@ -767,19 +729,15 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
                   int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
                   float scale, int window, int num_splits, const FusedRope* fused, cudaStream_t st) {
     if (n_dec <= 0) return 0;
-    if (num_splits < 1) return (int)cudaErrorInvalidValue;
+    if (num_splits < 1 || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
     const size_t pipe = (size_t)DC_WARPS * DC_STAGES * 2 * DC_N * D * sizeof(bf16);
-    const size_t merge = (size_t)(DC_WARPS + 1) * 16 * (D + 2) * sizeof(float);
+    const size_t merge = (size_t)DC_WARPS * 16 * (D + 2) * sizeof(float);
     const size_t smem = (size_t)16 * D * sizeof(bf16) + BT_CAP * sizeof(int) + (pipe > merge ? pipe : merge);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaSuccess;
-#define RB_DC_CONFIG(F, C)                                                                                              \
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<F, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        if (e == cudaSuccess && C) e = cudaFuncSetAttribute(attn_decode_kernel<F, C>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-        RB_DC_CONFIG(false, false) RB_DC_CONFIG(true, false) RB_DC_CONFIG(false, true) RB_DC_CONFIG(true, true)
-#undef RB_DC_CONFIG
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -787,22 +745,15 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
     float* part_ml = scratch ? scratch + (size_t)n_dec * Hq * num_splits * D : nullptr;
     dim3 grid(n_dec, Hkv * m_tiles, num_splits);
     FusedRope none = {};
-    const FusedRope fr = fused != nullptr ? *fused : none;
-    const bool cluster = num_splits > 1 && num_splits <= DC_MAX_CLUSTER && RB_DECODE_CLUSTER;
-#define RB_DC_ARGS (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table, \
-        bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, fr
-    if (cluster) {
-        if (fused != nullptr)
-            return rb_launch_pdl_cluster(attn_decode_kernel<true, true>, grid, dim3(DC_WARPS * 32), smem, st, (unsigned)num_splits, RB_DC_ARGS);
-        return rb_launch_pdl_cluster(attn_decode_kernel<false, true>, grid, dim3(DC_WARPS * 32), smem, st, (unsigned)num_splits, RB_DC_ARGS);
-    }
-    if (num_splits > 1 && scratch == nullptr) return (int)cudaErrorInvalidValue;
     int rc;
     if (fused != nullptr)
-        rc = rb_launch_pdl(attn_decode_kernel<true, false>, grid, dim3(DC_WARPS * 32), smem, st, RB_DC_ARGS);
+        rc = rb_launch_pdl(attn_decode_kernel<true>, grid, dim3(DC_WARPS * 32), smem, st,
+            (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused);
     else
-        rc = rb_launch_pdl(attn_decode_kernel<false, false>, grid, dim3(DC_WARPS * 32), smem, st, RB_DC_ARGS);
-#undef RB_DC_ARGS
+        rc = rb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DC_WARPS * 32), smem, st,
+            (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none);
     if (rc != 0 || num_splits == 1) return rc;
     dim3 cgrid(n_dec, Hq);
     return rb_launch_pdl(attn_combine_kernel, cgrid, dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,

@@ -108,44 +108,6 @@ __device__ __forceinline__ void pdl_trigger_late() {            // after a kerne
 #endif
 }
 
-// Thread-block clusters: a barrier over all threads of all CTAs of the cluster (every thread calls
-// both halves), and reads of another CTA's shared memory at the same offset.
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ unsigned cluster_map_shared(unsigned smem_addr, unsigned cta_rank) {
-    unsigned r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
-    return r;
-}
-__device__ __forceinline__ float cluster_ld_f32(unsigned cluster_addr) {
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
-    return v;
-}
-
-// The same launch with the CTAs along z grouped into clusters of cluster_z.
-template <typename... KArgs, typename... Args>
-static inline int rb_launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
-                                        unsigned cluster_z, Args... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = cluster_z;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = RB_PDL_MODE == 3 ? 1 : 2;
-    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-
 template <typename... KArgs, typename... Args>
 static inline int rb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                 Args... args) {

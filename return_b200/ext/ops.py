@@ -454,7 +454,7 @@ def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, blo
     _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
                               _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
                               _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
-                              num_splits, _stream()), "attention_decode", 2 if floats else 1)
+                              num_splits, _stream()), "attention_decode", 2 if num_splits > 1 else 1)
 
 
 def _decode_split_count(batch, num_heads, num_kv_heads, window) -> int:
@@ -505,7 +505,7 @@ def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_d
                                     page_size, _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale,
                                     int(window or 0), splits, _ptr(q_weight), _ptr(k_weight), wd, eps, offset,
                                     _ptr(cos), _ptr(sin), rot_dim, 1 if write_kv else 0, _stream()),
-           "attention_decode_fused", 2 if floats else 1)
+           "attention_decode_fused", 2 if splits > 1 else 1)
 
 
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,
