@@ -98,7 +98,7 @@ def build_all():
     for d in TC5_ATTENTION_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], {"HEAD_DIM": d}))
     for d in PREBUILT_HEAD_DIMS:
-        paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], {"HEAD_DIM": d, "RB_PDL_MODE": PDL_MODE}))
+        paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], _attn_defines(d)))
     return paths
 
 
@@ -358,13 +358,22 @@ def attention_simt(qkv, k_pool, v_pool, pos, tok_seg, block_table, page_size, ou
 _attn_libs = {}
 
 
+def _attn_defines(head_dim: int):
+    """Build options of the mma.sync attention library; RETURN_B200_ATTN_DEFS="NAME=1,OTHER=2" adds tuning macros."""
+    defs = {"HEAD_DIM": head_dim, "RB_PDL_MODE": PDL_MODE}
+    for item in filter(None, _os.environ.get("RETURN_B200_ATTN_DEFS", "").split(",")):
+        k, _, v = item.partition("=")
+        defs[k.strip()] = v.strip() or "1"
+    return defs
+
+
 def attention_lib(head_dim: int) -> ctypes.CDLL:
     """The tensor-core attention kernels, compiled for this head size on first use."""
     lib = _attn_libs.get(head_dim)
     if lib is None:
         if head_dim % 16 or not (16 <= head_dim <= 256):
             raise KernelError(f"head_dim={head_dim}: the attention kernels take multiples of 16 from 16 to 256")
-        lib = build.load(f"return_attn_d{head_dim}", ["attention_mma.cu"], {"HEAD_DIM": head_dim, "RB_PDL_MODE": PDL_MODE})
+        lib = build.load(f"return_attn_d{head_dim}", ["attention_mma.cu"], _attn_defines(head_dim))
         P, I, F = c_void_p, c_int, c_float
         lib.rb_attn_prefill.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P]
         lib.rb_attn_decode.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, P, I, I, F, I, I, P]
