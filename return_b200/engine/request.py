@@ -44,6 +44,15 @@ class Request:
     def all_ids(self) -> List[int]:
         return list(self.prompt_ids) + self.output
 
+    def ids_slice(self, start: int, stop: int) -> List[int]:
+        """Tokens [start, stop) of prompt + output without building the whole list."""
+        n = len(self.prompt_ids)
+        if start >= n:
+            return self.output[start - n:stop - n]
+        if stop <= n:
+            return list(self.prompt_ids[start:stop])
+        return list(self.prompt_ids[start:]) + self.output[:stop - n]
+
     @property
     def num_tokens(self) -> int:
         return len(self.prompt_ids) + len(self.output)

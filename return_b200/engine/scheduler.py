@@ -112,16 +112,17 @@ class Scheduler:
         req.finish_reason, req.error = "error", err
         plan.failed.append(req)
 
-    def _portion(self, req: Request, budget: int, plan: StepPlan) -> int:
-        """Plans the next portion of a request that still has uncomputed tokens; returns its size."""
-        ids = req.all_ids
-        remaining = len(ids) - req.num_computed
-        n = self._max_fit(req.id, min(remaining, budget))
+    def _portion(self, req: Request, budget: int, plan: StepPlan, fits_budget: bool = False) -> int:
+        """Plans the next portion of a request that still has uncomputed tokens; returns its size.
+        ``fits_budget``: the caller has just seen that ``budget`` tokens fit the free pages."""
+        total = req.num_tokens
+        remaining = total - req.num_computed
+        n = min(remaining, budget) if fits_budget else self._max_fit(req.id, min(remaining, budget))
         if n <= 0:
             return 0
         start = self.manager.append(req.id, n)
         assert start == req.num_computed
-        plan.entries.append(PlannedEntry(req, ids[start:start + n], start, sample=(start + n == len(ids))))
+        plan.entries.append(PlannedEntry(req, req.ids_slice(start, start + n), start, sample=(start + n == total)))
         return n
 
     def schedule(self) -> StepPlan:
@@ -132,13 +133,15 @@ class Scheduler:
             for req in list(self.running):
                 if req not in self.running or not req.output or req.num_computed != req.num_tokens - 1:
                     continue
-                while not self.manager.fits(req.id, 1):
+                fits = self.manager.fits(req.id, 1)
+                while not fits:
                     victim = self.running[-1]
                     if victim is req:
                         break
                     self._undo_entry(victim, plan)
                     self._preempt(victim, plan)
-                if not self.manager.fits(req.id, 1):
+                    fits = self.manager.fits(req.id, 1)
+                if not fits:
                     # alone and still no page: the request does not fit the pool
                     if len(self.running) == 1:
                         self._fail(req, plan, KVCapacityError('Active KV exhausted the GPU pool'))   # rollout/engine.py:336-338
@@ -148,7 +151,7 @@ class Scheduler:
                     continue
                 if budget <= 0:
                     continue
-                budget -= self._portion(req, 1, plan)
+                budget -= self._portion(req, 1, plan, fits_budget=True)
             # 2. portions of prompts of running requests, then of newly admitted ones
             planned = {id(e.request) for e in plan.entries}
             for req in self.running:

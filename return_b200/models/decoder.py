@@ -22,6 +22,7 @@ class DecoderModel:
     def __init__(self, spec: DecoderSpec, env: BuildEnv):
         spec.validate()
         self.spec = spec
+        self._graph_safe = None
         self.env = env
         self.blocks = [BLOCKS.build(b, env) for b in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, env)
@@ -51,7 +52,9 @@ class DecoderModel:
 
     @property
     def graph_safe(self) -> bool:
-        return all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        if self._graph_safe is None:          # the parts do not change after the model is built
+            self._graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
+        return self._graph_safe
 
     # ------------------------------------------------------------------ caches
     def cache_needs(self) -> List[object]:
