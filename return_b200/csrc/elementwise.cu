@@ -270,27 +270,40 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
     }
 }
 
-// bfloat16 with I a multiple of 8: eight elements (16 bytes) per thread and iteration.
+// bfloat16 with I a multiple of 8: eight elements (16 bytes) per thread, two such pieces in flight.
+// The exponential and the division are the fast float32 forms (a few units in the last place, far
+// below the rounding to bfloat16 that follows): with the accurate ones the kernel is bound by
+// instruction issue, not by memory.
+__device__ __forceinline__ uint4 swiglu8(const uint4 gv, const uint4 uv) {
+    const bf16* g = (const bf16*)&gv;
+    const bf16* u = (const bf16*)&uv;
+    uint4 ov;
+    bf16* o = (bf16*)&ov;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float gf = __bfloat162float(g[k]);
+        o[k] = __float2bfloat16_rn(__fdividef(gf, 1.0f + __expf(-gf)) * __bfloat162float(u[k]));
+    }
+    return ov;
+}
+
 __global__ void swiglu_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int T, int I, int block) {
     pdl_launch_dependents();
     pdl_wait();
     const int I8 = I >> 3;
     const size_t total = (size_t)T * I8;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-         idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += 2 * stride) {
+        const size_t idx2 = idx + stride;
+        const bool two = idx2 < total;
         const size_t t = idx / I8, i = (idx - t * I8) << 3;
+        const size_t t2 = two ? idx2 / I8 : t, i2 = two ? (idx2 - t2 * I8) << 3 : i;
         const uint4 gv = *(const uint4*)(gu + t * 2 * I + (block ? 2 * i : i));
         const uint4 uv = *(const uint4*)(gu + t * 2 * I + (block ? 2 * i + 8 : I + i));
-        const bf16* g = (const bf16*)&gv;
-        const bf16* u = (const bf16*)&uv;
-        uint4 ov;
-        bf16* o = (bf16*)&ov;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float gf = __bfloat162float(g[k]);
-            o[k] = __float2bfloat16_rn(gf / (1.0f + expf(-gf)) * __bfloat162float(u[k]));
-        }
-        *(uint4*)(out + t * I + i) = ov;
+        const uint4 gv2 = *(const uint4*)(gu + t2 * 2 * I + (block ? 2 * i2 : i2));
+        const uint4 uv2 = *(const uint4*)(gu + t2 * 2 * I + (block ? 2 * i2 + 8 : I + i2));
+        *(uint4*)(out + t * I + i) = swiglu8(gv, uv);
+        if (two) *(uint4*)(out + t2 * I + i2) = swiglu8(gv2, uv2);
     }
 }
 

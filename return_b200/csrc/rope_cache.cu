@@ -31,11 +31,13 @@ template <> struct Pair<bf16> {
     }
 };
 
-// One warp per (token, head).  A lane holds the element pairs (i, i+1) of the first rotary half and
-// their partners (i + R/2, i + R/2 + 1) in registers, so a head is read once; head sizes up to 256.
+// One warp per token and HPW neighbouring heads; a lane holds the element pairs (i, i+1) of the first
+// rotary half and their partners (i + R/2, i + R/2 + 1) in registers, so a head is read once; head sizes
+// up to 256.  The loads of all of a warp's heads go out before the first is used: a head is only 256
+// to 512 bytes, and with one head a warp the kernel sat on memory latency at a quarter of the bandwidth.
 constexpr int ROPE_MAX_J = 2;                     // pairs of pairs per lane: R/2 <= 128
 
-template <typename TA>
+template <typename TA, int HPW>
 __global__ void qk_norm_rope_write_kernel(
         TA* __restrict__ qkv, int ld,
         const void* __restrict__ qw, const void* __restrict__ kw, int w_dtype, float eps, float offset,
@@ -48,71 +50,111 @@ __global__ void qk_norm_rope_write_kernel(
     pdl_wait();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
-    const int hh = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);      // one warp per head
+    const int hh0 = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HPW;      // this warp's first head
     const int n_heads = write_kv ? Hq + 2 * Hkv : Hq + Hkv;   // without a write, k is normed and rotated in place
-    if (hh >= n_heads) return;
+    if (hh0 >= n_heads) return;
     const int p = pos[t];
     const int half = rot_dim >> 1;
     long long slot_base = -1;     // element offset of (page, kv head 0, row) in a pool
-    if (write_kv && hh >= Hq) {
+    if (write_kv && hh0 + HPW > Hq) {
         const int page = block_table[(size_t)tok_seg[t] * bt_stride + p / page_size];
         if (page >= 0) slot_base = ((long long)page * Hkv * page_size + (p % page_size)) * D;
     }
-    TA* x = qkv + (size_t)t * ld + (size_t)hh * D;
-    if (hh >= Hq + Hkv) {                           // v head: copy
-        if (slot_base < 0) return;
-        TA* dst = vpool + slot_base + (long long)(hh - Hq - Hkv) * page_size * D;
-        for (int i = 2 * lane; i < D; i += 64) Pair<TA>::store(dst + i, Pair<TA>::load(x + i));
-        return;
-    }
-    const bool is_k = hh >= Hq;
-    const void* w = is_k ? kw : qw;
-    TA* dst = x;
-    if (is_k && write_kv) {
-        if (slot_base < 0) return;
-        dst = kpool + slot_base + (long long)(hh - Hq) * page_size * D;
-    }
-    float2 a[ROPE_MAX_J], b[ROPE_MAX_J];            // first-half pairs and their second-half partners
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < ROPE_MAX_J; ++j) {
-        const int i = 2 * lane + 64 * j;
-        if (i < half) {
-            a[j] = Pair<TA>::load(x + i);
-            b[j] = Pair<TA>::load(x + i + half);
-            ss += a[j].x * a[j].x + a[j].y * a[j].y + b[j].x * b[j].x + b[j].y * b[j].y;
-        }
-    }
-    for (int i = rot_dim + 2 * lane; i < D; i += 64) {        // dims beyond the rotary width
-        const float2 v = Pair<TA>::load(x + i);
-        ss += v.x * v.x + v.y * v.y;
-    }
-    float rstd = 1.f;
-    if (w) {
-        ss = warp_sum(ss);
-        rstd = 1.0f / sqrtf(ss / (float)D + eps);
-    }
+    TA* row = qkv + (size_t)t * ld;
+    // ---- every load first
+    float2 a[HPW][ROPE_MAX_J], b[HPW][ROPE_MAX_J];            // first-half pairs and their second-half partners
+    float2 c[ROPE_MAX_J], sn[ROPE_MAX_J];
     const float* cs = cos_t + (size_t)p * half;
-    const float* sn = sin_t + (size_t)p * half;
+    const float* ss_t = sin_t + (size_t)p * half;
 #pragma unroll
     for (int j = 0; j < ROPE_MAX_J; ++j) {
         const int i = 2 * lane + 64 * j;
         if (i < half) {
-            float2 x1 = make_float2(a[j].x * rstd, a[j].y * rstd), x2 = make_float2(b[j].x * rstd, b[j].y * rstd);
-            if (w) {
-                x1.x *= offset + load_as_f32(w, w_dtype, i);        x1.y *= offset + load_as_f32(w, w_dtype, i + 1);
-                x2.x *= offset + load_as_f32(w, w_dtype, i + half); x2.y *= offset + load_as_f32(w, w_dtype, i + half + 1);
-            }
-            const float2 c = *reinterpret_cast<const float2*>(cs + i), s = *reinterpret_cast<const float2*>(sn + i);
-            Pair<TA>::store(dst + i, make_float2(x1.x * c.x - x2.x * s.x, x1.y * c.y - x2.y * s.y));
-            Pair<TA>::store(dst + i + half, make_float2(x2.x * c.x + x1.x * s.x, x2.y * c.y + x1.y * s.y));
+            c[j] = *reinterpret_cast<const float2*>(cs + i);
+            sn[j] = *reinterpret_cast<const float2*>(ss_t + i);
         }
     }
-    for (int i = rot_dim + 2 * lane; i < D; i += 64) {
-        float2 v = Pair<TA>::load(x + i);
-        v.x *= rstd; v.y *= rstd;
-        if (w) { v.x *= offset + load_as_f32(w, w_dtype, i); v.y *= offset + load_as_f32(w, w_dtype, i + 1); }
-        Pair<TA>::store(dst + i, v);
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        const int hh = hh0 + u;
+        if (hh >= n_heads) break;
+        const TA* x = row + (size_t)hh * D;
+        if (hh >= Hq + Hkv) {                       // v head: its two pairs ride in a[u][*]
+#pragma unroll
+            for (int j = 0; j < ROPE_MAX_J; ++j) {
+                const int i = 2 * lane + 64 * j;
+                if (i < D) a[u][j] = Pair<TA>::load(x + i);
+                if (i + 128 < D) b[u][j] = Pair<TA>::load(x + i + 128);
+            }
+            continue;
+        }
+#pragma unroll
+        for (int j = 0; j < ROPE_MAX_J; ++j) {
+            const int i = 2 * lane + 64 * j;
+            if (i < half) {
+                a[u][j] = Pair<TA>::load(x + i);
+                b[u][j] = Pair<TA>::load(x + i + half);
+            }
+        }
+    }
+    // ---- then head by head
+#pragma unroll
+    for (int u = 0; u < HPW; ++u) {
+        const int hh = hh0 + u;
+        if (hh >= n_heads) break;
+        TA* x = row + (size_t)hh * D;
+        if (hh >= Hq + Hkv) {                       // v head: copy
+            if (slot_base < 0) continue;
+            TA* dst = vpool + slot_base + (long long)(hh - Hq - Hkv) * page_size * D;
+#pragma unroll
+            for (int j = 0; j < ROPE_MAX_J; ++j) {
+                const int i = 2 * lane + 64 * j;
+                if (i < D) Pair<TA>::store(dst + i, a[u][j]);
+                if (i + 128 < D) Pair<TA>::store(dst + i + 128, b[u][j]);
+            }
+            continue;
+        }
+        const bool is_k = hh >= Hq;
+        const void* w = is_k ? kw : qw;
+        TA* dst = x;
+        if (is_k && write_kv) {
+            if (slot_base < 0) continue;
+            dst = kpool + slot_base + (long long)(hh - Hq) * page_size * D;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < ROPE_MAX_J; ++j) {
+            const int i = 2 * lane + 64 * j;
+            if (i < half) ss += a[u][j].x * a[u][j].x + a[u][j].y * a[u][j].y + b[u][j].x * b[u][j].x + b[u][j].y * b[u][j].y;
+        }
+        for (int i = rot_dim + 2 * lane; i < D; i += 64) {        // dims beyond the rotary width
+            const float2 v = Pair<TA>::load(x + i);
+            ss += v.x * v.x + v.y * v.y;
+        }
+        float rstd = 1.f;
+        if (w) {
+            ss = warp_sum(ss);
+            rstd = 1.0f / sqrtf(ss / (float)D + eps);
+        }
+#pragma unroll
+        for (int j = 0; j < ROPE_MAX_J; ++j) {
+            const int i = 2 * lane + 64 * j;
+            if (i < half) {
+                float2 x1 = make_float2(a[u][j].x * rstd, a[u][j].y * rstd), x2 = make_float2(b[u][j].x * rstd, b[u][j].y * rstd);
+                if (w) {
+                    x1.x *= offset + load_as_f32(w, w_dtype, i);        x1.y *= offset + load_as_f32(w, w_dtype, i + 1);
+                    x2.x *= offset + load_as_f32(w, w_dtype, i + half); x2.y *= offset + load_as_f32(w, w_dtype, i + half + 1);
+                }
+                Pair<TA>::store(dst + i, make_float2(x1.x * c[j].x - x2.x * sn[j].x, x1.y * c[j].y - x2.y * sn[j].y));
+                Pair<TA>::store(dst + i + half, make_float2(x2.x * c[j].x + x1.x * sn[j].x, x2.y * c[j].y + x1.y * sn[j].y));
+            }
+        }
+        for (int i = rot_dim + 2 * lane; i < D; i += 64) {
+            float2 v = Pair<TA>::load(x + i);
+            v.x *= rstd; v.y *= rstd;
+            if (w) { v.x *= offset + load_as_f32(w, w_dtype, i); v.y *= offset + load_as_f32(w, w_dtype, i + 1); }
+            Pair<TA>::store(dst + i, v);
+        }
     }
 }
 
@@ -127,12 +169,25 @@ RB_EXPORT int rb_qk_norm_rope_write(
     if (rot_dim > D || (rot_dim & 3) || (D & 1) || rot_dim > 128 * ROPE_MAX_J) return (int)cudaErrorInvalidValue;
     const int threads = 128;
     const int heads = write_kv ? Hq + 2 * Hkv : Hq + Hkv;
+    // many tokens: four heads a warp, so that enough bytes are in flight; few tokens: one head a warp, so that
+    // the few warps there are spread over the SMs
+    if ((long long)T * heads >= 8192) {
+        constexpr int HPW = 4;
+        const dim3 grid(T, (heads + 4 * HPW - 1) / (4 * HPW));
+        if (act_dtype == RB_F32)
+            return rb_launch_pdl(qk_norm_rope_write_kernel<float, HPW>, grid, dim3(threads), 0, st,
+                (float*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
+                block_table, bt_stride, page_size, (float*)kpool, (float*)vpool, Hq, Hkv, D, write_kv);
+        return rb_launch_pdl(qk_norm_rope_write_kernel<bf16, HPW>, grid, dim3(threads), 0, st,
+                (bf16*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
+                block_table, bt_stride, page_size, (bf16*)kpool, (bf16*)vpool, Hq, Hkv, D, write_kv);
+    }
     const dim3 grid(T, (heads + 3) / 4);
     if (act_dtype == RB_F32)
-        return rb_launch_pdl(qk_norm_rope_write_kernel<float>, grid, dim3(threads), 0, st,
+        return rb_launch_pdl(qk_norm_rope_write_kernel<float, 1>, grid, dim3(threads), 0, st,
             (float*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
             block_table, bt_stride, page_size, (float*)kpool, (float*)vpool, Hq, Hkv, D, write_kv);
-    return rb_launch_pdl(qk_norm_rope_write_kernel<bf16>, grid, dim3(threads), 0, st,
+    return rb_launch_pdl(qk_norm_rope_write_kernel<bf16, 1>, grid, dim3(threads), 0, st,
             (bf16*)qkv, ld, qw, kw, w_dtype, eps, offset, cos_t, sin_t, rot_dim, pos, tok_seg,
             block_table, bt_stride, page_size, (bf16*)kpool, (bf16*)vpool, Hq, Hkv, D, write_kv);
 }

@@ -420,10 +420,11 @@ def test_one_far_key_among_hundreds_and_the_windows_edge(dtype):
 @pytest.mark.parametrize("Hq,Hkv,D,P,rot", [(4, 2, 16, 16, 16), (6, 3, 32, 8, 32), (5, 1, 48, 16, 48), (3, 1, 80, 4, 32),
                                              (32, 8, 128, 16, 128)])
 @pytest.mark.parametrize("with_norm", [True, False])
-def test_qk_norm_rope_write(dtype, Hq, Hkv, D, P, rot, with_norm):
+@pytest.mark.parametrize("long_first", [20, 1200])      # many tokens take the form with four heads a warp
+def test_qk_norm_rope_write(dtype, Hq, Hkv, D, P, rot, with_norm, long_first):
     ops = _ops()
     g = torch.Generator().manual_seed(D)
-    starts, lens = [0, 37, 5], [20, 1, 9]
+    starts, lens = [0, 37, 5], [long_first, 1, 9]
     T = sum(lens)
     qkv = torch.randn(T, (Hq + 2 * Hkv) * D, generator=g).to(dtype)
     qw = (1 + 0.1 * torch.randn(D, generator=g)) if with_norm else None
@@ -431,7 +432,7 @@ def test_qk_norm_rope_write(dtype, Hq, Hkv, D, P, rot, with_norm):
     eps, theta = 2e-5, 5000.0
     half = rot // 2
     inv = 1.0 / (theta ** (torch.arange(0, half, dtype=torch.float32) / half))
-    ang = torch.outer(torch.arange(64, dtype=torch.float32), inv)
+    ang = torch.outer(torch.arange(max(64, long_first + 8), dtype=torch.float32), inv)
     cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
     pos = torch.tensor([s + i for s, L in zip(starts, lens) for i in range(L)], dtype=torch.int32)
     tok_seg = torch.tensor([i for i, L in enumerate(lens) for _ in range(L)], dtype=torch.int32)
