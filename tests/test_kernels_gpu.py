@@ -414,6 +414,75 @@ def test_one_far_key_among_hundreds_and_the_windows_edge(dtype):
                 assert close == last_row_sees
 
 
+def _attention_all_kernels(ops, pg, Hq, Hkv, D, P, scale, window, dtype):
+    """The outputs of every attention kernel that takes this case: name -> [T, Hq*D] float32 on the CPU."""
+    T = sum(pg.q_lens)
+    outs = {}
+    o = torch.empty(T, Hq * D, device=DEV, dtype=dtype)
+    ops.attention_simt(pg.qkv, pg.kpool, pg.vpool, pg.pos, pg.tok_seg, pg.bt, P, o, Hq, Hkv, D, scale, window or 0)
+    outs["simt"] = o.float().cpu()
+    if dtype != torch.bfloat16:
+        return outs
+    if all(q == 1 for q in pg.q_lens):
+        segs = torch.arange(pg.n, dtype=torch.int32, device=DEV)
+        for splits in (1, 4):
+            o = torch.full((T, Hq * D), float("nan"), device=DEV, dtype=dtype)
+            ops.attention_decode_mma(pg.qkv, pg.kpool, pg.vpool, segs, pg.cu_q, pg.seg_kv_len, pg.bt, P, o, Hq, Hkv, D, scale,
+                                     window or 0, num_splits=splits)
+            outs[f"decode_mma/{splits}"] = o.float().cpu()
+    else:
+        tiles = torch.tensor([(i, r0) for i, ql in enumerate(pg.q_lens) for r0 in range(0, ql, 64)], dtype=torch.int32, device=DEV)
+        o = torch.full((T, Hq * D), float("nan"), device=DEV, dtype=dtype)
+        ops.attention_prefill_mma(pg.qkv, pg.kpool, pg.vpool, tiles, pg.cu_q, pg.seg_pos0, pg.bt, P, o, Hq, Hkv, D, scale, window or 0)
+        outs["prefill_mma"] = o.float().cpu()
+        if D in ops.TC5_ATTENTION_HEAD_DIMS:
+            tiles = torch.tensor([(i, r0) for i, ql in enumerate(pg.q_lens) for r0 in range(0, ql, ops.TC5_TILE_ROWS)],
+                                 dtype=torch.int32, device=DEV)
+            o = torch.full((T, Hq * D), float("nan"), device=DEV, dtype=dtype)
+            ops.attention_prefill_tc5(pg.qkv, pg.kpool, pg.vpool, tiles, pg.cu_q, pg.seg_pos0, pg.bt, P, o, Hq, Hkv, D, scale, window or 0)
+            torch.cuda.synchronize()
+            st = ops.tc5_status(torch.device(DEV))
+            assert int(st.item()) == 0
+            outs["prefill_tc5"] = o.float().cpu()
+    return outs
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("q_len", [1, 200])
+@pytest.mark.parametrize("D,P", [(64, 16), (128, 8)])
+def test_one_far_key_stands_out_and_the_windows_edge_is_exact(dtype, q_len, D, P):
+    """Random keys hide a lost tile or an edge that is off by one.  Here one key far back is made to
+    dominate the last query (no window), and with a window the key just inside it dominates while the
+    key just outside it, made as strong, must leave no trace."""
+    ops = _ops()
+    Hq, Hkv, L = 4, 2, 700
+    scale = 1.0 / math.sqrt(D)
+    for window, strong, silent in ((None, 5, None), (37, L - 37, L - 38)):
+        pg = Paged([L], [q_len], Hq, Hkv, D, P, dtype, seed=3, poison=False)
+        last = q_len - 1                                   # the last query: position L - 1
+
+        def put_key(j, vec):
+            page, off = int(pg.bt[0, j // P]), j % P
+            pg.k[0][j] = vec
+            pg.kpool[page, :, off] = vec.to(dtype).to(DEV)
+
+        direction = torch.randn(D, generator=torch.Generator().manual_seed(9))
+        direction = direction / direction.norm() * 12.0
+        put_key(strong, direction.expand(Hkv, D).clone())
+        if silent is not None:
+            put_key(silent, (1.5 * direction).expand(Hkv, D).clone())      # stronger still, but outside the window
+        pg.q[0][last] = direction.expand(Hq, D) * 1.2
+        pg.qkv[last, :Hq * D] = pg.q[0][last].reshape(-1).to(dtype).to(DEV)
+        ref = pg.reference(scale, window)
+        want_v = pg.v[0][strong].to(dtype).float()                          # [Hkv, D]
+        for name, got in _attention_all_kernels(ops, pg, Hq, Hkv, D, P, scale, window, dtype).items():
+            tol = dict(atol=2e-4, rtol=2e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+            assert torch.allclose(got, ref, **tol), (name, window)
+            row = got[last].reshape(Hq, D)
+            for h in range(Hq):                                             # the output is the strong key's value, almost alone
+                assert torch.allclose(row[h], want_v[h // (Hq // Hkv)], atol=6e-2, rtol=6e-2), (name, window, h)
+
+
 # ------------------------------------------------------------------------------- rope + cache write
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
