@@ -150,13 +150,11 @@ def main():
         engine.add_request(r)
     while any(len(r.output) < 1 for r in reqs):        # prompts, in portions under the token budget
         engine.step()
-    for _ in range(W):                                   # warm-up decode steps (captures the graph)
-        engine.step()
+    engine.run(max_steps=W)                              # warm-up decode steps (captures the graph)
     torch.cuda.synchronize()
     before = sum(len(r.output) for r in reqs)
     t1 = time.perf_counter()
-    for _ in range(K):                                   # every step: tables in from pinned memory, tokens out
-        engine.step()
+    engine.run(max_steps=K)                              # every step: tables in from pinned memory, tokens out to the host
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t1
     e2e_tokens = sum(len(r.output) for r in reqs) - before

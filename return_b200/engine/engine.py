@@ -89,6 +89,90 @@ class Engine:
         self._steps += 1
         return ended
 
+    # ------------------------------------------------------------------ decode steps that run ahead of the host
+    def _can_run_ahead(self) -> bool:
+        """Every running request is decoding, none waits for a slot that is free, and decode steps go
+        through captured graphs: the next step can then start before the host has read the last
+        step's tokens, because its tokens can come straight from the sampler's device buffer."""
+        sch = self.scheduler
+        if not sch.running or not self.runner.runs_ahead():
+            return False
+        if sch.waiting and self.runner.manager.free_slots > 0:
+            return False
+        return all(r.output and r.num_computed == r.num_tokens - 1 for r in sch.running)
+
+    def _decode_ahead(self, max_steps: Optional[int] = None) -> List[Request]:
+        """Consecutive steps of one decoded token per running request, each launched while the step
+        before it still runs: the host reads step k's tokens (and sees which requests ended) while
+        step k + 1 is on the GPU.  A request that ends on a stop sequence has then run one token too
+        many, which is dropped; ends by length are known beforehand and cost nothing.  Returns the
+        requests that ended; stops at the first end, when pages run short (the ordinary step then
+        decides who gives way), or after ``max_steps`` steps."""
+        from .batch import StepEntry
+        sch, mgr = self.scheduler, self.runner.manager
+        reqs = list(sch.running)
+        n = len(reqs)
+        t0 = time.perf_counter()
+        # steps until the first request ends by length: known now, never overrun
+        room = min(min(r.max_new_tokens - len(r.output), sch.max_model_len - r.num_tokens) for r in reqs)
+        limit = room if max_steps is None else min(room, max_steps)
+        launched = committed = 0
+        tokens_dev = None
+        ended: List[Request] = []
+        stop = False
+        while True:
+            can_launch = (not stop and launched < limit and launched - committed < Sampler.SLOTS
+                          and all(mgr.fits(r.id, 1) for r in reqs))
+            if can_launch:
+                entries = []
+                for r in reqs:
+                    tok = r.output[-1] if launched == committed else 0          # 0: replaced on the device
+                    entries.append(StepEntry(r.id, [tok], [0], mgr.append(r.id, 1)))
+                logits = self.runner.step(entries, tokens_dev if launched > committed else None)
+                params = [(r.temperature, r.top_k, r.top_p, uniform_draw(r.seed, len(r.output) + launched - committed))
+                          for r in reqs]
+                tokens_dev = self.sampler.launch(logits, params, launched % Sampler.SLOTS)
+                launched += 1
+                continue
+            if committed == launched:
+                break
+            toks, lps = self.sampler.fetch(committed % Sampler.SLOTS)
+            committed += 1
+            for r, t, lp in zip(reqs, toks, lps):
+                if r.finish_reason is not None:
+                    continue                                  # ended a step ago: this token is one too many
+                r.num_computed += 1
+                r.push(t, lp)
+                if r.finished or r.num_tokens >= sch.max_model_len:
+                    r.finish_reason = r.reason() if r.finished else "length"
+                    ended.append(r)
+                    stop = True
+            self._steps += 1
+            self._dc_tok += n
+        for r in ended:
+            mgr.free(r.id)
+            sch.running.remove(r)
+        self._acc_decode += time.perf_counter() - t0
+        return ended
+
+    def run(self, max_steps: Optional[int] = None) -> List[Request]:
+        """Runs model steps until no request is left or ``max_steps`` steps have run; returns the requests
+        that ended.  Decode steps run ahead of the host where they can (see ``_decode_ahead``)."""
+        ended: List[Request] = []
+        left = max_steps
+        while self.has_unfinished() and (left is None or left > 0):
+            if self._can_run_ahead():
+                before = self._steps
+                ended += self._decode_ahead(left)
+                if left is not None:
+                    left -= self._steps - before
+                if self._steps > before:
+                    continue
+            ended += self.step()                              # also where pages run short and someone gives way
+            if left is not None:
+                left -= 1
+        return ended
+
     # ------------------------------------------------------------------ whole generations
     def generate(self, prompts: Sequence[Union[Request, Sequence[int]]], max_new_tokens: int = 32,
                  temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0,
@@ -108,7 +192,7 @@ class Engine:
             self.add_request(r)
             reqs.append(r)
         while self.has_unfinished():
-            for r in self.step():
+            for r in self.run():
                 if r.finish_reason == "error" and r in reqs:
                     raise r.error
         return [GenerationResult(r.id, list(r.output), list(r.output_logprobs), len(r.output), r.finish_reason)

@@ -102,17 +102,27 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs the entries as one batch; float32 logits [wanted places, vocab], in entry order."""
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs the entries as one batch; float32 logits [wanted places, vocab], in entry order.
+
+        ``device_tokens`` (int32 [n], a step of single decoded tokens through a captured graph only): the
+        tokens are taken from this device tensor, in stream order, instead of from the entries; this is
+        how a step starts before the host has seen the tokens the step before it sampled."""
         host = build_host_batch(entries, self.manager, self.vocab_size, self.max_positions)
         with torch.cuda.device(self.env.device):
             if self.config.use_cuda_graph and host.num_tokens == host.num_segments and self.model.graph_safe:
-                return self._graphed_decode(host)
+                return self._graphed_decode(host, device_tokens)
+            if device_tokens is not None:
+                raise ValueError("tokens on the device are taken by captured decode steps only")
             batch = StepBatch(host, self.env.device, self.staging)
             return self.model.forward(batch, self.storage)
 
     # ------------------------------------------------------------------ CUDA graphs for decode steps
-    def _graphed_decode(self, host) -> torch.Tensor:
+    def runs_ahead(self) -> bool:
+        """Whether decode steps go through captured graphs, which can take their tokens from the device."""
+        return bool(self.config.use_cuda_graph and self.model.graph_safe)
+
+    def _graphed_decode(self, host, device_tokens=None) -> torch.Tensor:
         """A step of single decoded tokens replays a graph captured for its batch size, as the
         reference does (rollout/model.py:346-407); graphs are captured on first use.  A captured
         launch cannot change its grid, so there is one graph per batch size and per span of context
@@ -125,6 +135,8 @@ class ModelRunner:
             entry = self._capture(n, span)
         graph, static, logits = entry
         static.fill(host)
+        if device_tokens is not None:
+            static.tokens.copy_(device_tokens[:n], non_blocking=True)     # after the upload, in stream order
         graph.replay()
         if host.num_want == n and (host.want_rows == range(n)).all():
             return logits

@@ -150,3 +150,56 @@ def test_command_line(tmp_path):
     assert p.returncode == 0, p.stderr[-2000:]
     out = json.loads(p.stdout.strip().splitlines()[-1])
     assert out["output_ids"] == _plain_greedy(model, [prompt], 5)[0] and out["finish_reason"] == "length"
+
+
+def test_decode_that_runs_ahead_of_the_host_gives_the_same_tokens(tmp_path):
+    """With captured graphs the engine launches decode step k + 1 before it has read step k's tokens.
+    Requests that end at different times (by length, by a stop sequence seen one step late) and sampled
+    tokens must come out as they do step by step."""
+    from return_b200.engine.request import Request
+    d = helpers.make_model_dir(tmp_path, "B")
+    prompts = [helpers.random_ids(384, n, 21 + i) for i, n in enumerate((9, 40, 71, 5))]
+    free = _plain_greedy(d, [prompts[1]], 14)[0]
+
+    def requests():
+        return [Request("a", prompts[0], max_new_tokens=5, temperature=0.7, top_p=0.9, seed=11),
+                Request("b", prompts[1], max_new_tokens=14, temperature=0.0, stop_ids=[free[6:8]]),
+                Request("c", prompts[2], max_new_tokens=9, temperature=1.3, top_k=20, seed=5),
+                Request("d", prompts[3], max_new_tokens=20, temperature=0.0)]
+
+    step_wise = _engine(d, page_size=8, use_cuda_graph=False).generate(requests())
+    eng = _engine(d, page_size=8, use_cuda_graph=True)
+    ahead = eng.generate(requests())
+    assert [r.output_ids for r in ahead] == [r.output_ids for r in step_wise]
+    assert [r.finish_reason for r in ahead] == ["length", "stop", "length", "length"]
+    stop = free[6:8]
+    first = next(i for i in range(1, 14) if free[i - 1:i + 1] == stop)     # greedy output may repeat itself
+    assert ahead[1].output_ids == free[:first + 1]
+    assert all(abs(x - y) < 1e-5 for r, s in zip(ahead, step_wise) for x, y in zip(r.output_logprobs, s.output_logprobs))
+    assert eng.runner.manager.pages_used() == [0] * len(eng.runner.manager.groups)
+    assert eng.runner.manager.free_slots == 4
+
+    # run(max_steps) runs exactly that many steps
+    eng = _engine(d, page_size=8, use_cuda_graph=True)
+    reqs = [Request(f"r{i}", p, max_new_tokens=30, temperature=0.0) for i, p in enumerate(prompts)]
+    for r in reqs:
+        eng.add_request(r)
+    while any(not r.output for r in reqs):
+        eng.step()
+    have, steps = [len(r.output) for r in reqs], eng.stats()["steps"]
+    eng.run(max_steps=7)
+    assert [len(r.output) for r in reqs] == [h + 7 for h in have] and eng.stats()["steps"] == steps + 7
+    want = _plain_greedy(d, prompts, 10)
+    assert [r.output[:8] for r in reqs] == [w[:8] for w in want]
+
+
+def test_running_ahead_gives_way_when_pages_run_short(tmp_path):
+    """A pool too small for all: the loop that runs ahead stops, the ordinary step preempts, and the
+    tokens are still those of plain greedy decoding."""
+    d = helpers.make_model_dir(tmp_path, "B")
+    prompts = [helpers.random_ids(384, n, 31 + i) for i, n in enumerate((30, 28, 33))]
+    want = _plain_greedy(d, prompts, 24)
+    eng = _engine(d, max_token=136, page_size=8, use_cuda_graph=True, max_model_len=128)
+    got = eng.generate(prompts, max_new_tokens=24, temperature=0.0)
+    assert [r.output_ids for r in got] == want
+    assert eng.stats()["preemptions"] > 0
