@@ -162,16 +162,19 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                               _stream()), "gemm_f32")
 
 
-SKINNY_MAX_ROWS = 32
+SKINNY_KERNEL_MAX_ROWS = 32     # what the kernel takes
+SKINNY_MAX_ROWS = 8             # what the engine gives it: beyond 8 rows the library is faster (38 us against 58 at
+                                # 16 rows and 106 at 32, for N = 24576, K = 4096)
 
 
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
-    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 32 in bfloat16: the weight-streaming kernel of decode steps.
+    """out[M, N] = x[M, K] @ w[N, K]^T for M <= 32 in bfloat16: the weight-streaming kernel of decode steps
+    (the engine uses it up to 8 rows).
     ``gated``: w holds gate and up rows interleaved in blocks of 8; out[M, N/2] = silu(gate) * up."""
     M, K = x.shape
     N = w.shape[0]
     assert x.dtype == w.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32)
-    assert w.shape[1] == K and out.shape == (M, N // 2 if gated else N) and M <= SKINNY_MAX_ROWS
+    assert w.shape[1] == K and out.shape == (M, N // 2 if gated else N) and M <= SKINNY_KERNEL_MAX_ROWS
     assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
     _check(core().rb_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
                                  1 if gated else 0, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()),
@@ -299,7 +302,7 @@ def gemm_tc5_bmn(x: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int = 
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out = x @ w^T.  float32: the engine's own FFMA kernel.  bfloat16 with up to 32 rows: the
+    """out = x @ w^T.  float32: the engine's own FFMA kernel.  bfloat16 with up to 8 rows: the
     engine's weight-streaming kernel.  bfloat16 with more rows: cuBLAS with float32 accumulation.
     The output is bfloat16 or float32 (``out``'s dtype)."""
     if x.dtype == torch.float32:
