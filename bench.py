@@ -20,7 +20,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Qwen3-8B shape
+# the layer sizes of Qwen3-8B, the benchmark's named configuration
 MODEL = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
              num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0,
              rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960)

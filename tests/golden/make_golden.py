@@ -25,7 +25,9 @@ os.environ["TRITON_INTERPRET"] = "1"
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py PATH_TO_THE_REFERENCE_CHECKOUT")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 
 import torch
