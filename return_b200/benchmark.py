@@ -264,3 +264,31 @@ def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[st
     ms = _time_kernels(fns, iters, warmup)
     return {"kernel": ("gated_linear", "gemm_tc5_gated", "cublas+swiglu")[impl], "M": M, "I": I, "K": K, "ms": ms,
             "TFLOPs": 4.0 * M * I * K / ms / 1e9}
+
+
+def probe_tc5_rate(iters=2000) -> Dict[str, object]:
+    """Cycles per ``tcgen05.mma`` (M x N x 16, bf16, operands in shared memory) for one and two issuing
+    threads of a CTA, on every SM."""
+    import ctypes
+    from .ext import build
+    lib = build.load("return_probes", ["probes.cu"])
+    lib.rb_probe_tc5_rate.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 2
+    lib.rb_probe_tc5_rate.restype = ctypes.c_int
+    dev = torch.device("cuda:0")
+    cyc = torch.zeros(8, dtype=torch.int64, device=dev)
+    rows = []
+    for M in (128, 64):
+        for N in (16, 64, 128, 256):
+            row = {"M": M, "N": N}
+            for threads in (1, 2):
+                if threads * N > 512:
+                    continue
+                rc = lib.rb_probe_tc5_rate(148, M, N, iters, threads, ctypes.c_void_p(cyc.data_ptr()),
+                                           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                assert rc == 0
+                torch.cuda.synchronize()
+                per = float(cyc[1].item()) / iters
+                row[f"cycles_per_mma_{threads}thread"] = round(per, 1)
+                row[f"tflops_{threads}thread"] = round(threads * 2.0 * M * N * 16 / per * 148 * 1.9e9 / 1e12)
+            rows.append(row)
+    return {"probe": "tc5_rate", "rows": rows}

@@ -93,7 +93,8 @@ def cmd_bench(args) -> int:
 def cmd_kernel_bench(args) -> int:
     from . import benchmark
     fn = {"attention_decode": benchmark.kernel_attention_decode, "attention_prefill": benchmark.kernel_attention_prefill,
-          "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated, "mma_rate": benchmark.probe_mma_rate}[args.kernel]
+          "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated, "mma_rate": benchmark.probe_mma_rate,
+          "tc5_rate": benchmark.probe_tc5_rate}[args.kernel]
     kw = {}
     for item in args.set or []:
         k, v = item.split("=")
@@ -153,7 +154,7 @@ def main(argv=None) -> int:
     b.set_defaults(fn=cmd_bench)
 
     k = sub.add_parser("kernel-bench", help="time one kernel alone on random data (for profiles)")
-    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated", "mma_rate"])
+    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated", "mma_rate", "tc5_rate"])
     k.add_argument("--set", action="append", help="an integer argument of the kernel case, e.g. batch=64 ctx=2048 M=8")
     k.set_defaults(fn=cmd_kernel_bench)
 
