@@ -274,7 +274,9 @@ class AsyncEngine:
             if not self.engine.has_unfinished():
                 await self._wake.wait()
                 continue
-            ended = await asyncio.to_thread(self.engine.step)
+            # a few steps at a time, so that decode steps can run ahead of the host and a new request still
+            # waits for eight steps at most before the scheduler sees it
+            ended = await asyncio.to_thread(self.engine.run, 8)
             for r in ended:
                 fut = self._futures.pop(r.id, None)
                 if fut is None or fut.done():
