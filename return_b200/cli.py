@@ -58,7 +58,7 @@ def cmd_generate(args) -> int:
         return 2
     stops = [_ids(s) for s in (args.stop_ids or [])]
     results = engine.generate(prompts, max_new_tokens=args.new, temperature=args.temperature, top_p=args.top_p,
-                              top_k=args.top_k, stop_ids=stops, seed=args.seed)
+                              top_k=args.top_k, stop_ids=stops, seed=args.seed, eos_token_id=args.eos_token_id)
     for r in results:
         print(json.dumps(r.as_dict()))
     print(json.dumps({"stats": engine.stats()}), file=sys.stderr)
@@ -135,6 +135,7 @@ def main(argv=None) -> int:
     g.add_argument("--top-p", type=float, default=1.0)
     g.add_argument("--top-k", type=int, default=0)
     g.add_argument("--stop-ids", action="append", help="a stop sequence of token ids (repeatable)")
+    g.add_argument("--eos-token-id", type=int, default=None, help="a stop sequence of one token")
     g.set_defaults(fn=cmd_generate)
 
     r = sub.add_parser("random-weights", help="write a random model folder")

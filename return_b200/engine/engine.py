@@ -176,10 +176,14 @@ class Engine:
     # ------------------------------------------------------------------ whole generations
     def generate(self, prompts: Sequence[Union[Request, Sequence[int]]], max_new_tokens: int = 32,
                  temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0,
-                 stop_ids: Optional[List[List[int]]] = None, seed: Optional[int] = None) -> List[GenerationResult]:
+                 stop_ids: Optional[List[List[int]]] = None, seed: Optional[int] = None,
+                 eos_token_id: Optional[int] = None) -> List[GenerationResult]:
         """Generates for every prompt (token ids, or ``Request`` records with their own options) and
-        returns the results in the order given.  A request that cannot fit the pool raises
-        ``KVCapacityError``."""
+        returns the results in the order given.  ``eos_token_id`` is a stop sequence of one token.  A
+        request that cannot fit the pool raises ``KVCapacityError``."""
+        stop_ids = list(stop_ids or [])
+        if eos_token_id is not None:
+            stop_ids.append([int(eos_token_id)])
         reqs: List[Request] = []
         for i, p in enumerate(prompts):
             if isinstance(p, Request):

@@ -65,6 +65,9 @@ def test_stop_sequence(tmp_path):
     stop = [free[3:5]]
     got = _engine(d).generate([prompt], max_new_tokens=10, temperature=0.0, stop_ids=stop)[0]
     assert got.output_ids == free[:5] and got.finish_reason == "stop"
+    eos = free[2]                                        # an end-of-sequence id is a stop sequence of one token
+    got = _engine(d).generate([prompt], max_new_tokens=10, temperature=0.0, eos_token_id=eos)[0]
+    assert got.output_ids == free[:free.index(eos) + 1] and got.finish_reason == "stop"
 
 
 def test_sampling_is_reproducible_and_independent_of_the_batch(tmp_path):
