@@ -170,9 +170,10 @@ def kernel_attention_decode(batch=64, ctx=2048, heads=32, kv_heads=8, head_dim=1
 
 
 def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8, head_dim=128, page=16,
-                             iters=10, warmup=3, impl=0) -> Dict[str, float]:
+                             iters=10, warmup=3, impl=0, splits=0) -> Dict[str, float]:
     """The prefill attention kernel alone: device time and causal TFLOP/s.
-    ``impl`` 0: the tcgen05 kernel (head sizes 64 and 128); 1: the mma.sync kernel."""
+    ``impl`` 0: the tcgen05 kernel (head sizes 64 and 128); 1: the mma.sync kernel.
+    ``splits``: ways the tcgen05 kernel splits the keys (0: the engine's choice for this many CTAs)."""
     from .ext import ops
     dev = torch.device("cuda:0")
     qkv, k_pool, v_pool, bt, cu_q, seg_pos0, _ = _paged_case(batch, ctx, q_len, heads, kv_heads, head_dim, page, dev)
@@ -180,12 +181,14 @@ def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8
     rows = 64 if impl else ops.TC5_TILE_ROWS
     tiles = torch.tensor([(i, r) for i in range(batch) for r in range(0, q_len, rows)], dtype=torch.int32, device=dev)
     kernel = ops.attention_prefill_mma if impl else ops.attention_prefill_tc5
+    splits = splits or ops.prefill_splits(int(tiles.shape[0]) * heads, ctx)
+    more = {} if impl else {"num_splits": splits, "held": {}}
     fn = lambda: kernel(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, bt, page, out, heads,
-                        kv_heads, head_dim, head_dim ** -0.5, 0)
+                        kv_heads, head_dim, head_dim ** -0.5, 0, **more)
     ms = _time_kernels([fn], iters, warmup)
     flops = 4.0 * batch * heads * head_dim * (q_len * (ctx - q_len) + q_len * q_len / 2.0)
-    return {"kernel": "attention_prefill_mma" if impl else "attention_prefill_tc5", "batch": batch, "ctx": ctx, "q_len": q_len, "ms": ms,
-            "TFLOPs": flops / ms / 1e9}
+    return {"kernel": "attention_prefill_mma" if impl else "attention_prefill_tc5", "batch": batch, "ctx": ctx, "q_len": q_len, "splits": 1 if impl else splits,
+            "ctas": int(tiles.shape[0]) * heads, "ms": ms, "TFLOPs": flops / ms / 1e9}
 
 
 def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> Dict[str, float]:
@@ -292,3 +295,63 @@ def probe_tc5_rate(iters=2000) -> Dict[str, object]:
                 row[f"tflops_{threads}thread"] = round(threads * 2.0 * M * N * 16 / per * 148 * 1.9e9 / 1e12)
             rows.append(row)
     return {"probe": "tc5_rate", "rows": rows}
+
+
+# ------------------------------------------------------------------------------- named workloads through the engine
+
+WORKLOADS = {
+    # 64 requests with prompt lengths uniform in [16, 4096], prompts in portions of 512 tokens beside decodes
+    "0.6b-mixed": dict(
+        model=dict(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28,
+                   num_attention_heads=16, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0,
+                   rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=40960),
+        seed=5, requests=64, prompt=(16, 4096), new=128, chunk=512, max_reside=64, ctx=8192),
+    # 16 requests with 2,048-token prompts, then 256 decoded tokens each
+    "32b": dict(
+        model=dict(vocab_size=151936, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64,
+                   num_attention_heads=64, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0,
+                   rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960),
+        seed=6, requests=16, prompt=(2048, 2048), new=256, chunk=8192, max_reside=16, ctx=8192),
+}
+
+
+def run_workload(name: str, layers: int = 0, new: int = 0) -> Dict[str, object]:
+    """One of the named workloads through ``Engine.generate`` (scheduler, portions, decode, sampling off: greedy):
+    wall time, tokens per second of the whole job and of its decode steps.  ``layers`` / ``new``: fewer layers or
+    fewer new tokens than the workload names, where time needs it (both are reported)."""
+    import time
+    from .config.model_config import Qwen3Config
+    from .engine.config import EngineConfig
+    from .engine.engine import Engine
+    from .engine.request import Request
+    from .engine.runner import ModelRunner
+    w = WORKLOADS[name]
+    raw = dict(w["model"])
+    full_layers = raw["num_hidden_layers"]
+    if layers:
+        raw["num_hidden_layers"] = layers
+    cfg = Qwen3Config.from_dict(raw)
+    n_new = new or w["new"]
+    gen = torch.Generator().manual_seed(w["seed"])
+    lo, hi = w["prompt"]
+    lens = [int(torch.randint(lo, hi + 1, (1,), generator=gen)) for _ in range(w["requests"])]
+    pool = sum((n + n_new + 63) // 64 * 64 for n in lens) + 1024
+    ecfg = EngineConfig(max_token=pool, max_reside=w["max_reside"], page_size=16, prefill_chunk=w["chunk"], dtype="bfloat16",
+                        max_model_len=w["ctx"], use_cuda_graph=True, seed=w["seed"])
+    runner = ModelRunner.from_random(cfg, ecfg, seed=w["seed"])
+    engine = Engine(runner)
+    reqs = [Request(f"w{i}", _random_ids(cfg.vocab_size, n, gen), max_new_tokens=n_new, temperature=0.0) for i, n in enumerate(lens)]
+    # warm-up: one short request through prefill and a few decode steps (compiles, captures a graph)
+    engine.generate([_random_ids(cfg.vocab_size, 64, gen)], max_new_tokens=4, temperature=0.0)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = engine.generate(reqs)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    st = engine.stats()
+    return {"workload": name, "layers": cfg.num_hidden_layers, "full_layers": full_layers, "requests": len(reqs),
+            "prompt_tokens": sum(lens), "new_tokens": sum(r.num_tokens for r in out), "seconds": round(dt, 3),
+            "tokens_per_s": round((sum(lens) + sum(r.num_tokens for r in out)) / dt, 1),
+            "generated_per_s": round(sum(r.num_tokens for r in out) / dt, 1),
+            "steps": st["steps"], "preemptions": st["preemptions"], "decode_tps": st.get("decode_tps"),
+            "prefill_tps": st.get("prefill_tps")}

@@ -9,6 +9,7 @@ sampling options are the fields of its ``Request`` (rollout/engine.py:17-21).
   random-weights  write a model folder (config.json, model.safetensors) from a config.json and a seed
   bench           decode tokens/s per batch size and prefill tokens/s
   kernel-bench    one kernel alone on random data
+  workload        a named workload (Qwen3-0.6B mixed batch, Qwen3-32B batch 16) through the engine, random weights
   replay          trace replay (what ``bin/trace_run`` does), from a file of JSON lines
 """
 from __future__ import annotations
@@ -90,6 +91,12 @@ def cmd_bench(args) -> int:
     return 0
 
 
+def cmd_workload(args) -> int:
+    from . import benchmark
+    print(json.dumps(benchmark.run_workload(args.name, args.layers, args.new)))
+    return 0
+
+
 def cmd_kernel_bench(args) -> int:
     from . import benchmark
     fn = {"attention_decode": benchmark.kernel_attention_decode, "attention_prefill": benchmark.kernel_attention_prefill,
@@ -153,6 +160,12 @@ def main(argv=None) -> int:
     b.add_argument("--steps", type=int, default=50)
     b.add_argument("--warmup", type=int, default=10)
     b.set_defaults(fn=cmd_bench)
+
+    wl = sub.add_parser("workload", help="a named workload through the engine, random weights of that shape")
+    wl.add_argument("name", choices=["0.6b-mixed", "32b"])
+    wl.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has, where time needs it")
+    wl.add_argument("--new", type=int, default=0, help="fewer new tokens per request than the workload names")
+    wl.set_defaults(fn=cmd_workload)
 
     k = sub.add_parser("kernel-bench", help="time one kernel alone on random data (for profiles)")
     k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated", "mma_rate", "tc5_rate"])
