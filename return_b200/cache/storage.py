@@ -55,6 +55,7 @@ class CacheStorage:
             self._group_layers.append(0)
             self._group_shape.append((0, 0))
         self.pools: List[Optional[torch.Tensor]] = []
+        self._layer_views: Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]] = {}
         self.states: Dict[int, torch.Tensor] = {}
 
     def make_manager(self) -> CacheManager:
@@ -63,6 +64,7 @@ class CacheStorage:
     def allocate(self) -> None:
         dev, dt = self.env.device, self.env.act_dtype
         self.pools = []
+        self._layer_views = {}
         for spec, layers, (hkv, d) in zip(self.group_specs, self._group_layers, self._group_shape):
             if layers == 0:
                 self.pools.append(None)
@@ -93,8 +95,11 @@ class CacheStorage:
         place = self.entry_place.get(owner_index)
         if place is not None:
             g, layer = place
-            pool = self.pools[g]
-            ctx.kv = KVView(k=pool[layer, 0], v=pool[layer, 1], block_table=batch.block_tables[g],
+            views = self._layer_views.get(place)
+            if views is None:                # the views of a layer's keys and values are made once
+                pool = self.pools[g]
+                views = self._layer_views[place] = (pool[layer, 0], pool[layer, 1])
+            ctx.kv = KVView(k=views[0], v=views[1], block_table=batch.block_tables[g],
                             page_size=self.group_specs[g].page_size)
         if owner_index in self.states:
             ctx.state = self.states[owner_index]

@@ -25,6 +25,9 @@
 // 192 KB of shared memory and all 512 TMEM columns a CTA (head size 128).  Same contract as the
 // reference's prefill kernel (rollout/attention.py:45-142) and as attention_mma.cu; keys arrive
 // rotated, tiles are aligned to absolute positions, a sliding window bounds the keys from below.
+// A step with too few such CTAs to fill the GPU (a short portion of a long prompt) splits the keys of every
+// block over gridDim.z CTAs; each leaves its unnormalised O with its reference maximum and sum in float32,
+// and a second kernel merges them (the same arithmetic as the decode kernel's merge).
 // *status is raised if a wait gave up.
 #include "tc5.cuh"
 
@@ -91,6 +94,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                         const int* __restrict__ cu_q, const int* __restrict__ seg_pos0,
                         const int* __restrict__ block_table, int bt_stride, int page_size,
                         bf16* __restrict__ out, int Hq, int Hkv, float scale_log2, int window,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int total_rows,
                         int* __restrict__ status) {
     // The swizzled tiles need 1024-byte alignment.  The kernel has no static shared memory, so the
     // dynamic window starts at the CTA's shared base; should it ever not be aligned, the kernel
@@ -115,11 +119,22 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     const int p0 = seg_pos0[seg] + row0;                  // position of the CTA's first query
     const int p_last = p0 + m_rows - 1;
     const int lo_min = window > 0 ? max(0, p0 - window + 1) : 0;
-    const int jt_begin = lo_min / KN;
-    // key tiles of each query tile, counted from jt_begin: B (if it has rows) needs all of the CTA's, A stops earlier
-    const int n_a = min(p_last, p0 + QM - 1) / KN - jt_begin + 1;
-    const int n_b = m_rows > QM ? p_last / KN - jt_begin + 1 : 0;
-    const int n_tiles = max(n_a, n_b);
+    int jt_first = lo_min / KN;
+    // key tiles of each query tile, counted from the first: B (if it has rows) needs all of the block's, A stops earlier
+    int na = min(p_last, p0 + QM - 1) / KN - jt_first + 1;
+    int nb = m_rows > QM ? p_last / KN - jt_first + 1 : 0;
+    int nt = max(na, nb);
+    const int n_split = gridDim.z, split = blockIdx.z;
+    if (n_split > 1) {                                    // this CTA's share of the block's key tiles; it may be empty
+        const int per = (nt + n_split - 1) / n_split;
+        const int t0 = split * per;
+        const int len = max(0, min(nt, t0 + per) - t0);
+        jt_first += t0;
+        na = min(max(na - t0, 0), len);
+        nb = min(max(nb - t0, 0), len);
+        nt = len;
+    }
+    const int jt_begin = jt_first, n_a = na, n_b = nb, n_tiles = nt;
     const int* bt_row = block_table + (size_t)seg * bt_stride;
     const Paging pg(page_size);
     const unsigned bar0 = smem_u32(bars);
@@ -238,8 +253,32 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         if (n_mine > 0) {
             ok = mbar_wait(bar(B_PV_DONE + qt), (n_mine - 1) & 1) && ok;
             fence_after_sync();
+        }
+        const size_t token = (size_t)(q_begin + row0 + grow);
+        if (n_split > 1) {
+            // one of several CTAs over this row's keys: O as it stands, with the reference maximum and the sum
+            const size_t slot = ((size_t)split * total_rows + token) * Hq + h;
+            if (row_valid) {
+                part_ml[2 * slot] = n_mine > 0 ? m_ref : -INFINITY;
+                part_ml[2 * slot + 1] = n_mine > 0 ? l_run : 0.f;
+            }
+            if (n_mine > 0) {
+                float* prow = part_o + slot * D;
+#pragma unroll 1
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    unsigned o[32];
+                    tmem_ld32(o_addr + c0, o);
+                    tmem_ld_wait();
+                    if (row_valid) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<uint4*>(prow + c0 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                    }
+                }
+            }
+        } else if (n_mine > 0) {
             const float inv = 1.f / l_run;
-            bf16* orow = out + (size_t)(q_begin + row0 + grow) * ((size_t)Hq * D) + (size_t)h * D;
+            bf16* orow = out + token * ((size_t)Hq * D) + (size_t)h * D;
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
                 unsigned o[32];
@@ -261,7 +300,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             }
         }
     } else if (warp == W_MMA) {
-        if (lane == 0) {
+        if (lane == 0 && n_tiles > 0) {
             // ============================================================== the MMA issuer
             // One thread's instruction latency is the pace of the tensor core here, so every descriptor is
             // a base worked out once plus a constant.
@@ -322,6 +361,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         const bf16* pool = is_k ? kpool : vpool;
         const unsigned bufs = smem_u32(is_k ? sK : sV);
         const int b_full = is_k ? B_K_FULL : B_V_FULL, b_free = is_k ? B_K_FREE : B_V_FREE;
+        if (n_tiles > 0) {
         for (int t = 0; t < n_tiles; ++t) {
             const int st = t % STAGES;
             if (t >= STAGES) ok = mbar_wait(bar(b_free + st), ((t / STAGES) - 1) & 1) && ok;
@@ -357,6 +397,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(b_full + (n_tiles - 1) % STAGES));
+        }
     }
     if (!ok) atomicExch(status, 1);
     fence_before_sync();
@@ -364,28 +405,72 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     if (warp == W_MMA) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// out[row, h] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the splits of the keys: one warp a (row, head).
+__global__ void __launch_bounds__(256)
+merge_key_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                        const int* __restrict__ tiles, const int* __restrict__ cu_q, int n_split, int total_rows,
+                        int Hq, bf16* __restrict__ out) {
+    const int seg = tiles[2 * blockIdx.y], row0 = tiles[2 * blockIdx.y + 1];
+    const int q_begin = cu_q[seg];
+    const int m_rows = min(NQ * QM, cu_q[seg + 1] - q_begin - row0);
+    const int r = blockIdx.z * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31, h = blockIdx.x;
+    if (r >= m_rows) return;
+    const size_t token = (size_t)(q_begin + row0 + r);
+    constexpr int PER = D / 32;                            // floats of a row a lane holds: 2 or 4
+    float m_all = -INFINITY;
+    for (int s = 0; s < n_split; ++s) m_all = fmaxf(m_all, part_ml[2 * (((size_t)s * total_rows + token) * Hq + h)]);
+    float acc[PER] = {}, l_all = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+        const size_t slot = ((size_t)s * total_rows + token) * Hq + h;
+        const float l = part_ml[2 * slot + 1];
+        if (l == 0.f) continue;                            // a share without keys for this row left no O
+        const float wgt = fast_exp2(part_ml[2 * slot] - m_all);
+        l_all += l * wgt;
+        const float* prow = part_o + slot * D + lane * PER;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] += prow[i] * wgt;
+    }
+    const float inv = 1.f / l_all;
+    bf16* orow = out + token * ((size_t)Hq * D) + (size_t)h * D + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; i += 2)
+        *reinterpret_cast<__nv_bfloat162*>(orow + i) = __floats2bfloat162_rn(acc[i] * inv, acc[i + 1] * inv);
+}
+
 }  // namespace
 
 RB_EXPORT int rb_attn_tc5_head_dim() { return D; }
 RB_EXPORT int rb_attn_tc5_tile_rows() { return NQ * QM; }
 
+// float32 values of the two buffers that n_split > 1 needs: [n_split, total_rows, Hq, D] and [n_split, total_rows, Hq, 2]
+RB_EXPORT long long rb_attn_tc5_split_floats(int n_split, int total_rows, int Hq) {
+    return n_split > 1 ? (long long)n_split * total_rows * Hq * (D + 2) : 0;
+}
+
 // tiles: [n_tiles, 2] = (segment, first row of a block of up to 256 query rows), the blocks with the
-// longest contexts first.
+// longest contexts first.  n_split > 1 splits the keys of every block over that many CTAs; ``scratch`` then
+// holds rb_attn_tc5_split_floats(...) floats and total_rows is the number of rows of q.
 RB_EXPORT int rb_attn_prefill_tc5(const void* q, int ld, const void* kpool, const void* vpool, const int* tiles,
                                   int n_tiles, const int* cu_q, const int* seg_pos0, const int* block_table,
                                   int bt_stride, int page_size, void* out, int Hq, int Hkv, float scale, int window,
-                                  int* status, cudaStream_t st) {
+                                  int n_split, void* scratch, int total_rows, int* status, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
-    if (n_tiles > 65535) return (int)cudaErrorInvalidValue;
+    if (n_tiles > 65535 || n_split < 1 || n_split > 64 || (n_split > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(Hq, n_tiles);
+    float* part_o = (float*)scratch;
+    float* part_ml = part_o ? part_o + (size_t)n_split * total_rows * Hq * D : nullptr;
+    dim3 grid(Hq, n_tiles, n_split);
     attn_prefill_tc5_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(
         (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride,
-        page_size, (bf16*)out, Hq, Hkv, scale * LOG2E, window, status);
+        page_size, (bf16*)out, Hq, Hkv, scale * LOG2E, window, part_o, part_ml, total_rows, status);
+    if (n_split > 1) {
+        dim3 mgrid(Hq, n_tiles, NQ * QM / 8);
+        merge_key_splits_kernel<<<mgrid, 256, 0, st>>>(part_o, part_ml, tiles, cu_q, n_split, total_rows, Hq, (bf16*)out);
+    }
     return rb_launch_status();
 }

@@ -128,6 +128,7 @@ class StepBatch:
 
     def __init__(self, host: HostBatch, device, staging: "BatchStaging"):
         self.host = host
+        self.scratch = {}                    # work buffers and memoised choices of this step (LayerContext.buffer)
         self.num_tokens = host.num_tokens
         self.num_segments = host.num_segments
         self.num_want = host.num_want
@@ -207,6 +208,7 @@ class StaticDecodeBatch:
         self.n = n
         self.num_tokens = self.num_segments = self.num_want = n
         self.fixed_decode_splits = fixed_decode_splits
+        self.scratch = {}                    # work buffers of the captured step: they live as long as the graph
         self.host = _StaticHost(n)
         self._max_blocks = list(max_blocks)
         sizes = [n, n, n, n, n + 1, n, n, n, n] + [n * b for b in max_blocks]

@@ -37,7 +37,8 @@ class ModelRunner:
         self.storage.allocate()
         self.staging = BatchStaging(self.env.device)
         self.vocab_size = model.spec.vocab_size
-        self._graphs = {}                   # (decode batch size, context span) -> (graph, static batch, static logits)
+        self._kv_groups_cached = 0
+        self._graphs = {}                   # (decode batch size, key splits) -> (graph, static batch, static logits)
         self._graph_pool = None
         self.launches_per_replay = {}       # decode batch size -> kernels of this package in its graph
 
@@ -125,14 +126,14 @@ class ModelRunner:
     def _graphed_decode(self, host, device_tokens=None) -> torch.Tensor:
         """A step of single decoded tokens replays a graph captured for its batch size, as the
         reference does (rollout/model.py:346-407); graphs are captured on first use.  A captured
-        launch cannot change its grid, so there is one graph per batch size and per span of context
-        lengths (the longest request's, rounded up to a power of two or one and a half): the span fixes how many ways
-        the decode attention splits the keys."""
+        launch cannot change its grid, so there is one graph per batch size and per number of ways the
+        decode attention splits the keys.  That number follows from the span of context lengths (the
+        longest request's, rounded up to a power of two or one and a half); many spans share one."""
         n = host.num_tokens
-        span = self._span(int(host.seg_kv_len.max()))
-        entry = self._graphs.get((n, span))
+        splits = self._splits(n, int(host.seg_kv_len.max()))
+        entry = self._graphs.get((n, splits))
         if entry is None:
-            entry = self._capture(n, span)
+            entry = self._capture(n, splits)
         graph, static, logits = entry
         static.fill(host)
         if device_tokens is not None:
@@ -149,19 +150,25 @@ class ModelRunner:
             span += span // 2 if span & (span - 1) == 0 else span // 3     # 512, 768, 1024, 1536, 2048, ...
         return span
 
+    def _splits(self, n: int, longest: int) -> int:
+        return ops.decode_splits(n * self._kv_groups(), self._span(longest))
+
     def _kv_groups(self) -> int:
         """CTAs a decoded token gives the attention kernel per split, at most over the layers."""
+        if self._kv_groups_cached:
+            return self._kv_groups_cached
         most = 1
         for layer in self.model.spec.layers:
             heads, kv = getattr(layer.mixer, "num_heads", None), getattr(layer.mixer, "num_kv_heads", None)
             if heads and kv:
                 most = max(most, kv * ((heads // kv + 15) // 16))
+        self._kv_groups_cached = most
         return most
 
-    def _capture(self, n: int, span: int):
+    def _capture(self, n: int, splits: int):
         max_blocks = [(self.max_positions + g.page_size - 1) // g.page_size for g in self.manager.groups]
         # every mixer of a captured step sees the same fixed split count
-        static = StaticDecodeBatch(n, max_blocks, self.env.device, ops.decode_splits(n * self._kv_groups(), span))
+        static = StaticDecodeBatch(n, max_blocks, self.env.device, splits)
         side = torch.cuda.Stream(device=self.env.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                      # warm-up outside the capture
@@ -175,12 +182,12 @@ class ModelRunner:
         self.launches_per_replay[n] = ops.launch_count - before
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        self._graphs[(n, span)] = (graph, static, logits)
-        return self._graphs[(n, span)]
+        self._graphs[(n, splits)] = (graph, static, logits)
+        return self._graphs[(n, splits)]
 
     def capture_decode_graphs(self, batch_sizes=None) -> None:
         """Captures the decode graphs ahead of the first request (the reference's ``build_graph``)."""
-        span = self._span(min(self.max_positions, 4096))
         for n in (batch_sizes or range(1, self.config.max_reside + 1)):
-            if (n, span) not in self._graphs:
-                self._capture(n, span)
+            splits = self._splits(n, min(self.max_positions, 4096))
+            if (n, splits) not in self._graphs:
+                self._capture(n, splits)

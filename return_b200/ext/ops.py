@@ -36,10 +36,19 @@ def _ptr(t: Optional[torch.Tensor]):
         return None
     if not t.is_cuda:
         raise KernelError("the engine's kernels run on a CUDA device only; got a CPU tensor")
-    return c_void_p(t.data_ptr())
+    return t.data_ptr()              # an int: ctypes makes the pointer from it (argtypes are set)
+
+
+try:                                                  # the raw handle, without building a Stream object
+    _raw_stream, _device_index = torch._C._cuda_getCurrentRawStream, torch._C._cuda_getDevice
+except AttributeError:                                # a torch without these: the public way, slower
+    _raw_stream = None
 
 
 def _stream():
+    """The current stream of the current device (each launch asks: a graph capture changes it)."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(_device_index()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -187,14 +196,18 @@ def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, interleave: int) -> None:
+def gated_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, interleave: int, ctx=None) -> None:
     """out[T, I] = silu(x @ gate^T) * (x @ up^T) for the fused weight ``w`` [2I, K] of a gated
     feed-forward.  With the interleaved layout and few rows the product's epilogue does the
-    gating; otherwise a product into a [T, 2I] buffer is followed by the SwiGLU kernel."""
+    gating; otherwise a product into a [T, 2I] buffer (from ``ctx``, a parts.base.LayerContext, if given)
+    is followed by the SwiGLU kernel."""
     if interleave == 8 and skinny_ok(x, w):
         gemm_skinny(x, w, out, gated=True)
         return
-    gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
+    if ctx is not None:
+        gu = ctx.buffer("gated_linear.gate_up", (x.shape[0], w.shape[0]), x.dtype, x.device)
+    else:
+        gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
     linear(x, w, gu)
     swiglu(gu, out, interleave)
 
@@ -394,6 +407,7 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
 _attn_tc5_libs = {}
 TC5_ATTENTION_HEAD_DIMS = (64, 128)
 TC5_TILE_ROWS = 256            # query rows of one CTA of the tcgen05 prefill attention kernel
+NUM_SMS = 148
 
 
 def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
@@ -404,26 +418,62 @@ def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
             raise KernelError(f"head_dim={head_dim}: the tcgen05 attention kernel takes {TC5_ATTENTION_HEAD_DIMS}")
         lib = build.load(f"return_attn_tc5_d{head_dim}", ["attention_tc5.cu"], {"HEAD_DIM": head_dim})
         P, I, F = c_void_p, c_int, c_float
-        lib.rb_attn_prefill_tc5.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, P, P]
+        lib.rb_attn_prefill_tc5.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, I, P, I, P, P]
+        lib.rb_attn_tc5_split_floats.argtypes = [I, I, I]
+        lib.rb_attn_tc5_split_floats.restype = ctypes.c_longlong
         lib.rb_attn_prefill_tc5.restype = c_int
         _attn_tc5_libs[head_dim] = lib
     return lib
 
 
 def attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_table, page_size, out, num_heads,
-                          num_kv_heads, head_dim, scale, window=0) -> None:
+                          num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None) -> None:
     """tcgen05 attention for the listed (segment, first row) blocks of up to TC5_TILE_ROWS query rows
-    (the blocks with the longest contexts should come first: they take longest)."""
+    (the blocks with the longest contexts should come first: they take longest).  ``num_splits`` > 1 splits
+    every block's keys over that many CTAs and merges them in a second launch; ``held``: the step's map of
+    work buffers, so that the layers share the buffer of the partial results."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     assert tiles.dtype == torch.int32 and tiles.is_contiguous()
     lib = attention_tc5_lib(head_dim)
+    T = qkv.shape[0]
+    scratch = None
+    if num_splits > 1:
+        key = ("attention.prefill_split_scratch", num_splits, T, num_heads, head_dim)
+        scratch = held.get(key) if held is not None else None
+        if scratch is None:
+            scratch = torch.empty(lib.rb_attn_tc5_split_floats(num_splits, T, num_heads), dtype=torch.float32, device=qkv.device)
+            if held is not None:
+                held[key] = scratch
     _check(lib.rb_attn_prefill_tc5(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(tiles),
                                    tiles.shape[0], _ptr(cu_q), _ptr(seg_pos0), _ptr(block_table),
                                    block_table.stride(0), page_size, _ptr(out), num_heads, num_kv_heads, scale,
-                                   int(window or 0), _ptr(tc5_status(qkv.device)), _stream()), "attention_prefill_tc5")
+                                   int(window or 0), num_splits, _ptr(scratch), T, _ptr(tc5_status(qkv.device)),
+                                   _stream()), "attention_prefill_tc5", 2 if num_splits > 1 else 1)
 
 
-NUM_SMS = 148
+PREFILL_SPLIT_MIN_KEYS = 512       # a CTA of a split block keeps at least this many keys
+
+
+def prefill_splits(n_ctas: int, longest_context: int) -> int:
+    """How many ways the keys of the prompt blocks are split: a CTA owns an SM, so blocks x heads below
+    the SM count leave SMs idle (a short portion of a long prompt); the keys are then shared out until the
+    CTAs fill the GPU once, as long as every share keeps PREFILL_SPLIT_MIN_KEYS keys."""
+    return max(1, min(NUM_SMS // max(1, n_ctas), longest_context // PREFILL_SPLIT_MIN_KEYS, 64))
+
+
+def _prefill_split_count(batch, num_heads, window) -> int:
+    held = getattr(batch, "scratch", None)
+    key = ("attention.prefill_splits", num_heads, window)
+    if held is not None and key in held:
+        return held[key]
+    host = batch.host
+    longest = int(host.seg_kv_len[host.prefill_tiles_tc5[:, 0]].max())
+    if window:
+        longest = min(longest, int(window) + TC5_TILE_ROWS)
+    n = prefill_splits(host.prefill_tiles_tc5.shape[0] * num_heads, longest)
+    if held is not None:
+        held[key] = n
+    return n
 
 
 def decode_splits(n_ctas_base: int, max_kv_len: int, ctas_per_sm: int = 2) -> int:
@@ -455,14 +505,26 @@ def attention_prefill_mma(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_tabl
            "attention_prefill")
 
 
+def _split_scratch(lib, n, num_heads, num_splits, device, held=None):
+    """The buffer in which the splits of the keys leave their partial results (none for one split).
+    ``held``: the step's map of work buffers; every layer of the step then shares one."""
+    key = ("attention.split_scratch", n, num_heads, num_splits)
+    if held is not None and key in held:
+        return held[key]
+    floats = lib.rb_attn_decode_scratch_floats(n, num_heads, num_splits)
+    scratch = torch.empty(floats, dtype=torch.float32, device=device) if floats else None
+    if held is not None:
+        held[key] = scratch
+    return scratch
+
+
 def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, block_table, page_size, out,
-                         num_heads, num_kv_heads, head_dim, scale, window=0, num_splits=1) -> None:
+                         num_heads, num_kv_heads, head_dim, scale, window=0, num_splits=1, held=None) -> None:
     """Tensor-core attention for segments of one token, the keys split ``num_splits`` ways."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     lib = attention_lib(head_dim)
     n = decode_segs.shape[0]
-    floats = lib.rb_attn_decode_scratch_floats(n, num_heads, num_splits)
-    scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device) if floats else None
+    scratch = _split_scratch(lib, n, num_heads, num_splits, qkv.device, held)
     _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
                               _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
                               _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
@@ -470,6 +532,18 @@ def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, blo
 
 
 def _decode_split_count(batch, num_heads, num_kv_heads, window) -> int:
+    """The split count of this step's decoded tokens, worked out once per step and kind of layer."""
+    held = getattr(batch, "scratch", None)
+    if held is None:
+        return _decode_split_count_now(batch, num_heads, num_kv_heads, window)
+    key = ("attention.splits", num_heads, num_kv_heads, window)
+    n = held.get(key)
+    if n is None:
+        n = held[key] = _decode_split_count_now(batch, num_heads, num_kv_heads, window)
+    return n
+
+
+def _decode_split_count_now(batch, num_heads, num_kv_heads, window) -> int:
     host = batch.host
     n_dec = host.decode_segs.shape[0]
     group = num_heads // num_kv_heads
@@ -504,8 +578,7 @@ def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_d
     lib = attention_lib(head_dim)
     n = batch.decode_segs.shape[0]
     splits = _decode_split_count(batch, num_heads, num_kv_heads, window)
-    floats = lib.rb_attn_decode_scratch_floats(n, num_heads, splits)
-    scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device) if floats else None
+    scratch = _split_scratch(lib, n, num_heads, splits, qkv.device, getattr(batch, "scratch", None))
     if rot_dim:
         assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape[1] * 2 == rot_dim
         assert cos.is_contiguous() and sin.is_contiguous()
@@ -535,7 +608,8 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
     if host.prefill_tiles.shape[0]:
         if head_dim in TC5_ATTENTION_HEAD_DIMS:
             attention_prefill_tc5(qkv, k_pool, v_pool, batch.prefill_tiles_tc5, batch.cu_q, batch.seg_pos0, block_table,
-                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
+                                  page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
+                                  _prefill_split_count(batch, num_heads, window), getattr(batch, "scratch", None))
         else:
             attention_prefill_mma(qkv, k_pool, v_pool, batch.prefill_tiles, batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
@@ -543,7 +617,7 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
     if n_dec:
         attention_decode_mma(qkv, k_pool, v_pool, batch.decode_segs, batch.cu_q, batch.seg_kv_len, block_table,
                              page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
-                             _decode_split_count(batch, num_heads, num_kv_heads, window))
+                             _decode_split_count(batch, num_heads, num_kv_heads, window), getattr(batch, "scratch", None))
 
 
 # ------------------------------------------------------------------------------- sampling

@@ -56,7 +56,7 @@ class PagedAttention(Mixer):
     def forward(self, x, ctx):
         s, b, kv = self.spec, ctx.batch, ctx.kv
         T = x.shape[0]
-        qkv = torch.empty((T, self.q_size + 2 * self.kv_size), dtype=x.dtype, device=x.device)
+        qkv = ctx.buffer("attention.qkv", (T, self.q_size + 2 * self.kv_size), x.dtype, x.device)
         ops.linear(x, self.p_qkv, qkv)
 
         qw = self.q_norm.p_weight if self.q_norm is not None else None
@@ -64,14 +64,14 @@ class PagedAttention(Mixer):
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         offset = s.qk_norm.offset if s.qk_norm is not None else 0.0
         tables = self.position.rotary_tables() if self.position is not None else None
-        o = torch.empty((T, self.q_size), dtype=x.dtype, device=x.device)
+        o = ctx.buffer("attention.o", (T, self.q_size), x.dtype, x.device)
         if (tables is not None or self.position is None) and ops.decode_only(b, x.dtype, s.num_heads, s.num_kv_heads, s.window):
             # single decoded tokens only: norm, rotation, cache write and attention are one kernel
             cos, sin, rot = tables if tables is not None else (None, None, 0)
             ops.attention_decode_fused(qkv, qw, kw, eps, offset, cos, sin, rot, kv.k, kv.v, b, kv.block_table,
                                        kv.page_size, o, s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
                                        write_kv=ctx.write_cache)
-            y = torch.empty((T, s.hidden_size), dtype=x.dtype, device=x.device)
+            y = ctx.buffer("attention.y", (T, s.hidden_size), x.dtype, x.device)
             ops.linear(o, self.p_o, y)
             return y
         if tables is not None or self.position is None:
@@ -93,6 +93,6 @@ class PagedAttention(Mixer):
 
         ops.paged_attention(qkv, kv.k, kv.v, b, kv.block_table, kv.page_size, o, s.num_heads,
                             s.num_kv_heads, s.head_dim, s.scale, s.window)
-        y = torch.empty((T, s.hidden_size), dtype=x.dtype, device=x.device)
+        y = ctx.buffer("attention.y", (T, s.hidden_size), x.dtype, x.device)
         ops.linear(o, self.p_o, y)
         return y

@@ -71,6 +71,27 @@ class LayerContext:
     state: Optional[torch.Tensor] = None      # [num_slots, *StateNeed.shape]; row = batch.seg_slot
     write_cache: bool = True
 
+    def buffer(self, name: str, shape, dtype, device) -> torch.Tensor:
+        """An uninitialised work buffer for the part that asks.  The layers of a step run one after the
+        other in one stream, so a buffer of the same name, shape and type is handed to every layer that
+        asks for it: the step allocates once, not once per layer.  Whoever asks owns the contents until
+        the next layer's part of the same name asks again; a name is unique to one use in one part."""
+        held = getattr(self.batch, "scratch", None)
+        if held is None:                       # a batch without a map of buffers: allocate each time
+            return torch.empty(shape, dtype=dtype, device=device)
+        key = (name, shape, dtype)
+        t = held.get(key)
+        if t is None:
+            t = held[key] = torch.empty(shape, dtype=dtype, device=device)
+        return t
+
+
+def work_buffer(ctx: Optional[LayerContext], name: str, shape, dtype, device) -> torch.Tensor:
+    """``ctx.buffer(...)``, or a fresh tensor for a part that is run on its own, without a context."""
+    if ctx is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    return ctx.buffer(name, shape, dtype, device)
+
 
 class Part:
     # False for a part whose forward looks at the step's tables on the host (its launches then

@@ -41,7 +41,7 @@ class PreNormBlock(Block):
 
     def forward(self, stream, delta, ctx):
         T, H = stream.shape
-        a = torch.empty((T, H), dtype=self.env.act_dtype, device=stream.device)
+        a = ctx.buffer("block.normed", (T, H), self.env.act_dtype, stream.device)
         self.mixer_norm.add_forward(stream, delta, a)             # stream += delta; a = norm(stream)
         mixed = self.mixer.forward(a, ctx)
         self.feed_forward_norm.add_forward(stream, mixed, a)      # stream += mixed; a = norm(stream)

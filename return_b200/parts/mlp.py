@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..ext import ops
-from .base import FEED_FORWARDS, FeedForward, ParamSpec
+from .base import FEED_FORWARDS, FeedForward, ParamSpec, work_buffer
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -26,8 +26,8 @@ class SwiGLU(FeedForward):
     def forward(self, x, ctx):
         s = self.spec
         T = x.shape[0]
-        act = torch.empty((T, s.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.gated_linear(x, self.p_gate_up, act, s.interleave)
-        y = torch.empty((T, s.hidden_size), dtype=x.dtype, device=x.device)
+        act = work_buffer(ctx, "mlp.act", (T, s.intermediate_size), x.dtype, x.device)
+        ops.gated_linear(x, self.p_gate_up, act, s.interleave, ctx)
+        y = work_buffer(ctx, "mlp.y", (T, s.hidden_size), x.dtype, x.device)
         ops.linear(act, self.p_down, y)
         return y

@@ -262,8 +262,11 @@ def test_attention_prefill_mma(Hq, Hkv, D, P, window):
 
 @pytest.mark.parametrize("Hq,Hkv,D,P", [(8, 8, 64, 4), (32, 8, 128, 16), (6, 2, 128, 8), (20, 1, 64, 16), (4, 4, 128, 64)])
 @pytest.mark.parametrize("window", [None, 37, 100])
-def test_attention_prefill_tc5(Hq, Hkv, D, P, window):
-    """The tcgen05 prefill kernel: blocks of 256 rows (two tiles of 128), tails, earlier keys in the cache, windows."""
+@pytest.mark.parametrize("splits", [1, 2, 5])
+def test_attention_prefill_tc5(Hq, Hkv, D, P, window, splits):
+    """The tcgen05 prefill kernel: blocks of 256 rows (two tiles of 128), tails, earlier keys in the cache, windows;
+    and the keys of every block split over several CTAs, some of which then have no keys at all, or keys
+    for the later rows only."""
     ops = _ops()
     kv_lens, q_lens = [2, 70, 200, 128, 129, 300, 640], [2, 70, 3, 128, 65, 130, 300]
     pg = Paged(kv_lens, q_lens, Hq, Hkv, D, P, torch.bfloat16, seed=D + 5)
@@ -272,13 +275,21 @@ def test_attention_prefill_tc5(Hq, Hkv, D, P, window):
     out = torch.full((sum(q_lens), Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
     scale = 0.7 / math.sqrt(D)
     ops.attention_prefill_tc5(pg.qkv, pg.kpool, pg.vpool, tiles, pg.cu_q, pg.seg_pos0, pg.bt, P, out, Hq, Hkv, D,
-                              scale, window or 0)
+                              scale, window or 0, num_splits=splits)
     torch.cuda.synchronize()
     st = ops.tc5_status(torch.device(DEV))
     flag = int(st.item())
     st.zero_()
     assert flag == 0, "a bounded wait inside the kernel gave up"
     assert torch.allclose(out.float().cpu(), pg.reference(scale, window), atol=3e-2, rtol=3e-2)
+
+
+def test_prefill_split_choice():
+    """Keys are split only while blocks x heads leave SMs idle and every share keeps enough keys."""
+    ops = _ops()
+    assert ops.prefill_splits(256, 8192) == 1 and ops.prefill_splits(100, 8192) == 1
+    assert ops.prefill_splits(64, 4096) == 2 and ops.prefill_splits(32, 4096) == 4
+    assert ops.prefill_splits(32, 1024) == 2 and ops.prefill_splits(32, 600) == 1 and ops.prefill_splits(2, 100000) == 64
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,P", ATT_SHAPES)
@@ -328,7 +339,8 @@ def test_attention_decode_fused(Hq, Hkv, D, P, window, rot_frac, norm):
 
 
 @pytest.mark.parametrize("D", [64, 128])
-def test_attention_prefill_tc5_long(D):
+@pytest.mark.parametrize("splits", [1, 3])
+def test_attention_prefill_tc5_long(D, splits):
     """Dozens of key tiles per query tile with every SM busy: the loaders, the issuing thread and the
     softmax rows drift apart in time, which is where a barrier that is waited on out of step shows.
     One far key is made to stand out for one late query, so a lost or misplaced tile shows too."""
@@ -347,7 +359,7 @@ def test_attention_prefill_tc5_long(D):
     scale = 1.0 / math.sqrt(D)
     for _ in range(3):
         ops.attention_prefill_tc5(pg.qkv, pg.kpool, pg.vpool, tiles, pg.cu_q, pg.seg_pos0, pg.bt, P, out, Hq, Hkv, D,
-                                  scale, 0)
+                                  scale, 0, num_splits=splits)
     torch.cuda.synchronize()
     st = ops.tc5_status(torch.device(DEV))
     flag = int(st.item())

@@ -108,6 +108,26 @@ def test_long_decoding(tmp_path):
         _compare(d, reqs, got, dtype)
 
 
+def test_short_portions_of_a_long_prompt_split_their_keys(tmp_path, monkeypatch):
+    """Head size 64 puts prompt portions on the tcgen05 attention kernel; a portion of 300 tokens behind more
+    than a thousand cached ones gives so few CTAs that the keys of every block are split over several and
+    merged.  The split must have happened, and the logits are those of the whole prompt."""
+    from return_b200.ext import ops
+    d = helpers.make_model_dir(tmp_path, "A", head_dim=64, max_position_embeddings=2048)
+    reqs = _requests("A", (1500, 700), 80)
+    steps = helpers.portions(reqs, (300, 260, 2, 130))
+    used, kernel = set(), ops.attention_prefill_tc5
+
+    def spy(*a, **k):
+        used.add(a[14] if len(a) > 14 else k.get("num_splits", 1))
+        return kernel(*a, **k)
+
+    monkeypatch.setattr(ops, "attention_prefill_tc5", spy)
+    got = _replay(d, "bfloat16", steps, 16)
+    _compare(d, reqs, got, "bfloat16")
+    assert 1 in used and max(used) > 1, used
+
+
 def test_first_tokens_of_a_sequence(tmp_path):
     for case in "AB":
         d = helpers.make_model_dir(tmp_path / case, case)
