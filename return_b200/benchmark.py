@@ -341,7 +341,9 @@ def run_workload(name: str, layers: int = 0, new: int = 0) -> Dict[str, object]:
     runner = ModelRunner.from_random(cfg, ecfg, seed=w["seed"])
     engine = Engine(runner)
     reqs = [Request(f"w{i}", _random_ids(cfg.vocab_size, n, gen), max_new_tokens=n_new, temperature=0.0) for i, n in enumerate(lens)]
-    # warm-up: one short request through prefill and a few decode steps (compiles, captures a graph)
+    # start-up, untimed: the decode graphs (as the reference's build_graph does), and one short request
+    # through prefill and a few decode steps
+    runner.capture_decode_graphs()
     engine.generate([_random_ids(cfg.vocab_size, 64, gen)], max_new_tokens=4, temperature=0.0)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -354,4 +356,4 @@ def run_workload(name: str, layers: int = 0, new: int = 0) -> Dict[str, object]:
             "tokens_per_s": round((sum(lens) + sum(r.num_tokens for r in out)) / dt, 1),
             "generated_per_s": round(sum(r.num_tokens for r in out) / dt, 1),
             "steps": st["steps"], "preemptions": st["preemptions"], "decode_tps": st.get("decode_tps"),
-            "prefill_tps": st.get("prefill_tps")}
+            "prefill_tps": st.get("prefill_tps"), "decode_graphs": len(runner._graphs)}

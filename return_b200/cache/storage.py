@@ -6,8 +6,9 @@ hence a page pool, a free list and block tables (``return_b200/cache/manager.py`
 a group is one tensor ``[layers, 2, num_pages, Hkv, page_size, D]`` in the activation dtype
 (index 0 of the second axis: keys, 1: values), so one page id addresses a slab in every layer of
 the group, as in the reference (rollout/cache.py:19-24), and one (page, kv head) tile is
-contiguous.  A mixer that asks for state of fixed size gets ``[max_reside, *shape]``, one row per
-request slot (after rollout/cache.py:340-360).
+contiguous.  A mixer that asks for state of fixed size gets ``[max_reside + 1, *shape]``, one row per
+request slot and a last one that belongs to no request (the padding rows of a captured decode step
+point at it) (after rollout/cache.py:340-360).
 """
 from __future__ import annotations
 
@@ -70,7 +71,7 @@ class CacheStorage:
                 self.pools.append(None)
                 continue
             self.pools.append(torch.zeros((layers, 2, spec.num_pages, hkv, spec.page_size, d), dtype=dt, device=dev))
-        self.states = {i: torch.zeros((self.max_reside,) + tuple(n.shape), dtype=n.dtype, device=dev)
+        self.states = {i: torch.zeros((self.max_reside + 1,) + tuple(n.shape), dtype=n.dtype, device=dev)
                        for i, n in self._state_needs.items()}
 
     def bytes_per_token(self) -> int:

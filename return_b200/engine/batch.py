@@ -202,10 +202,13 @@ class StaticDecodeBatch:
     """Tables of a step of exactly ``n`` single decoded tokens at fixed device addresses, so that the
     step can be captured in a CUDA graph once and replayed with new contents.  The block tables
     have a fixed width (``max_blocks`` of each group); the split count of the decode attention is
-    fixed too, because a captured launch cannot change its grid."""
+    fixed too, because a captured launch cannot change its grid.  A step of fewer than ``n`` tokens fills
+    the first rows; the rows behind them are padding: one key, no page (nothing of the cache is read or
+    written), and the state slot ``pad_slot`` that belongs to no request."""
 
-    def __init__(self, n: int, max_blocks: Sequence[int], device, fixed_decode_splits: int):
+    def __init__(self, n: int, max_blocks: Sequence[int], device, fixed_decode_splits: int, pad_slot: int = 0):
         self.n = n
+        self.pad_slot = pad_slot
         self.num_tokens = self.num_segments = self.num_want = n
         self.fixed_decode_splits = fixed_decode_splits
         self.scratch = {}                    # work buffers of the captured step: they live as long as the graph
@@ -241,16 +244,22 @@ class StaticDecodeBatch:
         self.upload()
 
     def fill(self, host: HostBatch) -> None:
-        """Takes the contents of a packed decode step of n tokens."""
-        assert host.num_tokens == self.n and host.num_segments == self.n
+        """Takes the contents of a packed decode step of up to n tokens; the rows behind them are padding."""
+        m = host.num_tokens
+        assert m <= self.n and host.num_segments == m
         self._event.synchronize()            # the copy that last read the pinned buffer is done
         for name in ("tokens", "pos", "seg_slot", "seg_pos0", "seg_kv_len"):
-            self._h[name][:] = getattr(host, name)
+            self._h[name][:m] = getattr(host, name)
+        if m < self.n:
+            for name, value in (("tokens", 0), ("pos", 0), ("seg_slot", self.pad_slot), ("seg_pos0", 0), ("seg_kv_len", 1)):
+                self._h[name][m:] = value
         for dst, src in zip(self._h_bt, host.block_tables):
             if src.shape[1] > dst.shape[1]:
                 raise ValueError("a request is longer than the captured block table")
-            dst[:, :src.shape[1]] = src
-        self.host.seg_kv_len = host.seg_kv_len
+            dst[:m, :src.shape[1]] = src     # what lies behind a row's pages is never read: its length bounds the keys
+            if m < self.n:
+                dst[m:] = -1
+        self.host.seg_kv_len = self._h["seg_kv_len"]
         self.upload()
 
     def upload(self) -> None:

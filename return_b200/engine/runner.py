@@ -129,7 +129,8 @@ class ModelRunner:
         launch cannot change its grid, so there is one graph per batch size and per number of ways the
         decode attention splits the keys.  That number follows from the span of context lengths (the
         longest request's, rounded up to a power of two or one and a half); many spans share one."""
-        n = host.num_tokens
+        m = host.num_tokens
+        n = self.graph_batch_size(m)
         splits = self._splits(n, int(host.seg_kv_len.max()))
         entry = self._graphs.get((n, splits))
         if entry is None:
@@ -137,11 +138,23 @@ class ModelRunner:
         graph, static, logits = entry
         static.fill(host)
         if device_tokens is not None:
-            static.tokens.copy_(device_tokens[:n], non_blocking=True)     # after the upload, in stream order
+            static.tokens[:m].copy_(device_tokens[:m], non_blocking=True)     # after the upload, in stream order
         graph.replay()
-        if host.num_want == n and (host.want_rows == range(n)).all():
-            return logits
+        if host.num_want == m and (host.want_rows == range(m)).all():
+            return logits[:m]
         return logits.index_select(0, torch.as_tensor(host.want_rows, dtype=torch.int64).to(logits.device))
+
+    def graph_batch_size(self, m: int) -> int:
+        """The batch size of the graph that runs a decode step of ``m`` tokens: ``m`` itself up to 8 (the
+        weight-streaming kernels are compiled per row count), then the next of 12, 16, 24, 32, 48, 64, ...
+        so that requests which end one by one do not each ask for a capture; the rows between are padding.
+        Never more than ``max_reside``."""
+        if m <= 8:
+            return m
+        n = 8
+        while n < m:
+            n += n // 2 if n & (n - 1) == 0 else n // 3
+        return min(n, max(m, self.config.max_reside))
 
     @staticmethod
     def _span(longest: int) -> int:
@@ -168,7 +181,7 @@ class ModelRunner:
     def _capture(self, n: int, splits: int):
         max_blocks = [(self.max_positions + g.page_size - 1) // g.page_size for g in self.manager.groups]
         # every mixer of a captured step sees the same fixed split count
-        static = StaticDecodeBatch(n, max_blocks, self.env.device, splits)
+        static = StaticDecodeBatch(n, max_blocks, self.env.device, splits, pad_slot=self.config.max_reside)
         side = torch.cuda.Stream(device=self.env.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                      # warm-up outside the capture
@@ -185,9 +198,19 @@ class ModelRunner:
         self._graphs[(n, splits)] = (graph, static, logits)
         return self._graphs[(n, splits)]
 
-    def capture_decode_graphs(self, batch_sizes=None) -> None:
-        """Captures the decode graphs ahead of the first request (the reference's ``build_graph``)."""
-        for n in (batch_sizes or range(1, self.config.max_reside + 1)):
-            splits = self._splits(n, min(self.max_positions, 4096))
-            if (n, splits) not in self._graphs:
-                self._capture(n, splits)
+    def capture_decode_graphs(self, batch_sizes=None) -> int:
+        """Captures the decode graphs ahead of the first request (the reference's ``build_graph``): for every
+        batch size that ``graph_batch_size`` can give (or those asked for), one graph per split count that
+        a span of context lengths up to the engine's limit leads to.  Returns how many graphs there are."""
+        sizes = batch_sizes or sorted({self.graph_batch_size(m) for m in range(1, self.config.max_reside + 1)})
+        spans, span = [], self._span(1)
+        while True:
+            spans.append(span)
+            if span >= self.max_positions:
+                break
+            span = self._span(span + 1)
+        for n in sizes:
+            for splits in sorted({self._splits(n, sp) for sp in spans}):
+                if (n, splits) not in self._graphs:
+                    self._capture(n, splits)
+        return len(self._graphs)

@@ -196,6 +196,30 @@ def test_decode_that_runs_ahead_of_the_host_gives_the_same_tokens(tmp_path):
     assert [r.output[:8] for r in reqs] == [w[:8] for w in want]
 
 
+def test_padded_decode_graphs_give_the_same_tokens(tmp_path):
+    """Beyond 8 requests a decode step runs in the graph of the next larger batch size, the rows between
+    being padding that touches no page.  Eleven requests that end one by one: same tokens as without graphs,
+    few graphs, no page left behind."""
+    from return_b200.engine.request import Request
+    d = helpers.make_model_dir(tmp_path, "B")
+    prompts = [helpers.random_ids(384, 5 + 3 * i, 90 + i) for i in range(11)]
+
+    def requests():
+        return [Request(f"p{i}", p, max_new_tokens=4 + 2 * i, temperature=0.0 if i % 2 else 0.9, top_k=30, seed=40 + i)
+                for i, p in enumerate(prompts)]
+
+    plain_steps = _engine(d, "bfloat16", page_size=8, max_reside=12, use_cuda_graph=False).generate(requests())
+    eng = _engine(d, "bfloat16", page_size=8, max_reside=12, use_cuda_graph=True)
+    graphed = eng.generate(requests())
+    assert [r.output_ids for r in graphed] == [r.output_ids for r in plain_steps]
+    sizes = sorted({n for n, _ in eng.runner._graphs})
+    assert sizes and set(sizes) <= {1, 2, 3, 4, 5, 6, 7, 8, 12} and 12 in sizes, sizes
+    assert [eng.runner.graph_batch_size(m) for m in (1, 8, 9, 11, 12)] == [1, 8, 12, 12, 12]          # never beyond max_reside
+    assert eng.runner.capture_decode_graphs() >= 9
+    assert eng.runner.manager.pages_used() == [0] * len(eng.runner.manager.groups)
+    eng.runner.manager.check()
+
+
 def test_running_ahead_gives_way_when_pages_run_short(tmp_path):
     """A pool too small for all: the loop that runs ahead stops, the ordinary step preempts, and the
     tokens are still those of plain greedy decoding."""

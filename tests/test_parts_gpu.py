@@ -264,7 +264,7 @@ def test_toy_mixer_with_state_of_its_own(tmp_path):
         steps = helpers.mixed(reqs, max_live=3, portion=6, decode_tail=3, seed=5)
         rp = TraceReplayer(d, "float32", helpers.pool_tokens(steps), page_size=16, max_reside=3)
         st = rp.runner.storage
-        assert len(st.states) == 2 and all(t.shape == (3, 25) for t in st.states.values())
+        assert len(st.states) == 2 and all(t.shape == (3 + 1, 25) for t in st.states.values())   # + the slot of no request
         got = helpers.collect(steps, [None if (lg := rp.run_step(s)) is None else lg.cpu() for s in steps])
         for rid, ids in reqs.items():
             assert (got[rid] - _toy_reference(d, cfg, ids)).abs().max() < 1e-4, rid
