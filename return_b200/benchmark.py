@@ -337,13 +337,12 @@ def run_workload(name: str, layers: int = 0, new: int = 0) -> Dict[str, object]:
     lens = [int(torch.randint(lo, hi + 1, (1,), generator=gen)) for _ in range(w["requests"])]
     pool = sum((n + n_new + 63) // 64 * 64 for n in lens) + 1024
     ecfg = EngineConfig(max_token=pool, max_reside=w["max_reside"], page_size=16, prefill_chunk=w["chunk"], dtype="bfloat16",
-                        max_model_len=w["ctx"], use_cuda_graph=True, seed=w["seed"])
+                        max_model_len=w["ctx"], use_cuda_graph=True, capture_at_start=True, seed=w["seed"])
     runner = ModelRunner.from_random(cfg, ecfg, seed=w["seed"])
     engine = Engine(runner)
     reqs = [Request(f"w{i}", _random_ids(cfg.vocab_size, n, gen), max_new_tokens=n_new, temperature=0.0) for i, n in enumerate(lens)]
-    # start-up, untimed: the decode graphs (as the reference's build_graph does), and one short request
-    # through prefill and a few decode steps
-    runner.capture_decode_graphs()
+    # start-up, untimed: the engine has captured its decode graphs (as the reference's build_graph does);
+    # one short request goes through prefill and a few decode steps
     engine.generate([_random_ids(cfg.vocab_size, 64, gen)], max_new_tokens=4, temperature=0.0)
     torch.cuda.synchronize()
     t0 = time.perf_counter()

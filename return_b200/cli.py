@@ -30,6 +30,8 @@ def _engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--graph", action=argparse.BooleanOptionalAction, default=True,
                    help="replay CUDA graphs for steps that only decode")
+    p.add_argument("--capture-at-start", action="store_true",
+                   help="capture every decode graph before the first request instead of on first use")
     p.add_argument("--seed", type=int, default=0)
 
 
@@ -37,7 +39,7 @@ def _make_engine(args):
     from .engine.config import EngineConfig
     from .engine.engine import Engine
     cfg = EngineConfig(max_token=args.max_token, max_reside=args.max_reside, page_size=args.page_size,
-                       prefill_chunk=args.chunk, dtype=args.dtype, use_cuda_graph=args.graph, seed=args.seed,
+                       prefill_chunk=args.chunk, dtype=args.dtype, use_cuda_graph=args.graph, capture_at_start=args.capture_at_start, seed=args.seed,
                        device=args.device)
     return Engine(args.model, cfg)
 

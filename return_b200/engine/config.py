@@ -4,7 +4,9 @@
 ``max_reside`` most requests that hold cache at a time = largest batch (rollout/server.py:90);
 ``page_size``  token slots per page (PAGE_SIZE, rollout/constant.py:1; 64 there, 16 here);
 ``prefill_chunk`` most tokens one step runs (PREFILL_CHUNK, rollout/constant.py:5);
-``use_cuda_graph`` replay captured graphs for steps that only decode (USE_CUDA_GRAPH, :3).
+``use_cuda_graph`` replay captured graphs for steps that only decode (USE_CUDA_GRAPH, :3);
+``capture_at_start`` capture them all when the engine is built, as the reference does
+(rollout/model.py:346-407), instead of each on its first use.
 """
 from __future__ import annotations
 
@@ -23,6 +25,7 @@ class EngineConfig:
     dtype: str = "bfloat16"               # "bfloat16" | "float32"
     max_model_len: Optional[int] = None   # longest sequence; default min(max_position_embeddings, max_token)
     use_cuda_graph: bool = True
+    capture_at_start: bool = False
     seed: int = 0
     device: str = "cuda:0"
 

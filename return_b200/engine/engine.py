@@ -37,6 +37,8 @@ class Engine:
             self.runner = ModelRunner.from_model_dir(model, self.config)
         self.scheduler = Scheduler(self.runner.manager, self.config.prefill_chunk, self.runner.max_positions)
         self.sampler = Sampler(self.runner.env.device, max(16, self.config.max_reside))
+        if self.config.capture_at_start and self.runner.runs_ahead():
+            self.runner.capture_decode_graphs()
         self._t_start = time.perf_counter()
         self._acc_decode = self._acc_prefill = 0.0
         self._dc_tok = self._pf_tok = 0
