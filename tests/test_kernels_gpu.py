@@ -499,9 +499,10 @@ def test_one_far_key_stands_out_and_the_windows_edge_is_exact(dtype, q_len, D, P
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("Hq,Hkv,D,P,rot", [(4, 2, 16, 16, 16), (6, 3, 32, 8, 32), (5, 1, 48, 16, 48), (3, 1, 80, 4, 32),
-                                             (32, 8, 128, 16, 128)])
+                                             (32, 8, 128, 16, 128), (6, 2, 64, 8, 64), (3, 1, 256, 16, 256), (9, 3, 128, 16, 64)])
 @pytest.mark.parametrize("with_norm", [True, False])
-@pytest.mark.parametrize("long_first", [20, 1200])      # many tokens take the form with four heads a warp
+@pytest.mark.parametrize("long_first", [20, 1200, 3000])  # many tokens take the forms with several heads a warp (16-byte pieces
+                                                          # for bfloat16 heads of 64, 128, 256 rotated over their whole width)
 def test_qk_norm_rope_write(dtype, Hq, Hkv, D, P, rot, with_norm, long_first):
     ops = _ops()
     g = torch.Generator().manual_seed(D)
