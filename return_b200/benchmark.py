@@ -271,14 +271,24 @@ def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[st
 
 def probe_tc5_rate(iters=2000) -> Dict[str, object]:
     """Cycles per ``tcgen05.mma`` (M x N x 16, bf16, operands in shared memory) for one and two issuing
-    threads of a CTA, on every SM."""
+    threads of a CTA, on every SM; then, for N = 128, with B as an MN-major operand and with the other warps
+    writing to shared memory meanwhile, and the MMA mix of one key tile of the prefill attention kernel."""
     import ctypes
     from .ext import build
     lib = build.load("return_probes", ["probes.cu"])
-    lib.rb_probe_tc5_rate.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 2
+    lib.rb_probe_tc5_rate.argtypes = [ctypes.c_int] * 6 + [ctypes.c_void_p] * 2
     lib.rb_probe_tc5_rate.restype = ctypes.c_int
     dev = torch.device("cuda:0")
-    cyc = torch.zeros(8, dtype=torch.int64, device=dev)
+    cyc = torch.zeros(16, dtype=torch.int64, device=dev)
+
+    def run(M, N, threads, mode):
+        cyc.zero_()
+        rc = lib.rb_probe_tc5_rate(148, M, N, iters, threads, mode, ctypes.c_void_p(cyc.data_ptr()),
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+        torch.cuda.synchronize()
+        return float(cyc[1].item()) / iters, int(cyc[8].item())
+
     rows = []
     for M in (128, 64):
         for N in (16, 64, 128, 256):
@@ -286,15 +296,38 @@ def probe_tc5_rate(iters=2000) -> Dict[str, object]:
             for threads in (1, 2):
                 if threads * N > 512:
                     continue
-                rc = lib.rb_probe_tc5_rate(148, M, N, iters, threads, ctypes.c_void_p(cyc.data_ptr()),
-                                           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-                assert rc == 0
-                torch.cuda.synchronize()
-                per = float(cyc[1].item()) / iters
+                per, _ = run(M, N, threads, 0)
                 row[f"cycles_per_mma_{threads}thread"] = round(per, 1)
                 row[f"tflops_{threads}thread"] = round(threads * 2.0 * M * N * 16 / per * 148 * 1.9e9 / 1e12)
             rows.append(row)
-    return {"probe": "tc5_rate", "rows": rows}
+    variants = []
+    for name, N, mode in (("128x128x16, B K-major", 128, 0), ("128x128x16, B MN-major", 128, 1),
+                          ("128x128x16, B K-major, other warps storing", 128, 2),
+                          ("128x128x16, B MN-major, other warps storing", 128, 3),
+                          ("128x64x16, other warps storing", 64, 2),
+                          ("key tile of the attention kernel (16 S + 8 PV MMAs)", 128, 4),
+                          ("key tile of the attention kernel, other warps storing", 128, 6),
+                          ("key tile of the attention kernel with its six commits", 128, 12),
+                          ("key tile of the attention kernel, ten other warps polling a barrier", 128, 20)):
+        per, stored = run(128, N, 1, mode)
+        v = {"case": name, "cycles": round(per, 1)}
+        if stored:
+            v["stored_bytes_per_cycle"] = round(stored / (per * iters), 1)
+        variants.append(v)
+    for name, mode in (("tcgen05.commit to a barrier and the wait for it, nothing in flight", 32),
+                       ("one 128x64x16 MMA, commit, wait", 33),
+                       ("a token handed between two warps and back (arrive, wait, arrive, wait)", 64),
+                       ("thread time of a tcgen05.commit, back to back", 65),
+                       ("thread time of a barrier wait that succeeds at once", 66),
+                       ("thread time of tcgen05.fence::after_thread_sync", 67),
+                       ("key tile of the attention kernel with four waits and fences in the issuing thread", 100),
+                       ("key tile with four waits, no fences, in the issuing thread", 101),
+                       ("key tile, another warp waiting and fencing in a loop meanwhile", 102),
+                       ("thread time of one mbarrier.test_wait (complete phase)", 68),
+                       ("thread time of one mbarrier.try_wait.relaxed.cta (complete phase)", 69)):
+        per, _ = run(128, 64, 1, mode)
+        variants.append({"case": name, "cycles": round(per, 1)})
+    return {"probe": "tc5_rate", "rows": rows, "variants": variants}
 
 
 # ------------------------------------------------------------------------------- named workloads through the engine

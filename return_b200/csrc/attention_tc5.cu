@@ -13,16 +13,25 @@
 //   O += P V      tcgen05.mma, M = 128, N = head dim, V as it lies in the cache (rows = keys): an
 //                 MN-major B operand.
 // While the rows of A work on their scores, the tensor core computes B's, and so on in turn.
-// Eleven warps with fixed roles, tied together by mbarriers (every wait bounded, tc5.cuh):
+// Twelve warps with fixed roles, tied together by mbarriers (every wait bounded, tc5.cuh):
 //   warps 0-3  the rows of query tile A, warps 4-7 those of B;
-//   warp 8     one thread issues every MMA, with descriptors that are a base plus a constant;
+//   warp 8     one thread issues A's MMAs, warp 11 one thread B's, with descriptors that are a base plus a
+//              constant.  An issuing thread is stopped while its MMAs wait for the tensor pipe, and pays some
+//              230 cycles for every barrier wait, even one that succeeds at once, and 90 for every commit
+//              (profiles/tcgen05_mma_rate.md), all of which adds up in one thread; so a key tile costs each of
+//              the two threads two waits and two commits and no more: K(u) and V(u - 1) arrive on one barrier,
+//              and the commits that tell the rows that S is there and that P V is done free the K and V
+//              stages for the loaders as well;
 //   warp 9     gathers K tiles, warp 10 V tiles, page by page with cp.async into the
 //              128-byte-swizzled layout the MMA reads, through rings of three tiles each so that a
 //              tile is asked for two tiles before it is needed (keys outside the visible range, or on
 //              a page that was given back, are zero-filled, never read).
-// Every barrier has one line of waiters that take each of its phases in turn, and its next phase
-// needs them to have passed the current one: no parity wait can fall two phases behind.
-// 192 KB of shared memory and all 512 TMEM columns a CTA (head size 128).  Same contract as the
+// P has two buffers a query tile, so the exponentials of tile t run while P V(t - 1) does; the rows wait for
+// P V(t - 1) itself only when they have to rescale O.
+// Every barrier's next phase needs all its waiters to have passed the current one: no parity wait can fall two
+// phases behind.  That is why the barriers that a query tile's P and P V use come in pairs (tile & 1), and why
+// a loader announces tile t - 1 only after it has waited for the stage of tile t.
+// 224 KB of shared memory and all 512 TMEM columns a CTA (head size 128).  Same contract as the
 // reference's prefill kernel (rollout/attention.py:45-142) and as attention_mma.cu; keys arrive
 // rotated, tiles are aligned to absolute positions, a sliding window bounds the keys from below.
 // A step with too few such CTAs to fill the GPU (a short portion of a long prompt) splits the keys of every
@@ -31,6 +40,13 @@
 // *status is raised if a wait gave up.
 #include "tc5.cuh"
 
+// RB_AT_TRACE (tuning builds only): the first CTA stores the clock at the events of its first 256 key tiles into
+// status[64 + event * 256 + tile]; the caller then has to give a status buffer of 64 + 24 * 256 ints.
+#ifdef RB_AT_TRACE
+#define AT_STAMP(ev, t) do { if (trace_on && (t) < 256) status[64 + (ev) * 256 + (t)] = (int)clock64(); } while (0)
+#else
+#define AT_STAMP(ev, t) do {} while (0)
+#endif
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=64 or -DHEAD_DIM=128"
 #endif
@@ -46,23 +62,27 @@ constexpr int QM = 128;                       // rows of a query tile
 constexpr int NQ = 2;                         // query tiles per CTA
 constexpr int KN = 64;                        // keys per tile
 constexpr int STAGES = 3;                     // K tiles, and V tiles, in flight
-constexpr int THREADS = 352;                  // warps 0..3: tile A's rows; 4..7: tile B's; 8: MMA; 9: K loader; 10: V loader
-constexpr int W_MMA = 8, W_K = 9;
+constexpr int THREADS = 384;                  // warps 0..3: tile A's rows; 4..7: tile B's; 8: A's MMAs; 9: K loader; 10: V loader; 11: B's MMAs
+constexpr int W_MMA = 8, W_K = 9, W_V = 10, W_MMA_B = 11;
 constexpr float RESCALE_STEP = 8.0f;          // log2 units the true maximum may run ahead of the reference
 constexpr unsigned Q_BYTES = DS * QM * 128, K_BYTES = DS * KN * 128, P_BYTES = QM * 128;
-constexpr unsigned SMEM_USED = NQ * Q_BYTES + 2 * STAGES * K_BYTES + NQ * P_BYTES + 512;
+constexpr unsigned SMEM_USED = NQ * Q_BYTES + 2 * STAGES * K_BYTES + 2 * NQ * P_BYTES + 512;
 // a CTA takes all of an SM's tensor memory, so it asks for more than half of its shared memory too
 constexpr unsigned SMEM_BYTES = SMEM_USED > 120 * 1024 ? SMEM_USED : 120 * 1024;
 constexpr unsigned TMEM_COLS = 512;           // S: 2 query tiles x 2 buffers x 64 columns; O: 2 x HEAD_DIM columns from 256
 constexpr unsigned O_COL = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
-// barriers
-constexpr int B_S_FULL = 0;                   // [query tile][buffer]: 4
-constexpr int B_K_FULL = 4, B_K_FREE = 7, B_V_FULL = 10, B_V_FREE = 13;       // [stage]: 3 each
-constexpr int B_P_READY = 16, B_PV_DONE = 18; // [query tile]: 2 each
-constexpr int B_Q_READY = 20;
-constexpr int N_BARS = 21;
+// barriers.  A thread that issues MMAs pays some 200 cycles for every wait, even one that succeeds at once, 90
+// for every commit and 55 to 90 for every MMA, so each query tile has an issuing thread of its own, with two
+// waits and two commits a key tile.
+constexpr int B_KV_FULL = 0;                  // [stage]: K of tile u and V of tile u - 1 have landed, u % STAGES == stage (the two loaders)
+constexpr int B_S_FULL = 3;                   // [query tile][S buffer]: S is computed (its issuer's commit); also frees the K stage
+constexpr int B_P_READY = 7;                  // [query tile][tile & 1 = P buffer]: P is written (the tile's four warps of rows)
+constexpr int B_PV_DONE = 11;                 // [query tile][tile & 1]: P V is done (its issuer's commit); also frees the V stage
+constexpr int B_Q_READY = 15;
+constexpr int N_BARS = 16;
+static_assert(STAGES == 3, "the barrier numbering above is for rings of three");
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -107,8 +127,8 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     unsigned char* sQ = smem_raw;                         // [query tile]
     unsigned char* sK = sQ + NQ * Q_BYTES;                // [stage]
     unsigned char* sV = sK + STAGES * K_BYTES;            // [stage]
-    unsigned char* sP = sV + STAGES * K_BYTES;            // [query tile]
-    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + NQ * P_BYTES);
+    unsigned char* sP = sV + STAGES * K_BYTES;            // [query tile][P buffer]
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(sP + 2 * NQ * P_BYTES);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 32);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -143,7 +163,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     if (warp == W_MMA) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     if (tid == 0) {
         for (int i = 0; i < N_BARS; ++i)
-            mbar_init(bar(i), i == B_P_READY || i == B_P_READY + 1 ? QM : i == B_Q_READY ? NQ * QM : 1);
+            mbar_init(bar(i), i < B_KV_FULL + STAGES ? 2 : i >= B_P_READY && i < B_P_READY + 2 * NQ ? 4 : i == B_Q_READY ? NQ * 4 : 1);
         mbar_init_fence();
     }
     fence_before_sync();
@@ -151,6 +171,9 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     fence_after_sync();
     const unsigned tmem = *tmem_slot;
     bool ok = true;
+#ifdef RB_AT_TRACE
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 128 || lane == 0);
+#endif
 
     if (warp < 2 * 4) {
         // ================================================================== one query row per thread
@@ -163,7 +186,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         const int p0_t = p0 + qt * QM, p_last_t = min(p_last, p0_t + QM - 1);      // the tile's first and last position
         const bool full_tile = m_rows >= (qt + 1) * QM;
         unsigned char* myQ = sQ + qt * Q_BYTES;
-        unsigned char* myP = sP + qt * P_BYTES;
+        unsigned char* myPs = sP + qt * 2 * P_BYTES;           // this query tile's two P buffers
         {
             const bf16* qrow = q + (size_t)(q_begin + row0 + grow) * ld + (size_t)h * D;
 #pragma unroll
@@ -174,7 +197,8 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             }
         }
         fence_proxy_async();
-        mbar_arrive(bar(B_Q_READY));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_Q_READY));
 
         float m_ref = -INFINITY, l_run = 0.f;                // the reference maximum and the sum relative to it
         const unsigned lane_addr = tmem + ((unsigned)((warp & 3) * 32) << 16);
@@ -183,6 +207,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             const int j_base = (jt_begin + t) * KN;
             ok = mbar_wait(bar(B_S_FULL + qt * 2 + (t & 1)), (t >> 1) & 1) && ok;
             fence_after_sync();
+            if ((tid & 127) == 0) AT_STAMP(8 + qt * 4, t);
             const bool all_visible = full_tile && j_base + KN - 1 <= p0_t && (window <= 0 || j_base > p_last_t - window);
             unsigned a[64];
             tmem_ld32(lane_addr + (qt * 2 + (t & 1)) * KN, reinterpret_cast<unsigned(&)[32]>(a[0]));
@@ -211,10 +236,16 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 moved = true;
             }
             const float mu = m_ref == -INFINITY ? 0.f : m_ref;
+            if ((tid & 127) == 0) AT_STAMP(9 + qt * 4, t);
 
-            if (t > 0) ok = mbar_wait(bar(B_PV_DONE + qt), (t - 1) & 1) && ok;     // O and the P buffer are free
-            fence_after_sync();
+            // P(t) goes into the buffer that P V(t - 2) read, so the exponentials of this tile run while P V(t - 1)
+            // does; O may only be touched when P V(t - 1) is done too, which the rows wait for only when they
+            // have to rescale it.  Tile t's P V commits to barrier [t & 1], phase t >> 1.
+            if (t >= 2) ok = mbar_wait(bar(B_PV_DONE + qt * 2 + (t & 1)), ((t >> 1) - 1) & 1) && ok;
+            if ((tid & 127) == 0) AT_STAMP(10 + qt * 4, t);
             if (t > 0 && __any_sync(0xffffffffu, moved)) {                  // rescale this row of O in tensor memory
+                ok = mbar_wait(bar(B_PV_DONE + qt * 2 + ((t - 1) & 1)), ((t - 1) >> 1) & 1) && ok;
+                fence_after_sync();
 #pragma unroll 1
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     unsigned o[32];
@@ -226,6 +257,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 }
                 tmem_st_wait();
             }
+            unsigned char* myP = myPs + (t & 1) * P_BYTES;
             // p = 2^(scale * s - m), summed in float32, rounded to bfloat16 into the A operand of P V
             float sum = 0.f;
 #pragma unroll
@@ -248,10 +280,12 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             l_run = l_run * alpha + sum;
             fence_proxy_async();
             fence_before_sync();
-            mbar_arrive(bar(B_P_READY + qt));              // S(t) is read, O is rescaled, P(t) is written
+            if ((tid & 127) == 0) AT_STAMP(11 + qt * 4, t);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_P_READY + qt * 2 + (t & 1)));      // S(t) is read, O is rescaled, P(t) is written
         }
         if (n_mine > 0) {
-            ok = mbar_wait(bar(B_PV_DONE + qt), (n_mine - 1) & 1) && ok;
+            ok = mbar_wait(bar(B_PV_DONE + qt * 2 + ((n_mine - 1) & 1)), ((n_mine - 1) >> 1) & 1) && ok;
             fence_after_sync();
         }
         const size_t token = (size_t)(q_begin + row0 + grow);
@@ -299,60 +333,66 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 }
             }
         }
-    } else if (warp == W_MMA) {
-        if (lane == 0 && n_tiles > 0) {
-            // ============================================================== the MMA issuer
-            // One thread's instruction latency is the pace of the tensor core here, so every descriptor is
-            // a base worked out once plus a constant.
+    } else if (warp == W_MMA || warp == W_MMA_B) {
+        const int qt = warp == W_MMA ? 0 : 1;
+        const int n_q = qt == 0 ? n_a : n_b;                 // key tiles of this query tile: the first n_q of the CTA's
+        if (lane == 0 && n_q > 0) {
+            // ============================================================== the MMA issuer of one query tile
+            // One thread's instruction latency is its pace, so every descriptor is a base worked out once plus a
+            // constant, and stage, buffer and parity of the tile being issued are kept as running values.
             const unsigned idesc_s = instr_desc_bf16(QM, KN, false);
             const unsigned idesc_o = instr_desc_bf16(QM, D, true);
-            const unsigned long long dQ = smem_desc_sw128(smem_u32(sQ), 0), dK = smem_desc_sw128(smem_u32(sK), 0);
-            const unsigned long long dP = smem_desc_sw128(smem_u32(sP), 0);
+            const unsigned long long q_tile = smem_desc_sw128(smem_u32(sQ) + qt * Q_BYTES, 0), dK = smem_desc_sw128(smem_u32(sK), 0);
+            const unsigned long long dP = smem_desc_sw128(smem_u32(sP) + qt * 2 * P_BYTES, 0);
             const unsigned long long dV = smem_desc_sw128_mn(smem_u32(sV), KN * 128, 1024u);
-            auto issue_s = [&](int t) {                    // S(t) = Q K(t)^T for both query tiles
-                const int st = t % STAGES;
-                ok = mbar_wait(bar(B_K_FULL + st), (t / STAGES) & 1) && ok;
+            const unsigned d_o = tmem + O_COL + qt * D;
+            unsigned long long k_tile = dK, v_tile = dV;   // descriptors of the K stage of S's tile and the V stage of P V's tile
+            unsigned kv_full = bar(B_KV_FULL), kv_par = 0;
+            int kv_st = 0, v_st = 0;
+            unsigned s_buf = 0;                            // S buffer of the tile being issued: u & 1
+            // S(u) = Q K(u)^T once K(u) has landed; V(u - 1) has landed then too.  For u = n_q only the wait is left.
+            auto issue_s = [&](int u) {
+                ok = mbar_wait(kv_full, kv_par) && ok;
                 fence_after_sync();
-                const unsigned long long k_tile = dK + (unsigned long long)(st * (K_BYTES >> 4));
+                if (u < n_q) {
+                    const unsigned d_s = tmem + (qt * 2 + s_buf) * KN;
 #pragma unroll
-                for (int qt = 0; qt < NQ; ++qt) {
-                    if (t < (qt == 0 ? n_a : n_b)) {
-                        const unsigned d_s = tmem + (qt * 2 + (t & 1)) * KN;
-                        const unsigned long long q_tile = dQ + (unsigned long long)(qt * (Q_BYTES >> 4));
-#pragma unroll
-                        for (int d16 = 0; d16 < D / 16; ++d16)     // 64-wide slabs of the head dim, four steps of 16 (32 bytes) in each
-                            mma_ss(d_s, q_tile + (unsigned long long)(((d16 >> 2) * (QM * 128) + (d16 & 3) * 32) >> 4),
-                                   k_tile + (unsigned long long)(((d16 >> 2) * (KN * 128) + (d16 & 3) * 32) >> 4), idesc_s, d16 > 0);
-                        mma_commit(bar(B_S_FULL + qt * 2 + (t & 1)));
-                    }
+                    for (int d16 = 0; d16 < D / 16; ++d16)     // 64-wide slabs of the head dim, four steps of 16 (32 bytes) in each
+                        mma_ss(d_s, q_tile + (unsigned long long)(((d16 >> 2) * (QM * 128) + (d16 & 3) * 32) >> 4),
+                               k_tile + (unsigned long long)(((d16 >> 2) * (KN * 128) + (d16 & 3) * 32) >> 4), idesc_s, d16 > 0);
+                    mma_commit(bar(B_S_FULL + qt * 2) + 8u * s_buf);    // the rows may read S; the K loader may reuse the stage
+                    s_buf ^= 1u;
                 }
-                mma_commit(bar(B_K_FREE + st));            // the K tile is free once these products have read it
+                if (++kv_st == STAGES) {
+                    kv_st = 0; kv_par ^= 1u;
+                    k_tile = dK; kv_full = bar(B_KV_FULL);
+                } else {
+                    k_tile += (unsigned long long)(K_BYTES >> 4); kv_full += 8u;
+                }
             };
             ok = mbar_wait(bar(B_Q_READY), 0) && ok;
             fence_after_sync();
             issue_s(0);
-            for (int t = 0; t < n_tiles; ++t) {
-                // S(t+1) goes into the buffers that S(t-1) used: their rows were read before P(t-1) was ready
-                if (t + 1 < n_tiles) issue_s(t + 1);
-                const int st = t % STAGES;
-                ok = mbar_wait(bar(B_V_FULL + st), (t / STAGES) & 1) && ok;
-                const unsigned long long v_tile = dV + (unsigned long long)(st * (K_BYTES >> 4));
+            unsigned p_par = 0;
+            for (int t = 0; t < n_q; ++t) {
+                // S(t+1) goes into the buffer that S(t-1) used: its rows were read before P(t-1) was ready
+                if (qt == 0) AT_STAMP(0, t);
+                issue_s(t + 1);
+                if (qt == 0) AT_STAMP(2, t);
+                ok = mbar_wait(bar(B_P_READY + qt * 2) + 8u * (unsigned)(t & 1), p_par) && ok;
+                fence_after_sync();
+                if (qt == 0) AT_STAMP(4, t);
+                const unsigned long long p_tile = dP + (unsigned long long)((t & 1) * (P_BYTES >> 4));
+                if (t == 0) mma_ss(d_o, p_tile, v_tile, idesc_o, false);
+                else mma_ss(d_o, p_tile, v_tile, idesc_o, true);
 #pragma unroll
-                for (int qt = 0; qt < NQ; ++qt) {
-                    if (t < (qt == 0 ? n_a : n_b)) {
-                        ok = mbar_wait(bar(B_P_READY + qt), t & 1) && ok;
-                        fence_after_sync();
-                        const unsigned d_o = tmem + O_COL + qt * D;
-                        const unsigned long long p_tile = dP + (unsigned long long)(qt * (P_BYTES >> 4));
-                        if (t == 0) mma_ss(d_o, p_tile, v_tile, idesc_o, false);
-                        else mma_ss(d_o, p_tile, v_tile, idesc_o, true);
-#pragma unroll
-                        for (int k16 = 1; k16 < KN / 16; ++k16)    // 16 keys: 32 bytes along P's rows, 2048 bytes down V's
-                            mma_ss(d_o, p_tile + (unsigned long long)(k16 * 2), v_tile + (unsigned long long)(k16 * 128), idesc_o, true);
-                        mma_commit(bar(B_PV_DONE + qt));
-                    }
-                }
-                mma_commit(bar(B_V_FREE + st));
+                for (int k16 = 1; k16 < KN / 16; ++k16)    // 16 keys: 32 bytes along P's rows, 2048 bytes down V's
+                    mma_ss(d_o, p_tile + (unsigned long long)(k16 * 2), v_tile + (unsigned long long)(k16 * 128), idesc_o, true);
+                mma_commit(bar(B_PV_DONE + qt * 2) + 8u * (unsigned)(t & 1));      // the rows may touch O and P; the V loader may reuse the stage
+                if (qt == 0) AT_STAMP(7, t);
+                p_par ^= (unsigned)(t & 1);                 // each of the two barriers has a phase every other tile
+                if (++v_st == STAGES) { v_st = 0; v_tile = dV; }
+                else v_tile += (unsigned long long)(K_BYTES >> 4);
             }
         }
     } else {
@@ -360,11 +400,19 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         const bool is_k = warp == W_K;
         const bf16* pool = is_k ? kpool : vpool;
         const unsigned bufs = smem_u32(is_k ? sK : sV);
-        const int b_full = is_k ? B_K_FULL : B_V_FULL, b_free = is_k ? B_K_FREE : B_V_FREE;
         if (n_tiles > 0) {
+        // K(u) and V(u - 1) arrive on the same barrier, stage u % STAGES; "V(-1)" and "K(n_tiles)" stand in at the ends.
+        if (!is_k && lane == 0) mbar_arrive(bar(B_KV_FULL));
+        int st = 0;
         for (int t = 0; t < n_tiles; ++t) {
-            const int st = t % STAGES;
-            if (t >= STAGES) ok = mbar_wait(bar(b_free + st), ((t / STAGES) - 1) & 1) && ok;
+            if (t >= STAGES) {
+                // the stage held tile t - 3: its keys are free when S(t - 3) is computed, its values when P V(t - 3) is done
+                const int f = t - STAGES;
+                const int b_free = is_k ? B_S_FULL : B_PV_DONE;
+                if (f < n_a) ok = mbar_wait(bar(b_free + (f & 1)), (f >> 1) & 1) && ok;
+                if (f < n_b) ok = mbar_wait(bar(b_free + 2 + (f & 1)), (f >> 1) & 1) && ok;
+            }
+            AT_STAMP(16 + (is_k ? 0 : 3), t);
             const unsigned tile_smem = bufs + st * K_BYTES;
             const int jt = jt_begin + t;
             // A lane gathers two whole rows: one look-up each, then copies at constant offsets.
@@ -386,17 +434,28 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                     cp_async16(dst + (cc >> 3) * (KN * 128) + ((((unsigned)cc & 7u) ^ x) << 4), src + cc * 8, pred);
             }
             cp_async_commit();
-            if (t > 0) {                                   // tile t is on its way; tile t - 1 has to have landed
+            AT_STAMP(17 + (is_k ? 0 : 3), t);
+            // tile t is on its way; tile t - 1 has to have landed.  It is announced only now, after the wait for
+            // the stage above: the product that completes the next phase of that wait's barrier needs this
+            // announcement, so the wait cannot fall a phase behind.
+            const int st_prev = st == 0 ? STAGES - 1 : st - 1;      // stage of tile t - 1
+            if (t > 0) {
                 cp_async_wait<1>();
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(b_full + (t - 1) % STAGES));
+                if (lane == 0) mbar_arrive(bar(B_KV_FULL + (is_k ? st_prev : st)));      // K(t-1): its own stage; V(t-1): the stage of K(t)
             }
+            AT_STAMP(18 + (is_k ? 0 : 3), t);
+            st = st + 1 == STAGES ? 0 : st + 1;
         }
         cp_async_wait<0>();
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(b_full + (n_tiles - 1) % STAGES));
+        if (lane == 0) {
+            const int st_last = st == 0 ? STAGES - 1 : st - 1;      // stage of the last tile; st is that of "tile n_tiles"
+            mbar_arrive(bar(B_KV_FULL + (is_k ? st_last : st)));
+            if (is_k) mbar_arrive(bar(B_KV_FULL + st));
+        }
         }
     }
     if (!ok) atomicExch(status, 1);

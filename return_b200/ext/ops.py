@@ -105,7 +105,7 @@ def build_all():
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
     paths.append(build.library_path("return_tc5", _TC5_SOURCES, _tc5_defines()))
     for d in TC5_ATTENTION_HEAD_DIMS:
-        paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], {"HEAD_DIM": d}))
+        paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], _attn_tc5_defines(d)))
     for d in PREBUILT_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_d{d}", ["attention_mma.cu"], _attn_defines(d)))
     return paths
@@ -410,13 +410,22 @@ TC5_TILE_ROWS = 256            # query rows of one CTA of the tcgen05 prefill at
 NUM_SMS = 148
 
 
+def _attn_tc5_defines(head_dim: int):
+    """Build options of the tcgen05 attention library; RETURN_B200_ATTN_TC5_DEFS="NAME=1" adds tuning macros."""
+    defs = {"HEAD_DIM": head_dim}
+    for item in filter(None, _os.environ.get("RETURN_B200_ATTN_TC5_DEFS", "").split(",")):
+        k, _, v = item.partition("=")
+        defs[k.strip()] = v.strip() or "1"
+    return defs
+
+
 def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
     """The tcgen05 prefill attention kernel, compiled for this head size (64 or 128) on first use."""
     lib = _attn_tc5_libs.get(head_dim)
     if lib is None:
         if head_dim not in TC5_ATTENTION_HEAD_DIMS:
             raise KernelError(f"head_dim={head_dim}: the tcgen05 attention kernel takes {TC5_ATTENTION_HEAD_DIMS}")
-        lib = build.load(f"return_attn_tc5_d{head_dim}", ["attention_tc5.cu"], {"HEAD_DIM": head_dim})
+        lib = build.load(f"return_attn_tc5_d{head_dim}", ["attention_tc5.cu"], _attn_tc5_defines(head_dim))
         P, I, F = c_void_p, c_int, c_float
         lib.rb_attn_prefill_tc5.argtypes = [P, I, P, P, P, I, P, P, P, I, I, P, I, I, F, I, I, P, I, P, P]
         lib.rb_attn_tc5_split_floats.argtypes = [I, I, I]
