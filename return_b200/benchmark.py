@@ -8,6 +8,7 @@ uniform over the vocabulary (rollout/utils/bench_sym.py:26).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List
 
 import torch
@@ -189,6 +190,56 @@ def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8
     flops = 4.0 * batch * heads * head_dim * (q_len * (ctx - q_len) + q_len * q_len / 2.0)
     return {"kernel": "attention_prefill_mma" if impl else "attention_prefill_tc5", "batch": batch, "ctx": ctx, "q_len": q_len, "splits": 1 if impl else splits,
             "ctas": int(tiles.shape[0]) * heads, "ms": ms, "TFLOPs": flops / ms / 1e9}
+
+
+def kernel_attention_trace(ctx=16384, heads=32, kv_heads=8, head_dim=128, page=16, first=50, last=200) -> Dict[str, object]:
+    """Where the cycles of a key tile go in the tcgen05 prefill attention kernel: a build with -DRB_AT_TRACE=1
+    stores clock64() at the events of the first CTA's first 256 key tiles; this reads them back and gives
+    the mean cycles of each segment over key tiles ``first`` to ``last`` (one prompt of ``ctx`` tokens)."""
+    import numpy as np
+    from .ext import ops
+    _os_environ_defs = os.environ.get("RETURN_B200_ATTN_TC5_DEFS", "")
+    os.environ["RETURN_B200_ATTN_TC5_DEFS"] = ",".join(filter(None, [_os_environ_defs, "RB_AT_TRACE=1"]))
+    ops._attn_tc5_libs.pop(head_dim, None)            # the traced build is another library
+    try:
+        dev = torch.device("cuda:0")
+        qkv, k_pool, v_pool, bt, cu_q, seg_pos0, _ = _paged_case(1, ctx, ctx, heads, kv_heads, head_dim, page, dev)
+        out = torch.empty((ctx, heads * head_dim), dtype=torch.bfloat16, device=dev)
+        tiles = torch.tensor([(0, r) for r in reversed(range(0, ctx, ops.TC5_TILE_ROWS))], dtype=torch.int32, device=dev)
+        trace = torch.zeros(64 + 24 * 256, dtype=torch.int32, device=dev)
+        saved = dict(ops._tc5_status)
+        ops._tc5_status[dev] = trace
+        try:
+            for _ in range(2):
+                ops.attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, bt, page, out, heads, kv_heads,
+                                          head_dim, head_dim ** -0.5, 0)
+            torch.cuda.synchronize()
+        finally:
+            ops._tc5_status.clear()
+            ops._tc5_status.update(saved)
+        w = trace.cpu().numpy().astype(np.int64)
+    finally:
+        os.environ["RETURN_B200_ATTN_TC5_DEFS"] = _os_environ_defs
+        ops._attn_tc5_libs.pop(head_dim, None)
+    if w[0] != 0:
+        raise RuntimeError("a bounded wait inside the kernel gave up")
+    events = {"issuer_top": 0, "issuer_s_issued": 2, "issuer_p_got": 4, "issuer_pv_issued": 7,
+              "rowA_s_got": 8, "rowA_max_known": 9, "rowA_p_buffer_free": 10, "rowA_p_written": 11,
+              "rowB_s_got": 12, "rowB_max_known": 13, "rowB_p_buffer_free": 14, "rowB_p_written": 15,
+              "k_stage_free": 16, "k_issued": 17, "k_announced": 18, "v_stage_free": 19, "v_issued": 20, "v_announced": 21}
+    ev = {n: w[64 + i * 256 + first: 64 + i * 256 + last] for n, i in events.items()}
+    delta = lambda x: ((x + 2 ** 31) % 2 ** 32) - 2 ** 31          # the stamps are the low 32 bits of the clock
+    seg = lambda a, b: round(float(np.mean(delta(ev[b] - ev[a]))), 1)
+    return {"kernel": "attention_prefill_tc5 (traced build)", "ctx": ctx, "tiles": [first, last],
+            "cycles_per_key_tile": round(float(np.mean(delta(np.diff(ev["issuer_top"])))), 1),
+            "issuer_A": {"wait_kv_and_8_S_mmas": seg("issuer_top", "issuer_s_issued"),
+                         "wait_p": seg("issuer_s_issued", "issuer_p_got"), "4_PV_mmas": seg("issuer_p_got", "issuer_pv_issued")},
+            "row_of_A": {"s_to_max": seg("rowA_s_got", "rowA_max_known"), "wait_p_buffer": seg("rowA_max_known", "rowA_p_buffer_free"),
+                         "exp_and_store": seg("rowA_p_buffer_free", "rowA_p_written")},
+            "row_of_B": {"s_to_max": seg("rowB_s_got", "rowB_max_known"), "wait_p_buffer": seg("rowB_max_known", "rowB_p_buffer_free"),
+                         "exp_and_store": seg("rowB_p_buffer_free", "rowB_p_written")},
+            "k_loader": {"stage_free_to_issued": seg("k_stage_free", "k_issued"), "issued_to_announced": seg("k_issued", "k_announced")},
+            "v_loader": {"stage_free_to_issued": seg("v_stage_free", "v_issued"), "issued_to_announced": seg("v_issued", "v_announced")}}
 
 
 def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> Dict[str, float]:

@@ -102,6 +102,7 @@ def cmd_workload(args) -> int:
 def cmd_kernel_bench(args) -> int:
     from . import benchmark
     fn = {"attention_decode": benchmark.kernel_attention_decode, "attention_prefill": benchmark.kernel_attention_prefill,
+          "attention_trace": benchmark.kernel_attention_trace,
           "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated, "mma_rate": benchmark.probe_mma_rate,
           "tc5_rate": benchmark.probe_tc5_rate}[args.kernel]
     kw = {}
@@ -170,7 +171,7 @@ def main(argv=None) -> int:
     wl.set_defaults(fn=cmd_workload)
 
     k = sub.add_parser("kernel-bench", help="time one kernel alone on random data (for profiles)")
-    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated", "mma_rate", "tc5_rate"])
+    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "attention_trace", "gemm", "gated", "mma_rate", "tc5_rate"])
     k.add_argument("--set", action="append", help="an integer argument of the kernel case, e.g. batch=64 ctx=2048 M=8")
     k.set_defaults(fn=cmd_kernel_bench)
 

@@ -239,9 +239,10 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             if ((tid & 127) == 0) AT_STAMP(9 + qt * 4, t);
 
             // P(t) goes into the buffer that P V(t - 2) read, so the exponentials of this tile run while P V(t - 1)
-            // does; O may only be touched when P V(t - 1) is done too, which the rows wait for only when they
-            // have to rescale it.  Tile t's P V commits to barrier [t & 1], phase t >> 1.
-            if (t >= 2) ok = mbar_wait(bar(B_PV_DONE + qt * 2 + (t & 1)), ((t >> 1) - 1) & 1) && ok;
+            // does.  P V(t - 2) is done: the commit that announced S(t) came from the same thread after it, and
+            // a commit stands for everything that thread issued before.  O may only be touched when P V(t - 1)
+            // is done too, which the rows wait for only when they have to rescale it.  Tile t's P V commits
+            // to barrier [t & 1], phase t >> 1.
             if ((tid & 127) == 0) AT_STAMP(10 + qt * 4, t);
             if (t > 0 && __any_sync(0xffffffffu, moved)) {                  // rescale this row of O in tensor memory
                 ok = mbar_wait(bar(B_PV_DONE + qt * 2 + ((t - 1) & 1)), ((t - 1) >> 1) & 1) && ok;
@@ -404,6 +405,17 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
         // K(u) and V(u - 1) arrive on the same barrier, stage u % STAGES; "V(-1)" and "K(n_tiles)" stand in at the ends.
         if (!is_k && lane == 0) mbar_arrive(bar(B_KV_FULL));
         int st = 0;
+        // The pages of rows `lane` and `lane + 32` of a key tile are asked for one tile ahead and not looked at
+        // until that tile's turn, so the look-up's latency passes while the loader copies and waits.
+        auto ask_pages = [&](int jt, int (&page)[2]) {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int j = jt * KN + u * 32 + lane;
+                page[u] = bt_row[j >= lo_min && j <= p_last ? pg.block(j) : 0];      // entry 0 exists; the range is checked again at use
+            }
+        };
+        int next_page[2];
+        ask_pages(jt_begin, next_page);
         for (int t = 0; t < n_tiles; ++t) {
             if (t >= STAGES) {
                 // the stage held tile t - 3: its keys are free when S(t - 3) is computed, its values when P V(t - 3) is done
@@ -415,25 +427,35 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             AT_STAMP(16 + (is_k ? 0 : 3), t);
             const unsigned tile_smem = bufs + st * K_BYTES;
             const int jt = jt_begin + t;
-            // A lane gathers two whole rows: one look-up each, then copies at constant offsets.
+            // Lane L looks up where rows L and L + 32 of the tile lie (a null pointer: not to be read).  The copies
+            // then go row by row, D / 8 neighbouring lanes taking the 16-byte pieces of one row, so that a
+            // warp's instruction reads whole 128-byte lines; each row's address comes from the lane that
+            // looked it up.  (One lane a row, piece by piece, asked for 32 lines an instruction and took
+            // 1,800 cycles a tile.)
+            unsigned long long where[2];
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
-                const int krow = u * 32 + lane;
-                const int j = jt * KN + krow;
-                bool pred = j >= lo_min && j <= p_last;
-                const bf16* src = pool;
-                if (pred) {
-                    const int page = bt_row[pg.block(j)];
-                    pred = page >= 0;
-                    if (pred) src = pool + (((size_t)page * Hkv + kvh) * pg.page_size + pg.row(j)) * D;
-                }
-                const unsigned dst = tile_smem + (krow >> 3) * 1024 + (krow & 7) * 128;
-                const unsigned x = (unsigned)(krow & 7);
+                const int j = jt * KN + u * 32 + lane;
+                where[u] = 0ull;
+                if (j >= lo_min && j <= p_last && next_page[u] >= 0)
+                    where[u] = reinterpret_cast<unsigned long long>(pool + (((size_t)next_page[u] * Hkv + kvh) * pg.page_size + pg.row(j)) * D);
+            }
+            constexpr int LPR = D / 8, RPI = 32 / LPR;              // lanes a row, rows an instruction
+            const int sub = lane % LPR, rsel = lane / LPR;
+            const unsigned piece = (unsigned)(sub >> 3) * (KN * 128), c7 = (unsigned)(sub & 7);
 #pragma unroll
-                for (int cc = 0; cc < D / 8; ++cc)
-                    cp_async16(dst + (cc >> 3) * (KN * 128) + ((((unsigned)cc & 7u) ^ x) << 4), src + cc * 8, pred);
+            for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                for (int i = 0; i < 32 / RPI; ++i) {
+                    const int owner = i * RPI + rsel;                 // the lane that looked this row up
+                    const int krow = u * 32 + owner;
+                    const unsigned long long w = __shfl_sync(0xffffffffu, where[u], owner);
+                    const bf16* src = w ? reinterpret_cast<const bf16*>(w) + sub * 8 : pool;
+                    cp_async16(tile_smem + (krow >> 3) * 1024 + (krow & 7) * 128 + piece + ((c7 ^ (unsigned)(krow & 7)) << 4), src, w != 0ull);
+                }
             }
             cp_async_commit();
+            if (t + 1 < n_tiles) ask_pages(jt + 1, next_page);
             AT_STAMP(17 + (is_k ? 0 : 3), t);
             // tile t is on its way; tile t - 1 has to have landed.  It is announced only now, after the wait for
             // the stage above: the product that completes the next phase of that wait's barrier needs this
