@@ -54,7 +54,7 @@ RB_EXPORT int rb_probe_mma_rate(int ctas, int warps, int chains, int iters, floa
 // one shape: 2 x 8 MMAs of 128 x 64 x 16 (K-major) and 2 x 4 of 128 x 128 x 16 (B MN-major), `iters` tiles,
 // cycles counted per tile; bit 3 (with bit 2): a tcgen05.commit to a barrier nobody waits on after each of the
 // tile's four groups of MMAs and two more, as the attention kernel has them.  cycles[8] = 16-byte stores the
-// other warps made.  bit 4: the CTA has eleven warps (as the attention kernel) and the ten that issue nothing
+// other warps made.  bit 4: the CTA has eleven warps and the ten that issue nothing
 // wait on a barrier that completes only when the MMAs are done, every thread polling as the kernels' waits do.
 // mode 32: no MMAs; one thread does `iters` rounds of tcgen05.commit to a barrier and a wait for it: cycles a
 // round = what a commit takes to reach its barrier with nothing in flight.  mode 33: the same with one
