@@ -189,25 +189,34 @@ tc5_gemm_bmn_kernel(const bf16* __restrict__ x, const bf16* __restrict__ bmat, f
 }
 
 // ------------------------------------------------------------------------------------ the product kernel
+#ifndef RB_TC5_STAGES                      // tuning builds may choose the ring: stages x k blocks a stage x 48 KB <= 192 KB
+#define RB_TC5_STAGES 4
+#endif
+#ifndef RB_TC5_KPS
+#define RB_TC5_KPS 1
+#endif
 constexpr int TC5_THREADS = 192;          // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
 
 // Persistent: a CTA walks output tiles tile = blockIdx.x, + gridDim.x, ...; tiles that share a block
 // of W are neighbours (the M tile index runs fastest), so W is read from HBM once and X stays in L2.
 // The accumulator is double-buffered in TMEM (2 x BN columns): the epilogue warps drain tile i while
 // the MMA thread fills tile i + 1.  The ring of operand stages runs on across tiles.
-template <int BN, int STAGES, typename TOut, bool GATED>
+// KPS k blocks of 64 make one stage, with one wait and one commit of the issuing thread: a wait costs that
+// thread some 230 cycles even when it succeeds at once and a commit 90, beside 512 cycles for the four MMAs
+// of a k block, and they add up.
+template <int BN, int STAGES, int KPS, typename TOut, bool GATED>
 __global__ void __launch_bounds__(TC5_THREADS)
 tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                 TOut* __restrict__ out, int M, int N, int K, int ldo, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr unsigned A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr unsigned A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, BLOCK_BYTES = A_BYTES + B_BYTES, STAGE_BYTES = KPS * BLOCK_BYTES;
     __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
     __shared__ unsigned tmem_slot;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr unsigned TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     static_assert(2 * BN <= 512, "two accumulators must fit the 512 columns of tensor memory");
-    const int nkb = (K + BK - 1) / BK;
+    const int nkb = (K + BK * KPS - 1) / (BK * KPS);        // stages a tile; k blocks past K are zero-filled by the copy
     const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, tiles = m_tiles * n_tiles;
 
     if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
@@ -238,8 +247,11 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const unsigned full = smem_u32(&full_bar[s]);
                     mbar_arrive_expect_tx(full, STAGE_BYTES);
                     const unsigned dst = smem_u32(base + (size_t)s * STAGE_BYTES);
-                    tma::load_2d(dst, &map_x, kb * BK, m0, full);
-                    tma::load_2d(dst + A_BYTES, &map_w, kb * BK, n0, full);
+#pragma unroll
+                    for (int j = 0; j < KPS; ++j) {
+                        tma::load_2d(dst + j * BLOCK_BYTES, &map_x, (kb * KPS + j) * BK, m0, full);
+                        tma::load_2d(dst + j * BLOCK_BYTES + A_BYTES, &map_w, (kb * KPS + j) * BK, n0, full);
+                    }
                 }
             }
         }
@@ -256,10 +268,14 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                     const int s = it % STAGES;
                     ok = mbar_wait(smem_u32(&full_bar[s]), (it / STAGES) & 1) && ok;
                     fence_after_sync();
-                    const unsigned a = smem_u32(base + (size_t)s * STAGE_BYTES), b = a + A_BYTES;
+                    const unsigned a0 = smem_u32(base + (size_t)s * STAGE_BYTES);
 #pragma unroll
-                    for (int k16 = 0; k16 < BK / 16; ++k16)
-                        mma_ss(d, smem_desc_sw128(a, k16 * 32), smem_desc_sw128(b, k16 * 32), idesc, kb > 0 || k16 > 0);
+                    for (int j = 0; j < KPS; ++j) {
+                        const unsigned a = a0 + j * BLOCK_BYTES, b = a + A_BYTES;
+#pragma unroll
+                        for (int k16 = 0; k16 < BK / 16; ++k16)
+                            mma_ss(d, smem_desc_sw128(a, k16 * 32), smem_desc_sw128(b, k16 * 32), idesc, kb > 0 || j > 0 || k16 > 0);
+                    }
                     mma_commit(smem_u32(&empty_bar[s]));    // the stage is free once these MMAs have read it
                 }
                 mma_commit(smem_u32(&acc_full[buf]));       // this tile's accumulator is complete
@@ -324,15 +340,15 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 }
 
 // ------------------------------------------------------------------------------------ host side
-template <int BN, int STAGES, typename TOut, bool GATED>
+template <int BN, int STAGES, int KPS, typename TOut, bool GATED>
 int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo, int* status,
                cudaStream_t st) {
     CUtensorMap mx, mw;
     if (!tma::make_map_bf16(&mx, x, M, K, ldx, BM) || !tma::make_map_bf16(&mw, w, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
-    const size_t smem = (size_t)STAGES * (BM + BN) * BK * 2 + 1024;
+    const size_t smem = (size_t)STAGES * KPS * (BM + BN) * BK * 2 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN, STAGES, TOut, GATED>,
+        cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN, STAGES, KPS, TOut, GATED>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -345,7 +361,7 @@ int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int
         cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     }
     dim3 grid(tiles < num_sms ? tiles : num_sms);
-    return rb_launch_pdl(tc5_gemm_kernel<BN, STAGES, TOut, GATED>, grid, dim3(TC5_THREADS), smem, st, mx, mw,
+    return rb_launch_pdl(tc5_gemm_kernel<BN, STAGES, KPS, TOut, GATED>, grid, dim3(TC5_THREADS), smem, st, mx, mw,
                          (TOut*)out, M, N, K, ldo, status);
 }
 
@@ -359,10 +375,10 @@ RB_EXPORT int rb_tc5_gemm(const void* x, const void* w, void* out, int out_f32, 
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return (int)cudaErrorInvalidValue;
     if (gated) {
         if (out_f32 || N % 16) return (int)cudaErrorInvalidValue;
-        return launch_tc5<256, 4, bf16, true>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+        return launch_tc5<256, RB_TC5_STAGES, RB_TC5_KPS, bf16, true>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
     }
-    if (out_f32) return launch_tc5<256, 4, float, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
-    return launch_tc5<256, 4, bf16, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    if (out_f32) return launch_tc5<256, RB_TC5_STAGES, RB_TC5_KPS, float, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    return launch_tc5<256, RB_TC5_STAGES, RB_TC5_KPS, bf16, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
 }
 
 RB_EXPORT int rb_tc5_gemm_simple(const void* x, const void* w, void* out, int out_f32, int bn, int M, int N, int K,
