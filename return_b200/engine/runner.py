@@ -25,6 +25,19 @@ from .batch import BatchStaging, StaticDecodeBatch, StepBatch, StepEntry, build_
 from .config import EngineConfig
 
 
+def graph_batch_size(m: int, max_reside: int) -> int:
+    """The batch size of the graph that runs a decode step of ``m`` tokens: ``m`` itself up to 8 (the
+    weight-streaming kernels are compiled per row count), then the next of 12, 16, 24, 32, 48, 64, ...
+    so that requests which end one by one do not each ask for a capture; the rows between are padding.
+    Never more than ``max_reside``."""
+    if m <= 8:
+        return m
+    n = 8
+    while n < m:
+        n += n // 2 if n & (n - 1) == 0 else n // 3
+    return min(n, max(m, max_reside))
+
+
 class ModelRunner:
     def __init__(self, model: DecoderModel, engine_config: EngineConfig, max_positions: int):
         self.model = model
@@ -145,16 +158,7 @@ class ModelRunner:
         return logits.index_select(0, torch.as_tensor(host.want_rows, dtype=torch.int64).to(logits.device))
 
     def graph_batch_size(self, m: int) -> int:
-        """The batch size of the graph that runs a decode step of ``m`` tokens: ``m`` itself up to 8 (the
-        weight-streaming kernels are compiled per row count), then the next of 12, 16, 24, 32, 48, 64, ...
-        so that requests which end one by one do not each ask for a capture; the rows between are padding.
-        Never more than ``max_reside``."""
-        if m <= 8:
-            return m
-        n = 8
-        while n < m:
-            n += n // 2 if n & (n - 1) == 0 else n // 3
-        return min(n, max(m, self.config.max_reside))
+        return graph_batch_size(m, self.config.max_reside)
 
     @staticmethod
     def _span(longest: int) -> int:
