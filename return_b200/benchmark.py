@@ -226,7 +226,8 @@ def kernel_attention_trace(ctx=16384, heads=32, kv_heads=8, head_dim=128, page=1
     events = {"issuer_top": 0, "issuer_s_issued": 2, "issuer_p_got": 4, "issuer_pv_issued": 7,
               "rowA_s_got": 8, "rowA_max_known": 9, "rowA_p_buffer_free": 10, "rowA_p_written": 11,
               "rowB_s_got": 12, "rowB_max_known": 13, "rowB_p_buffer_free": 14, "rowB_p_written": 15,
-              "k_stage_free": 16, "k_issued": 17, "k_announced": 18, "v_stage_free": 19, "v_issued": 20, "v_announced": 21}
+              "k_stage_free": 16, "k_issued": 17, "k_announced": 18, "v_stage_free": 19, "v_issued": 20, "v_announced": 21,
+              "rowA_exp_done": 22, "rowB_exp_done": 23}
     ev = {n: w[64 + i * 256 + first: 64 + i * 256 + last] for n, i in events.items()}
     delta = lambda x: ((x + 2 ** 31) % 2 ** 32) - 2 ** 31          # the stamps are the low 32 bits of the clock
     seg = lambda a, b: round(float(np.mean(delta(ev[b] - ev[a]))), 1)
@@ -235,9 +236,9 @@ def kernel_attention_trace(ctx=16384, heads=32, kv_heads=8, head_dim=128, page=1
             "issuer_A": {"wait_kv_and_8_S_mmas": seg("issuer_top", "issuer_s_issued"),
                          "wait_p": seg("issuer_s_issued", "issuer_p_got"), "4_PV_mmas": seg("issuer_p_got", "issuer_pv_issued")},
             "row_of_A": {"s_to_max": seg("rowA_s_got", "rowA_max_known"), "wait_p_buffer": seg("rowA_max_known", "rowA_p_buffer_free"),
-                         "exp_and_store": seg("rowA_p_buffer_free", "rowA_p_written")},
+                         "exponentials": seg("rowA_p_buffer_free", "rowA_exp_done"), "round_store_fence": seg("rowA_exp_done", "rowA_p_written")},
             "row_of_B": {"s_to_max": seg("rowB_s_got", "rowB_max_known"), "wait_p_buffer": seg("rowB_max_known", "rowB_p_buffer_free"),
-                         "exp_and_store": seg("rowB_p_buffer_free", "rowB_p_written")},
+                         "exponentials": seg("rowB_p_buffer_free", "rowB_exp_done"), "round_store_fence": seg("rowB_exp_done", "rowB_p_written")},
             "k_loader": {"stage_free_to_issued": seg("k_stage_free", "k_issued"), "issued_to_announced": seg("k_issued", "k_announced")},
             "v_loader": {"stage_free_to_issued": seg("v_stage_free", "v_issued"), "issued_to_announced": seg("v_issued", "v_announced")}}
 

@@ -89,6 +89,31 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
 }
+// Two float32 operations an instruction (fma.rn.f32x2, add.rn.f32x2) and the three-input maximum: the rows are
+// bound by the instructions they issue, and these halve the count of the arithmetic around the exponentials.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ void cp_async16(unsigned smem_addr, const void* gmem, bool pred) {
     const int bytes = pred ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(bytes));
@@ -216,7 +241,7 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             float mx = -INFINITY;
             if (all_visible) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(a[i]));
+                for (int i = 0; i < 64; i += 2) mx = max3(mx, __uint_as_float(a[i]), __uint_as_float(a[i + 1]));
             } else {
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
@@ -260,13 +285,21 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             }
             unsigned char* myP = myPs + (t & 1) * P_BYTES;
             // p = 2^(scale * s - m), summed in float32, rounded to bfloat16 into the A operand of P V
-            float sum = 0.f;
+            const unsigned long long scale2 = pack2(scale_log2, scale_log2), shift2 = pack2(-mu, -mu);
+            unsigned long long sum2 = pack2(0.f, 0.f);
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float pv = fast_exp2(fmaf(__uint_as_float(a[i]), scale_log2, -mu));
-                sum += pv;
-                a[i] = __float_as_uint(pv);
+            for (int i = 0; i < 64; i += 2) {
+                float x0, x1;
+                unpack2(fma2(pack2(__uint_as_float(a[i]), __uint_as_float(a[i + 1])), scale2, shift2), x0, x1);
+                const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                sum2 = add2(sum2, pack2(p0, p1));
+                a[i] = __float_as_uint(p0);
+                a[i + 1] = __float_as_uint(p1);
             }
+            float sum_lo, sum_hi;
+            unpack2(sum2, sum_lo, sum_hi);
+            const float sum = sum_lo + sum_hi;
+            if ((tid & 127) == 0) AT_STAMP(22 + qt, t);
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint4 v;
