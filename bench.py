@@ -76,10 +76,10 @@ class ClockSampler:
 
 
 def run_reference(args):
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "wenhaoli-xmu/ReTurn has no setup.py or pyproject.toml: pip install --target baseline/_ref "
-                      "answers 'Directory is not installable', so there is no offline install to run"}))
-    return 0
+    """The reference's own engine on the same metric (baseline/reference_arm.py); nothing of return_b200 is imported."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm
+    return reference_arm.run(args, MODEL, PROMPT_LEN, FULL_LAYERS, peaks(), ClockSampler)
 
 
 def main():
@@ -92,6 +92,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
                     help="a reduced run for profiling: only the decode steps, or only the prefill")
+    ap.add_argument("--kernels", action="store_true",
+                    help="with --impl reference: time the reference's Triton kernels alone, one JSON line each")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

@@ -21,7 +21,7 @@ for other architectures, ``LinearStateCache`` slots of fixed size per resident s
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, Hashable, List, Optional, Sequence
+from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
 
 class KVCapacityError(MemoryError):
@@ -95,6 +95,10 @@ class CacheManager:
         self.max_requests = max_requests
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._req: Dict[Hashable, _RequestState] = {}
+        # called with the slot whenever a request takes one: whoever keeps per-request state on the device
+        # starts the slot from zero here, so that every way of admitting a request (replay, scheduler,
+        # re-admission after a preemption) resets it
+        self.on_slot_taken: List[Callable[[int], None]] = []
 
     # ------------------------------------------------------------------ requests and slots
     def __contains__(self, rid) -> bool:
@@ -115,6 +119,8 @@ class CacheManager:
             raise KVCapacityError(f"all {self.max_requests} request slots are in use")
         slot = self._free_slots.pop()
         self._req[rid] = _RequestState(slot=slot, blocks=[[] for _ in self.groups])
+        for hook in self.on_slot_taken:
+            hook(slot)
         return slot
 
     def free(self, rid) -> None:
@@ -156,6 +162,16 @@ class CacheManager:
 
     def fits(self, rid, n_tokens: int) -> bool:
         return all(need <= pool.num_free for need, pool in zip(self.pages_needed(rid, n_tokens), self.pools))
+
+    def fits_all(self, rids: Sequence[Hashable], n_tokens: int) -> bool:
+        """Whether every one of ``rids`` can append ``n_tokens`` in the same step: their needs are summed per
+        group before they are set against the free pages (two requests that each need the last free page
+        do not both fit, although ``fits`` says yes to either alone)."""
+        total = [0] * len(self.groups)
+        for rid in rids:
+            for g, need in enumerate(self.pages_needed(rid, n_tokens)):
+                total[g] += max(need, 0)     # pages a window gives back are not lent to a request that appends earlier
+        return all(need <= pool.num_free for need, pool in zip(total, self.pools))
 
     def append(self, rid, n_tokens: int) -> int:
         """Room for the next ``n_tokens`` of ``rid`` in every group; returns the old length.

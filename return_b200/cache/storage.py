@@ -60,7 +60,9 @@ class CacheStorage:
         self.states: Dict[int, torch.Tensor] = {}
 
     def make_manager(self) -> CacheManager:
-        return CacheManager(self.group_specs, self.max_reside)
+        manager = CacheManager(self.group_specs, self.max_reside)
+        manager.on_slot_taken.append(self.reset_slot)
+        return manager
 
     def allocate(self) -> None:
         dev, dt = self.env.device, self.env.act_dtype
@@ -89,7 +91,7 @@ class CacheStorage:
     def reset_slot(self, slot: int) -> None:
         """A request that takes a slot starts from zero state."""
         for t in self.states.values():
-            t[slot].zero_()
+            t[slot].zero_()                  # in stream order: after the last step of whoever held the slot before
 
     def layer_context(self, owner_index: int, batch, write: bool) -> LayerContext:
         ctx = LayerContext(batch=batch, write_cache=write)

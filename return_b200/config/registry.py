@@ -4,7 +4,8 @@ The reference picks its model by a substring test on ``config.model_type``
 (rollout/engine_actor.py:24-32) and raises ``ValueError`` for anything else.  Here the key is
 ``architectures[0]`` of config.json, with ``model_type`` as a fallback.  An architecture gives:
 ``config_cls`` (typed, ``from_dict``), ``decoder_spec(cfg, max_positions)`` -> DecoderSpec,
-``weight_sources(cfg)`` -> {parameter: Source}, ``ignorable_tensors(cfg)``.
+``weight_sources(cfg)`` -> {parameter: Source}, ``ignorable_tensors(cfg)`` (names, or name -> twin
+it must equal).
 """
 from __future__ import annotations
 

@@ -124,7 +124,7 @@ class Engine:
         stop = False
         while True:
             can_launch = (not stop and launched < limit and launched - committed < Sampler.SLOTS
-                          and all(mgr.fits(r.id, 1) for r in reqs))
+                          and mgr.fits_all([r.id for r in reqs], 1))
             if can_launch:
                 entries = []
                 for r in reqs:

@@ -97,9 +97,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> int:
-        slot = self.manager.add(rid)
-        self.storage.reset_slot(slot)
-        return slot
+        return self.manager.add(rid)         # the storage zeroes the slot's state (CacheManager.on_slot_taken)
 
     def free_request(self, rid: Hashable) -> None:
         self.manager.free(rid)

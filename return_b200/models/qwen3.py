@@ -65,8 +65,9 @@ def weight_sources(cfg: Qwen3Config) -> Dict[str, Source]:
 
 
 def ignorable_tensors(cfg: Qwen3Config):
-    """Checkpoint tensors that may be present without being used: a tied head saved beside the embedding."""
-    return {"lm_head.weight"} if cfg.tie_word_embeddings else set()
+    """Checkpoint tensors that may be present without being used, each with the tensor it must equal: a tied
+    head saved beside the embedding."""
+    return {"lm_head.weight": "model.embed_tokens.weight"} if cfg.tie_word_embeddings else {}
 
 
 def split_rows(cfg: Qwen3Config, param: str):

@@ -12,6 +12,9 @@ import torch
 
 from .base import POSITION_ENCODINGS, PositionEncoding
 
+# every layer of a model asks for the same tables: one copy per (rotary width, theta, positions, device)
+_TABLES = {}
+
 
 @POSITION_ENCODINGS.register("rope")
 class RotaryEncoding(PositionEncoding):
@@ -24,10 +27,20 @@ class RotaryEncoding(PositionEncoding):
     def rotary_tables(self):
         """(cos, sin, rotary_dim); cos and sin are float32 [max_positions, rotary_dim/2] on the device."""
         if self._tables is None:
-            half = self.spec.rotary_dim // 2
-            # made on the CPU in float32 so that every device sees the same angles
-            inv_freq = 1.0 / (self.spec.theta ** (torch.arange(0, half, dtype=torch.float32) / half))
-            ang = torch.outer(torch.arange(self.spec.max_positions, dtype=torch.float32), inv_freq)
-            self._tables = (ang.cos().contiguous().to(self.env.device),
-                            ang.sin().contiguous().to(self.env.device), self.spec.rotary_dim)
+            s = self.spec
+            key = (s.rotary_dim, float(s.theta), s.max_positions, str(self.env.device))
+            shared = _TABLES.get(key)
+            if shared is None:
+                half = s.rotary_dim // 2
+                # made on the CPU in float32 so that every device sees the same angles
+                inv_freq = 1.0 / (s.theta ** (torch.arange(0, half, dtype=torch.float32) / half))
+                ang = torch.outer(torch.arange(s.max_positions, dtype=torch.float32), inv_freq)
+                shared = _TABLES[key] = (ang.cos().contiguous().to(self.env.device),
+                                         ang.sin().contiguous().to(self.env.device), s.rotary_dim)
+            self._tables = shared
         return self._tables
+
+
+def drop_shared_tables() -> None:
+    """Forgets the shared tables (models that still hold them keep them alive)."""
+    _TABLES.clear()

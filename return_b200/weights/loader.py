@@ -60,20 +60,32 @@ def _target_dtype(stored: torch.dtype, role: str, act_dtype: torch.dtype) -> tor
     return act_dtype
 
 
-def check_checkpoint(expected: Dict[str, Tuple[int, ...]], files, ignorable: Set[str] = frozenset()) -> None:
+def check_checkpoint(expected: Dict[str, Tuple[int, ...]], files, ignorable=frozenset()) -> None:
     """Raises one WeightError unless ``files`` holds exactly the tensors of ``expected`` (checkpoint
-    name -> shape), each with its shape.  ``ignorable`` names may be present without being used."""
+    name -> shape), each with its shape.  ``ignorable``: names that may be present without being used;
+    given as a map name -> twin, such a tensor must equal its twin (a tied output head saved beside the
+    embedding: the reference ties unconditionally, rollout/engine_actor.py:46, so a head that differs
+    would be silently lost)."""
     missing = sorted(n for n in expected if n not in files)
     unexpected = sorted(n for n in files.names() if n not in expected and n not in ignorable)
     wrong = [f"{n} is {list(files.shape(n))}, the model wants {list(shape)}"
              for n, shape in expected.items() if n in files and tuple(files.shape(n)) != tuple(shape)]
-    if missing or unexpected or wrong:
-        raise WeightError(missing, unexpected, wrong)
+    other = []
+    if isinstance(ignorable, dict):
+        for n, twin in ignorable.items():
+            if n not in files or twin not in files:
+                continue
+            if tuple(files.shape(n)) != tuple(files.shape(twin)):
+                wrong.append(f"{n} is {list(files.shape(n))}, its twin {twin} is {list(files.shape(twin))}")
+            elif files.dtype(n) != files.dtype(twin) or not torch.equal(files.tensor(n), files.tensor(twin)):
+                other.append(f"{n} differs from {twin} although the configuration ties them")
+    if missing or unexpected or wrong or other:
+        raise WeightError(missing, unexpected, wrong, other)
 
 
 def load_parameters(params: Dict[str, "ParamSpec"], sources: Dict[str, Source],
                     expected: Dict[str, Tuple[int, ...]], model_dir: str, act_dtype: torch.dtype, device,
-                    ignorable: Set[str] = frozenset()) -> Dict[str, torch.Tensor]:
+                    ignorable=frozenset()) -> Dict[str, torch.Tensor]:
     """Every parameter as a device tensor, filled from the model folder's safetensors.
 
     ``expected``: checkpoint name -> shape, as ``checkpoint_shapes`` derives it."""

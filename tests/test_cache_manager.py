@@ -159,3 +159,30 @@ def test_host_batch_tables():
         build_host_batch(entries, m, vocab_size=9)
     with pytest.raises(ValueError, match="room"):
         build_host_batch([StepEntry("a", [1, 2], [], 3)], m)
+
+
+def test_fits_all_sums_the_needs_of_a_step():
+    """Two requests that each need the last free page: either fits alone, both do not."""
+    m = CacheManager([GroupSpec("full", 16, 3)], 4)
+    for rid in ("a", "b"):
+        m.add(rid)
+        m.append(rid, 16)
+    assert m.pools[0].num_free == 1
+    assert m.fits("a", 1) and m.fits("b", 1)
+    assert not m.fits_all(["a", "b"], 1)
+    assert m.fits_all(["a"], 1)
+    m.append("a", 1)
+    with pytest.raises(KVCapacityError):
+        m.append("b", 1)
+    m.check()
+
+
+def test_taking_a_slot_calls_the_hooks():
+    m = CacheManager([GroupSpec("full", 4, 8)], 2)
+    seen = []
+    m.on_slot_taken.append(seen.append)
+    a = m.add("a")
+    b = m.add("b")
+    m.free("a")
+    c = m.add("c")                       # the slot of "a", taken again: reset again
+    assert seen == [a, b, c] and c == a

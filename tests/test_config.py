@@ -99,3 +99,20 @@ def test_engine_config_checks():
     with pytest.raises(ValueError):
         EngineConfig(max_token=8, page_size=16)
     assert EngineConfig(max_token=1024, page_size=16).num_pages == 64
+
+
+def test_layers_share_one_pair_of_rotary_tables():
+    """Every layer's attention builds its own position encoding from the same specification; the
+    tables exist once per device, not once per layer."""
+    import torch
+    from return_b200.parts import rope
+    from return_b200.parts.base import BuildEnv
+    from return_b200.parts.spec import RopeSpec
+    env = BuildEnv(torch.float32, torch.device("cpu"))
+    spec = RopeSpec(rotary_dim=16, theta=10000.0, max_positions=64)
+    a, b = rope.RotaryEncoding(spec, env), rope.RotaryEncoding(spec, env)
+    ca, sa, _ = a.rotary_tables()
+    cb, sb, _ = b.rotary_tables()
+    assert ca.data_ptr() == cb.data_ptr() and sa.data_ptr() == sb.data_ptr()
+    other = rope.RotaryEncoding(RopeSpec(rotary_dim=16, theta=500000.0, max_positions=64), env).rotary_tables()
+    assert other[0].data_ptr() != ca.data_ptr()

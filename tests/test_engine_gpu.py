@@ -230,3 +230,18 @@ def test_running_ahead_gives_way_when_pages_run_short(tmp_path):
     got = eng.generate(prompts, max_new_tokens=24, temperature=0.0)
     assert [r.output_ids for r in got] == want
     assert eng.stats()["preemptions"] > 0
+
+
+def test_running_ahead_with_requests_that_cross_a_page_edge_together(tmp_path):
+    """Two prompts of one page each reach the page's edge in the same decode step while one page is free:
+    each alone would fit, both do not.  The loop that runs ahead must see that before it takes a page, and
+    leave the step to the scheduler, which preempts; the tokens stay those of plain greedy decoding."""
+    d = helpers.make_model_dir(tmp_path, "A")
+    prompts = [helpers.random_ids(256, 16, 61 + i) for i in range(2)]
+    want = _plain_greedy(d, prompts, 20)
+    eng = _engine(d, max_token=48, max_reside=2, page_size=16, use_cuda_graph=True, max_model_len=64)
+    got = eng.generate(prompts, max_new_tokens=20, temperature=0.0)
+    assert [r.output_ids for r in got] == want
+    assert eng.stats()["preemptions"] > 0
+    eng.runner.manager.check()
+    assert eng.runner.manager.pages_used() == [0]

@@ -115,6 +115,12 @@ def test_untied_model_without_head_is_an_error_and_tied_head_copy_is_ignored(tmp
     tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
     write_safetensors(os.path.join(d, "model.safetensors"), tensors.items())
     _load(d)
+    # a tied model whose file holds another head: loading it would silently drop that head
+    tensors["lm_head.weight"] = tensors["lm_head.weight"].clone()
+    tensors["lm_head.weight"][3, 5] += 0.5
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors.items())
+    with pytest.raises(WeightError, match="lm_head.weight differs from model.embed_tokens.weight"):
+        _load(d)
 
 
 def test_sharded_checkpoint_and_missing_shard(tmp_path):
