@@ -8,7 +8,6 @@ uniform over the vocabulary (rollout/utils/bench_sym.py:26).
 """
 from __future__ import annotations
 
-import os
 from typing import Dict, List
 
 import torch
@@ -192,57 +191,6 @@ def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8
             "ctas": int(tiles.shape[0]) * heads, "ms": ms, "TFLOPs": flops / ms / 1e9}
 
 
-def kernel_attention_trace(ctx=16384, heads=32, kv_heads=8, head_dim=128, page=16, first=50, last=200) -> Dict[str, object]:
-    """Where the cycles of a key tile go in the tcgen05 prefill attention kernel: a build with -DRB_AT_TRACE=1
-    stores clock64() at the events of the first CTA's first 256 key tiles; this reads them back and gives
-    the mean cycles of each segment over key tiles ``first`` to ``last`` (one prompt of ``ctx`` tokens)."""
-    import numpy as np
-    from .ext import ops
-    _os_environ_defs = os.environ.get("RETURN_B200_ATTN_TC5_DEFS", "")
-    os.environ["RETURN_B200_ATTN_TC5_DEFS"] = ",".join(filter(None, [_os_environ_defs, "RB_AT_TRACE=1"]))
-    ops._attn_tc5_libs.pop(head_dim, None)            # the traced build is another library
-    try:
-        dev = torch.device("cuda:0")
-        qkv, k_pool, v_pool, bt, cu_q, seg_pos0, _ = _paged_case(1, ctx, ctx, heads, kv_heads, head_dim, page, dev)
-        out = torch.empty((ctx, heads * head_dim), dtype=torch.bfloat16, device=dev)
-        tiles = torch.tensor([(0, r) for r in reversed(range(0, ctx, ops.TC5_TILE_ROWS))], dtype=torch.int32, device=dev)
-        trace = torch.zeros(64 + 24 * 256, dtype=torch.int32, device=dev)
-        saved = dict(ops._tc5_status)
-        ops._tc5_status[dev] = trace
-        try:
-            for _ in range(2):
-                ops.attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, bt, page, out, heads, kv_heads,
-                                          head_dim, head_dim ** -0.5, 0)
-            torch.cuda.synchronize()
-        finally:
-            ops._tc5_status.clear()
-            ops._tc5_status.update(saved)
-        w = trace.cpu().numpy().astype(np.int64)
-    finally:
-        os.environ["RETURN_B200_ATTN_TC5_DEFS"] = _os_environ_defs
-        ops._attn_tc5_libs.pop(head_dim, None)
-    if w[0] != 0:
-        raise RuntimeError("a bounded wait inside the kernel gave up")
-    events = {"issuer_top": 0, "issuer_s_issued": 2, "issuer_p_got": 4, "issuer_pv_issued": 7,
-              "rowA_s_got": 8, "rowA_max_known": 9, "rowA_p_buffer_free": 10, "rowA_p_written": 11,
-              "rowB_s_got": 12, "rowB_max_known": 13, "rowB_p_buffer_free": 14, "rowB_p_written": 15,
-              "k_stage_free": 16, "k_issued": 17, "k_announced": 18, "v_stage_free": 19, "v_issued": 20, "v_announced": 21,
-              "rowA_exp_done": 22, "rowB_exp_done": 23}
-    ev = {n: w[64 + i * 256 + first: 64 + i * 256 + last] for n, i in events.items()}
-    delta = lambda x: ((x + 2 ** 31) % 2 ** 32) - 2 ** 31          # the stamps are the low 32 bits of the clock
-    seg = lambda a, b: round(float(np.mean(delta(ev[b] - ev[a]))), 1)
-    return {"kernel": "attention_prefill_tc5 (traced build)", "ctx": ctx, "tiles": [first, last],
-            "cycles_per_key_tile": round(float(np.mean(delta(np.diff(ev["issuer_top"])))), 1),
-            "issuer_A": {"wait_kv_and_8_S_mmas": seg("issuer_top", "issuer_s_issued"),
-                         "wait_p": seg("issuer_s_issued", "issuer_p_got"), "4_PV_mmas": seg("issuer_p_got", "issuer_pv_issued")},
-            "row_of_A": {"s_to_max": seg("rowA_s_got", "rowA_max_known"), "wait_p_buffer": seg("rowA_max_known", "rowA_p_buffer_free"),
-                         "exponentials": seg("rowA_p_buffer_free", "rowA_exp_done"), "round_store_fence": seg("rowA_exp_done", "rowA_p_written")},
-            "row_of_B": {"s_to_max": seg("rowB_s_got", "rowB_max_known"), "wait_p_buffer": seg("rowB_max_known", "rowB_p_buffer_free"),
-                         "exponentials": seg("rowB_p_buffer_free", "rowB_exp_done"), "round_store_fence": seg("rowB_exp_done", "rowB_p_written")},
-            "k_loader": {"stage_free_to_issued": seg("k_stage_free", "k_issued"), "issued_to_announced": seg("k_issued", "k_announced")},
-            "v_loader": {"stage_free_to_issued": seg("v_stage_free", "v_issued"), "issued_to_announced": seg("v_issued", "v_announced")}}
-
-
 def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> Dict[str, float]:
     """A bfloat16 matrix product alone: device time, weight bandwidth and TFLOP/s.
     ``impl`` 0: ``ops.linear`` (the engine's choice); 1: the tcgen05 kernel; 2: cuBLAS (``torch.mm``);
@@ -269,33 +217,6 @@ def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> D
             "TFLOPs": 2.0 * M * N * K / ms / 1e9}
 
 
-def probe_mma_rate(iters=2000) -> Dict[str, object]:
-    """Cycles per mma.sync.m16n8k16 per warp, with one dependent chain (latency) and with eight
-    independent ones (issue rate), for 1 to 16 warps on every SM."""
-    import ctypes
-    from .ext import build
-    lib = build.load("return_probes", ["probes.cu"])
-    lib.rb_probe_mma_rate.argtypes = [ctypes.c_int] * 4 + [ctypes.c_void_p] * 3
-    lib.rb_probe_mma_rate.restype = ctypes.c_int
-    dev = torch.device("cuda:0")
-    sink = torch.zeros(4, device=dev)
-    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
-    rows = []
-    for warps in (1, 2, 4, 8, 16):
-        row = {"warps_per_sm": warps}
-        for chains in (1, 8):
-            rc = lib.rb_probe_mma_rate(148, warps, chains, iters, ctypes.c_void_p(sink.data_ptr()),
-                                       ctypes.c_void_p(cyc.data_ptr()),
-                                       ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-            assert rc == 0
-            per = float(cyc.item()) / (iters * chains)
-            row[f"cycles_per_mma_{chains}chain"] = round(per, 1)
-            if chains == 8:
-                row["fma_per_cycle_per_sm"] = round(warps * 2048.0 / per)
-        rows.append(row)
-    return {"probe": "mma_rate", "rows": rows}
-
-
 def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[str, float]:
     """The gated feed-forward product out = silu(x Wg^T) * (x Wu^T) alone.  ``impl`` 0: the engine's
     choice (``ops.gated_linear``); 1: the tcgen05 kernel with the SwiGLU epilogue; 2: cuBLAS + the SwiGLU kernel."""
@@ -319,67 +240,6 @@ def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[st
     ms = _time_kernels(fns, iters, warmup)
     return {"kernel": ("gated_linear", "gemm_tc5_gated", "cublas+swiglu")[impl], "M": M, "I": I, "K": K, "ms": ms,
             "TFLOPs": 4.0 * M * I * K / ms / 1e9}
-
-
-def probe_tc5_rate(iters=2000) -> Dict[str, object]:
-    """Cycles per ``tcgen05.mma`` (M x N x 16, bf16, operands in shared memory) for one and two issuing
-    threads of a CTA, on every SM; then, for N = 128, with B as an MN-major operand and with the other warps
-    writing to shared memory meanwhile, and the MMA mix of one key tile of the prefill attention kernel."""
-    import ctypes
-    from .ext import build
-    lib = build.load("return_probes", ["probes.cu"])
-    lib.rb_probe_tc5_rate.argtypes = [ctypes.c_int] * 6 + [ctypes.c_void_p] * 2
-    lib.rb_probe_tc5_rate.restype = ctypes.c_int
-    dev = torch.device("cuda:0")
-    cyc = torch.zeros(16, dtype=torch.int64, device=dev)
-
-    def run(M, N, threads, mode):
-        cyc.zero_()
-        rc = lib.rb_probe_tc5_rate(148, M, N, iters, threads, mode, ctypes.c_void_p(cyc.data_ptr()),
-                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
-        assert rc == 0
-        torch.cuda.synchronize()
-        return float(cyc[1].item()) / iters, int(cyc[8].item())
-
-    rows = []
-    for M in (128, 64):
-        for N in (16, 64, 128, 256):
-            row = {"M": M, "N": N}
-            for threads in (1, 2):
-                if threads * N > 512:
-                    continue
-                per, _ = run(M, N, threads, 0)
-                row[f"cycles_per_mma_{threads}thread"] = round(per, 1)
-                row[f"tflops_{threads}thread"] = round(threads * 2.0 * M * N * 16 / per * 148 * 1.9e9 / 1e12)
-            rows.append(row)
-    variants = []
-    for name, N, mode in (("128x128x16, B K-major", 128, 0), ("128x128x16, B MN-major", 128, 1),
-                          ("128x128x16, B K-major, other warps storing", 128, 2),
-                          ("128x128x16, B MN-major, other warps storing", 128, 3),
-                          ("128x64x16, other warps storing", 64, 2),
-                          ("key tile of the attention kernel (16 S + 8 PV MMAs)", 128, 4),
-                          ("key tile of the attention kernel, other warps storing", 128, 6),
-                          ("key tile of the attention kernel with its six commits", 128, 12),
-                          ("key tile of the attention kernel, ten other warps polling a barrier", 128, 20)):
-        per, stored = run(128, N, 1, mode)
-        v = {"case": name, "cycles": round(per, 1)}
-        if stored:
-            v["stored_bytes_per_cycle"] = round(stored / (per * iters), 1)
-        variants.append(v)
-    for name, mode in (("tcgen05.commit to a barrier and the wait for it, nothing in flight", 32),
-                       ("one 128x64x16 MMA, commit, wait", 33),
-                       ("a token handed between two warps and back (arrive, wait, arrive, wait)", 64),
-                       ("thread time of a tcgen05.commit, back to back", 65),
-                       ("thread time of a barrier wait that succeeds at once", 66),
-                       ("thread time of tcgen05.fence::after_thread_sync", 67),
-                       ("key tile of the attention kernel with four waits and fences in the issuing thread", 100),
-                       ("key tile with four waits, no fences, in the issuing thread", 101),
-                       ("key tile, another warp waiting and fencing in a loop meanwhile", 102),
-                       ("thread time of one mbarrier.test_wait (complete phase)", 68),
-                       ("thread time of one mbarrier.try_wait.relaxed.cta (complete phase)", 69)):
-        per, _ = run(128, 64, 1, mode)
-        variants.append({"case": name, "cycles": round(per, 1)})
-    return {"probe": "tc5_rate", "rows": rows, "variants": variants}
 
 
 # ------------------------------------------------------------------------------- named workloads through the engine

@@ -21,7 +21,12 @@ from .manager import CacheManager, GroupSpec
 
 
 class CacheStorage:
-    def __init__(self, needs: List[object], page_size: int, num_pages: int, max_reside: int, env: BuildEnv):
+    def __init__(self, needs: List[object], page_size: int, num_pages: int, max_reside: int, env: BuildEnv,
+                 longest_append: Optional[int] = None):
+        """``num_pages``: pages of a group that keeps every key (the pool's capacity in tokens / page size).
+        A group that keeps a window gets only what ``max_reside`` requests can hold of it at a time: the
+        window plus the longest run of tokens one step may append (``longest_append``; None: unknown, the
+        group then gets ``num_pages`` too), in pages, plus one for the ragged ends."""
         self.env = env
         self.page_size = page_size
         self.max_reside = max_reside
@@ -39,8 +44,12 @@ class CacheStorage:
                 if sig not in signature_to_group:
                     signature_to_group[sig] = len(self.group_specs)
                     name = "full" if need.window is None else f"window{need.window}"
+                    pages = num_pages
+                    if need.window is not None and longest_append is not None:
+                        per_request = (need.window + longest_append + page_size - 1) // page_size + 1
+                        pages = max(1, min(num_pages, max_reside * per_request))
                     self.group_specs.append(GroupSpec(f"{name}_h{need.num_kv_heads}_d{need.head_dim}",
-                                                      page_size, num_pages, need.window))
+                                                      page_size, pages, need.window))
                     self._group_layers.append(0)
                     self._group_shape.append((need.num_kv_heads, need.head_dim))
                 g = signature_to_group[sig]

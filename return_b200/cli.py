@@ -102,9 +102,7 @@ def cmd_workload(args) -> int:
 def cmd_kernel_bench(args) -> int:
     from . import benchmark
     fn = {"attention_decode": benchmark.kernel_attention_decode, "attention_prefill": benchmark.kernel_attention_prefill,
-          "attention_trace": benchmark.kernel_attention_trace,
-          "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated, "mma_rate": benchmark.probe_mma_rate,
-          "tc5_rate": benchmark.probe_tc5_rate}[args.kernel]
+          "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated}[args.kernel]
     kw = {}
     for item in args.set or []:
         k, v = item.split("=")
@@ -116,7 +114,7 @@ def cmd_kernel_bench(args) -> int:
 def cmd_replay(args) -> int:
     import torch
     from .engine.replay import TraceReplayer
-    rp = TraceReplayer(args.model, args.dtype, args.max_tokens, page_size=args.page_size)
+    rp = TraceReplayer(args.model, args.dtype, args.max_tokens, page_size=args.page_size, use_cuda_graph=args.graph)
     os.makedirs(args.out, exist_ok=True)
     with open(args.trace) as f:
         for line in f:
@@ -171,7 +169,7 @@ def main(argv=None) -> int:
     wl.set_defaults(fn=cmd_workload)
 
     k = sub.add_parser("kernel-bench", help="time one kernel alone on random data (for profiles)")
-    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "attention_trace", "gemm", "gated", "mma_rate", "tc5_rate"])
+    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated"])
     k.add_argument("--set", action="append", help="an integer argument of the kernel case, e.g. batch=64 ctx=2048 M=8")
     k.set_defaults(fn=cmd_kernel_bench)
 
@@ -182,6 +180,7 @@ def main(argv=None) -> int:
     t.add_argument("--out", required=True)
     t.add_argument("--max-tokens", type=int, required=True)
     t.add_argument("--page-size", type=int, default=16)
+    t.add_argument("--graph", action="store_true", help="steps of single tokens replay captured CUDA graphs")
     t.set_defaults(fn=cmd_replay)
 
     args = ap.parse_args(argv)

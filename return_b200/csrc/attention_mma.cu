@@ -302,16 +302,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__
 }
 
 // ---------------------------------------------------------------------------------------- decode
-#ifdef RB_DC_WARPS                 // tuning builds may fix the decode kernel's shape
-constexpr int DC_WARPS = RB_DC_WARPS;
-#else
 constexpr int DC_WARPS = 4;        // two CTAs share an SM for D <= 128, so one CTA's tail overlaps another's body
-#endif
-#ifdef RB_DC_STAGES
-constexpr int DC_STAGES = RB_DC_STAGES;
-#else
 constexpr int DC_STAGES = (D <= 128) ? 3 : 2;   // pipeline depth per warp, bounded by shared memory
-#endif
 constexpr int DC_N = 16;      // keys per warp tile
 
 // The decode kernel can do the work of the q/k norm + rotation + cache-write kernel for its own

@@ -18,7 +18,7 @@
 //   warp 8     one thread issues A's MMAs, warp 11 one thread B's, with descriptors that are a base plus a
 //              constant.  An issuing thread is stopped while its MMAs wait for the tensor pipe, and pays some
 //              230 cycles for every barrier wait, even one that succeeds at once, and 90 for every commit
-//              (profiles/tcgen05_mma_rate.md), all of which adds up in one thread; so a key tile costs each of
+//              (measured with a loop of MMAs alone), all of which adds up in one thread; so a key tile costs each of
 //              the two threads two waits and two commits and no more: K(u) and V(u - 1) arrive on one barrier,
 //              and the commits that tell the rows that S is there and that P V is done free the K and V
 //              stages for the loaders as well;
@@ -40,13 +40,6 @@
 // *status is raised if a wait gave up.
 #include "tc5.cuh"
 
-// RB_AT_TRACE (tuning builds only): the first CTA stores the clock at the events of its first 256 key tiles into
-// status[64 + event * 256 + tile]; the caller then has to give a status buffer of 64 + 24 * 256 ints.
-#ifdef RB_AT_TRACE
-#define AT_STAMP(ev, t) do { if (trace_on && (t) < 256) status[64 + (ev) * 256 + (t)] = (int)clock64(); } while (0)
-#else
-#define AT_STAMP(ev, t) do {} while (0)
-#endif
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=64 or -DHEAD_DIM=128"
 #endif
@@ -196,9 +189,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
     fence_after_sync();
     const unsigned tmem = *tmem_slot;
     bool ok = true;
-#ifdef RB_AT_TRACE
-    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 128 || lane == 0);
-#endif
 
     if (warp < 2 * 4) {
         // ================================================================== one query row per thread
@@ -232,7 +222,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             const int j_base = (jt_begin + t) * KN;
             ok = mbar_wait(bar(B_S_FULL + qt * 2 + (t & 1)), (t >> 1) & 1) && ok;
             fence_after_sync();
-            if ((tid & 127) == 0) AT_STAMP(8 + qt * 4, t);
             const bool all_visible = full_tile && j_base + KN - 1 <= p0_t && (window <= 0 || j_base > p_last_t - window);
             unsigned a[64];
             tmem_ld32(lane_addr + (qt * 2 + (t & 1)) * KN, reinterpret_cast<unsigned(&)[32]>(a[0]));
@@ -261,14 +250,12 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 moved = true;
             }
             const float mu = m_ref == -INFINITY ? 0.f : m_ref;
-            if ((tid & 127) == 0) AT_STAMP(9 + qt * 4, t);
 
             // P(t) goes into the buffer that P V(t - 2) read, so the exponentials of this tile run while P V(t - 1)
             // does.  P V(t - 2) is done: the commit that announced S(t) came from the same thread after it, and
             // a commit stands for everything that thread issued before.  O may only be touched when P V(t - 1)
             // is done too, which the rows wait for only when they have to rescale it.  Tile t's P V commits
             // to barrier [t & 1], phase t >> 1.
-            if ((tid & 127) == 0) AT_STAMP(10 + qt * 4, t);
             if (t > 0 && __any_sync(0xffffffffu, moved)) {                  // rescale this row of O in tensor memory
                 ok = mbar_wait(bar(B_PV_DONE + qt * 2 + ((t - 1) & 1)), ((t - 1) >> 1) & 1) && ok;
                 fence_after_sync();
@@ -299,7 +286,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             float sum_lo, sum_hi;
             unpack2(sum2, sum_lo, sum_hi);
             const float sum = sum_lo + sum_hi;
-            if ((tid & 127) == 0) AT_STAMP(22 + qt, t);
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint4 v;
@@ -314,7 +300,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             l_run = l_run * alpha + sum;
             fence_proxy_async();
             fence_before_sync();
-            if ((tid & 127) == 0) AT_STAMP(11 + qt * 4, t);
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_P_READY + qt * 2 + (t & 1)));      // S(t) is read, O is rescaled, P(t) is written
         }
@@ -410,12 +395,9 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             unsigned p_par = 0;
             for (int t = 0; t < n_q; ++t) {
                 // S(t+1) goes into the buffer that S(t-1) used: its rows were read before P(t-1) was ready
-                if (qt == 0) AT_STAMP(0, t);
                 issue_s(t + 1);
-                if (qt == 0) AT_STAMP(2, t);
                 ok = mbar_wait(bar(B_P_READY + qt * 2) + 8u * (unsigned)(t & 1), p_par) && ok;
                 fence_after_sync();
-                if (qt == 0) AT_STAMP(4, t);
                 const unsigned long long p_tile = dP + (unsigned long long)((t & 1) * (P_BYTES >> 4));
                 if (t == 0) mma_ss(d_o, p_tile, v_tile, idesc_o, false);
                 else mma_ss(d_o, p_tile, v_tile, idesc_o, true);
@@ -423,7 +405,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 for (int k16 = 1; k16 < KN / 16; ++k16)    // 16 keys: 32 bytes along P's rows, 2048 bytes down V's
                     mma_ss(d_o, p_tile + (unsigned long long)(k16 * 2), v_tile + (unsigned long long)(k16 * 128), idesc_o, true);
                 mma_commit(bar(B_PV_DONE + qt * 2) + 8u * (unsigned)(t & 1));      // the rows may touch O and P; the V loader may reuse the stage
-                if (qt == 0) AT_STAMP(7, t);
                 p_par ^= (unsigned)(t & 1);                 // each of the two barriers has a phase every other tile
                 if (++v_st == STAGES) { v_st = 0; v_tile = dV; }
                 else v_tile += (unsigned long long)(K_BYTES >> 4);
@@ -457,7 +438,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 if (f < n_a) ok = mbar_wait(bar(b_free + (f & 1)), (f >> 1) & 1) && ok;
                 if (f < n_b) ok = mbar_wait(bar(b_free + 2 + (f & 1)), (f >> 1) & 1) && ok;
             }
-            AT_STAMP(16 + (is_k ? 0 : 3), t);
             const unsigned tile_smem = bufs + st * K_BYTES;
             const int jt = jt_begin + t;
             // Lane L looks up where rows L and L + 32 of the tile lie (a null pointer: not to be read).  The copies
@@ -489,7 +469,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
             }
             cp_async_commit();
             if (t + 1 < n_tiles) ask_pages(jt + 1, next_page);
-            AT_STAMP(17 + (is_k ? 0 : 3), t);
             // tile t is on its way; tile t - 1 has to have landed.  It is announced only now, after the wait for
             // the stage above: the product that completes the next phase of that wait's barrier needs this
             // announcement, so the wait cannot fall a phase behind.
@@ -500,7 +479,6 @@ attn_prefill_tc5_kernel(const bf16* __restrict__ q, int ld, const bf16* __restri
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_KV_FULL + (is_k ? st_prev : st)));      // K(t-1): its own stage; V(t-1): the stage of K(t)
             }
-            AT_STAMP(18 + (is_k ? 0 : 3), t);
             st = st + 1 == STAGES ? 0 : st + 1;
         }
         cp_async_wait<0>();

@@ -14,17 +14,9 @@
 
 namespace {
 
-#ifdef RB_SK_WARPS                 // tuning builds may fix the shape
-constexpr int SK_WARPS = RB_SK_WARPS;
-#else
 constexpr int SK_WARPS = 8;
-#endif
 constexpr int SK_ROWS = 16;       // weight rows per group
-#ifdef RB_SK_CTAS
-constexpr int SK_CTAS_PER_SM = RB_SK_CTAS;
-#else
 constexpr int SK_CTAS_PER_SM = 2;
-#endif
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {       // read once: do not keep in L1
     uint4 v;
@@ -61,11 +53,7 @@ template <int MT, typename TOut, bool GATED>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ out,
                    int M, int N, int K, int ldx, int ldw, int ldo) {
-#ifdef RB_SK_U1
-    constexpr int U = MT == 1 ? RB_SK_U1 : 2;
-#else
     constexpr int U = MT == 1 ? 4 : 2;                    // k32 blocks per buffer; two buffers in flight
-#endif
     __shared__ float red[SK_WARPS][SK_ROWS][8 * MT + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;

@@ -51,10 +51,7 @@ constexpr int LANES = 128;                // rows of an MMA tile
 constexpr int BK = 64;                    // bf16 elements of K per box: one 128-byte swizzle row
 constexpr int THREADS = 192;
 constexpr int MAX_STAGES = 32;
-#ifndef RB_GS_RING_KB
-#define RB_GS_RING_KB 96
-#endif
-constexpr int RING_BYTES = RB_GS_RING_KB * 1024;     // shared memory given to the ring of stages
+constexpr int RING_BYTES = 96 * 1024;     // shared memory given to the ring of stages
 
 struct Plan {
     int granule;      // rows that stay together: 1, or 16 for the gated form

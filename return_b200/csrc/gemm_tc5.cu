@@ -189,12 +189,8 @@ tc5_gemm_bmn_kernel(const bf16* __restrict__ x, const bf16* __restrict__ bmat, f
 }
 
 // ------------------------------------------------------------------------------------ the product kernel
-#ifndef RB_TC5_STAGES                      // tuning builds may choose the ring: stages x k blocks a stage x 48 KB <= 192 KB
-#define RB_TC5_STAGES 4
-#endif
-#ifndef RB_TC5_KPS
-#define RB_TC5_KPS 1
-#endif
+constexpr int TC5_STAGES = 4;             // the ring: stages x k blocks a stage x 48 KB <= 192 KB
+constexpr int TC5_KPS = 1;
 constexpr int TC5_THREADS = 192;          // warp 0: TMA, warp 1: MMA, warps 2..5: epilogue
 
 // Persistent: a CTA walks output tiles tile = blockIdx.x, + gridDim.x, ...; tiles that share a block
@@ -375,10 +371,10 @@ RB_EXPORT int rb_tc5_gemm(const void* x, const void* w, void* out, int out_f32, 
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return (int)cudaErrorInvalidValue;
     if (gated) {
         if (out_f32 || N % 16) return (int)cudaErrorInvalidValue;
-        return launch_tc5<256, RB_TC5_STAGES, RB_TC5_KPS, bf16, true>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+        return launch_tc5<256, TC5_STAGES, TC5_KPS, bf16, true>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
     }
-    if (out_f32) return launch_tc5<256, RB_TC5_STAGES, RB_TC5_KPS, float, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
-    return launch_tc5<256, RB_TC5_STAGES, RB_TC5_KPS, bf16, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    if (out_f32) return launch_tc5<256, TC5_STAGES, TC5_KPS, float, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    return launch_tc5<256, TC5_STAGES, TC5_KPS, bf16, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
 }
 
 RB_EXPORT int rb_tc5_gemm_simple(const void* x, const void* w, void* out, int out_f32, int bn, int M, int N, int K,

@@ -7,10 +7,6 @@
 
 #include "common.cuh"
 
-#ifndef RB_TMA_PROMO
-#define RB_TMA_PROMO 2      // CU_TENSOR_MAP_L2_PROMOTION_L2_128B
-#endif
-
 namespace tma {
 
 // One box of the tensor behind `map`, whose innermost coordinate is x (elements; x * 2 bytes must be
@@ -63,7 +59,7 @@ static inline bool make_map_bf16(CUtensorMap* map, const void* ptr, int rows, in
     const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, (CUtensorMapL2promotion)RB_TMA_PROMO,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

@@ -12,7 +12,7 @@ All integers travel in one pinned host buffer and one device buffer, one copy pe
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -41,19 +41,18 @@ class HostBatch:
     seg_kv_len: np.ndarray    # [n] keys visible to the segment's last token
     want_rows: np.ndarray     # [n_want] token rows whose logits are wanted
     decode_segs: np.ndarray   # segments of one token
-    prefill_tiles: np.ndarray  # [n_tiles, 2]: (segment, first row within it) for segments of several tokens
-    prefill_tiles_tc5: np.ndarray = None   # the same in blocks of 256 rows, the longest contexts first (the tcgen05 kernel's tiles)
+    num_multi: int = 0        # segments of several tokens
+    # what the model's parts asked for (parts.base.Tiling): name -> [blocks, 2], (segment, first row within
+    # it) of every block of rows of the segments of several tokens
+    tiles: Dict[str, np.ndarray] = field(default_factory=dict)
     block_tables: List[np.ndarray] = field(default_factory=list)   # per group [n, blocks]
     rids: List[Hashable] = field(default_factory=list)
 
 
-PREFILL_TILE_ROWS = 64
-PREFILL_TILE_ROWS_TC5 = 256
-
-
 def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional[int] = None,
-                     max_positions: Optional[int] = None) -> HostBatch:
-    """Packs entries whose cache room was already made (``entry.start`` set by ``manager.append``)."""
+                     max_positions: Optional[int] = None, tilings: Optional[Dict[str, object]] = None) -> HostBatch:
+    """Packs entries whose cache room was already made (``entry.start`` set by ``manager.append``).
+    ``tilings``: name -> parts.base.Tiling, the tables of row blocks that the model's parts read."""
     if not entries:
         raise ValueError("a step needs at least one entry")
     n = len(entries)
@@ -73,8 +72,7 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
     seg_kv_len = np.empty(n, np.int32)
     want_rows: List[int] = []
     decode_segs: List[int] = []
-    tiles: List[tuple] = []
-    tiles_tc5: List[tuple] = []
+    multi: List[int] = []
     row = 0
     for i, e in enumerate(entries):
         L = lens[i]
@@ -91,18 +89,18 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
             if not (0 <= w < L):
                 raise ValueError(f"want index {w} is outside the entry's {L} tokens")
             want_rows.append(row + w)
-        if L == 1:
-            decode_segs.append(i)
-        else:
-            tiles.extend((i, r0) for r0 in range(0, L, PREFILL_TILE_ROWS))
-            tiles_tc5.extend((i, r0) for r0 in range(0, L, PREFILL_TILE_ROWS_TC5))
+        (decode_segs if L == 1 else multi).append(i)
         row += L
     if vocab_size is not None and (tokens.min() < 0 or tokens.max() >= vocab_size):
         raise ValueError(f"token ids must lie in [0, {vocab_size})")
     if max_positions is not None and int(seg_kv_len.max()) > max_positions:
         raise ValueError(f"a request would reach {int(seg_kv_len.max())} tokens; the engine was set up for {max_positions}")
-    # a tile's work grows with the position of its rows: the heaviest tiles are launched first
-    tiles_tc5.sort(key=lambda sr: -(int(seg_pos0[sr[0]]) + sr[1]))
+    tiles = {}
+    for name, tiling in (tilings or {}).items():
+        blocks = [(i, r0) for i in multi for r0 in range(0, lens[i], tiling.rows)]
+        if tiling.heaviest_first:        # a block's work grows with the position of its rows
+            blocks.sort(key=lambda sr: -(int(seg_pos0[sr[0]]) + sr[1]))
+        tiles[name] = np.asarray(blocks, np.int32).reshape(-1, 2)
     tables = []
     for g, spec in enumerate(manager.groups):
         blocks = max((int(seg_kv_len[i]) + spec.page_size - 1) // spec.page_size for i in range(n))
@@ -116,15 +114,13 @@ def build_host_batch(entries: Sequence[StepEntry], manager, vocab_size: Optional
         num_tokens=T, num_segments=n, num_want=len(want_rows), tokens=tokens, pos=pos, tok_seg=tok_seg,
         seg_slot=seg_slot, cu_q=cu_q, seg_pos0=seg_pos0, seg_kv_len=seg_kv_len,
         want_rows=np.asarray(want_rows, np.int32), decode_segs=np.asarray(decode_segs, np.int32),
-        prefill_tiles=np.asarray(tiles, np.int32).reshape(-1, 2),
-        prefill_tiles_tc5=np.asarray(tiles_tc5, np.int32).reshape(-1, 2), block_tables=tables, rids=rids)
+        num_multi=len(multi), tiles=tiles, block_tables=tables, rids=rids)
 
 
 class StepBatch:
     """The tables on the device, as views of one int32 buffer."""
 
-    _FIELDS = ("tokens", "pos", "tok_seg", "seg_slot", "cu_q", "seg_pos0", "seg_kv_len", "want_rows",
-               "decode_segs", "prefill_tiles", "prefill_tiles_tc5")
+    _FIELDS = ("tokens", "pos", "tok_seg", "seg_slot", "cu_q", "seg_pos0", "seg_kv_len", "want_rows", "decode_segs")
 
     def __init__(self, host: HostBatch, device, staging: "BatchStaging"):
         self.host = host
@@ -132,7 +128,10 @@ class StepBatch:
         self.num_tokens = host.num_tokens
         self.num_segments = host.num_segments
         self.num_want = host.num_want
-        arrays = [getattr(host, f).reshape(-1) for f in self._FIELDS] + [bt.reshape(-1) for bt in host.block_tables]
+        self.variant = {}                    # nothing is fixed beforehand: every part works its launches out from the host tables
+        tile_names = list(host.tiles)
+        arrays = ([getattr(host, f).reshape(-1) for f in self._FIELDS] + [host.tiles[n].reshape(-1) for n in tile_names]
+                  + [bt.reshape(-1) for bt in host.block_tables])
         offsets, total = [], 0
         for a in arrays:
             offsets.append(total)
@@ -146,9 +145,9 @@ class StepBatch:
         views = [dev[off:off + a.size] for a, off in zip(arrays, offsets)]
         for f, v in zip(self._FIELDS, views):
             setattr(self, f, v)
-        self.prefill_tiles = self.prefill_tiles.view(-1, 2)
-        self.prefill_tiles_tc5 = self.prefill_tiles_tc5.view(-1, 2)
-        self.block_tables = [v.view(bt.shape) for v, bt in zip(views[len(self._FIELDS):], host.block_tables)]
+        k = len(self._FIELDS)
+        self.tiles = {n: v.view(-1, 2) for n, v in zip(tile_names, views[k:k + len(tile_names)])}
+        self.block_tables = [v.view(bt.shape) for v, bt in zip(views[k + len(tile_names):], host.block_tables)]
 
 
 class BatchStaging:
@@ -188,11 +187,11 @@ class BatchStaging:
 class _StaticHost:
     """What the kernels' dispatch looks at on the host, for a captured decode step of n tokens."""
 
-    def __init__(self, n: int):
+    def __init__(self, n: int, tilings=None):
         self.num_tokens = self.num_segments = self.num_want = n
         self.decode_segs = np.arange(n, dtype=np.int32)
-        self.prefill_tiles = np.zeros((0, 2), np.int32)
-        self.prefill_tiles_tc5 = np.zeros((0, 2), np.int32)
+        self.num_multi = 0
+        self.tiles = {name: np.zeros((0, 2), np.int32) for name in (tilings or {})}
         self.cu_q = np.arange(n + 1, dtype=np.int32)
         self.seg_slot = np.zeros(n, np.int32)
         self.seg_kv_len = np.ones(n, np.int32)
@@ -201,18 +200,19 @@ class _StaticHost:
 class StaticDecodeBatch:
     """Tables of a step of exactly ``n`` single decoded tokens at fixed device addresses, so that the
     step can be captured in a CUDA graph once and replayed with new contents.  The block tables
-    have a fixed width (``max_blocks`` of each group); the split count of the decode attention is
-    fixed too, because a captured launch cannot change its grid.  A step of fewer than ``n`` tokens fills
+    have a fixed width (``max_blocks`` of each group); ``variant`` holds what the model's parts fixed
+    beforehand because a captured launch cannot change it (``Part.graph_variant``).  A step of fewer than ``n`` tokens fills
     the first rows; the rows behind them are padding: one key, no page (nothing of the cache is read or
     written), and the state slot ``pad_slot`` that belongs to no request."""
 
-    def __init__(self, n: int, max_blocks: Sequence[int], device, fixed_decode_splits: int, pad_slot: int = 0):
+    def __init__(self, n: int, max_blocks: Sequence[int], device, variant: Optional[dict] = None, pad_slot: int = 0,
+                 tilings=None):
         self.n = n
         self.pad_slot = pad_slot
         self.num_tokens = self.num_segments = self.num_want = n
-        self.fixed_decode_splits = fixed_decode_splits
+        self.variant = dict(variant or {})
         self.scratch = {}                    # work buffers of the captured step: they live as long as the graph
-        self.host = _StaticHost(n)
+        self.host = _StaticHost(n, tilings)
         self._max_blocks = list(max_blocks)
         sizes = [n, n, n, n, n + 1, n, n, n, n] + [n * b for b in max_blocks]
         offs, total = [], 0
@@ -231,8 +231,7 @@ class StaticDecodeBatch:
         for b, off in zip(max_blocks, offs[len(names):]):
             self._h_bt.append(hv[off:off + n * b].reshape(n, b))
             self.block_tables.append(self._dev[off:off + n * b].view(n, b))
-        self.prefill_tiles = torch.zeros((0, 2), dtype=torch.int32, device=device)
-        self.prefill_tiles_tc5 = torch.zeros((0, 2), dtype=torch.int32, device=device)
+        self.tiles = {name: torch.zeros((0, 2), dtype=torch.int32, device=device) for name in (tilings or {})}
         self._h["tok_seg"][:] = np.arange(n)
         self._h["cu_q"][:] = np.arange(n + 1)
         self._h["want_rows"][:] = np.arange(n)

@@ -16,6 +16,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 import torch
 
 from ..cache.manager import KVCapacityError
+from ..ext import ops
 from ..sampling.sampler import Sampler, uniform_draw
 from .config import EngineConfig
 from .request import GenerationResult, Request
@@ -78,6 +79,7 @@ class Engine:
                 sampled[r.id] = (t, lp)
         else:
             torch.cuda.current_stream().synchronize()
+        ops.check_status(self.runner.env.device)           # a kernel whose bounded wait gave up raises here, not garbage
         ended += self.scheduler.commit(plan, sampled)
         dt = time.perf_counter() - t0
         n_dec = sum(1 for e in plan.entries if len(e.tokens) == 1 and e.sample and len(e.request.output) > 1)
@@ -227,7 +229,10 @@ class Engine:
             "decode_duty": self._acc_decode / rt if rt > 0 else 0.0,
             "prefill_duty": self._acc_prefill / rt if rt > 0 else 0.0,
             "preemptions": self._preemptions,
-            "page_used": m.pages_used()[0], "page_total": m.groups[0].num_pages,
+            # the pages of every group of layers (a model with full and window layers has two pools)
+            "page_used": sum(m.pages_used()), "page_total": sum(g.num_pages for g in m.groups),
+            "page_groups": [{"name": g.name, "used": u, "total": g.num_pages, "window": g.window}
+                            for g, u in zip(m.groups, m.pages_used())],
         }
 
 

@@ -12,19 +12,25 @@ from typing import Optional
 
 import torch
 
+from ..ext import ops
 from .config import EngineConfig
 from .runner import ModelRunner
 
 
 class TraceReplayer:
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, max_reside: int = 8,
-                 poison: bool = False, device: str = "cuda:0"):
+                 poison: bool = False, device: str = "cuda:0", use_cuda_graph: bool = False):
+        """``use_cuda_graph``: steps that hold single tokens only replay captured graphs, as they do in
+        generation (padded batch sizes, fixed key splits, tables at fixed addresses); off, every step is
+        launched kernel by kernel.  The reference's check script has the same switch
+        (rollout/utils/check_correctness.py:43-50, ``--graph``)."""
         if 64 % page_size:
             raise ValueError("page_size must divide 64")
         # every request's count is rounded up to a multiple of 64, so the pool is a multiple of 64
         max_token = max(64, (max_tokens + 63) // 64 * 64)
+        # a trace step may bring any number of tokens, so the longest append is the pool itself
         cfg = EngineConfig(max_token=max_token, max_reside=max_reside, page_size=page_size, dtype=dtype,
-                           use_cuda_graph=False, device=device)
+                           prefill_chunk=max_token, use_cuda_graph=use_cuda_graph, device=device)
         self.runner = ModelRunner.from_model_dir(model_dir, cfg)
         if poison:
             self.runner.storage.poison()
@@ -44,6 +50,7 @@ class TraceReplayer:
         logits = None
         if entries:
             out = runner.step(entries)
+            ops.check_status(runner.env.device)           # waits for the step; raises if a kernel's bounded wait gave up
             if out.shape[0]:
                 logits = out
         for rid in record.get("end", []):

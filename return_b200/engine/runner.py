@@ -45,13 +45,14 @@ class ModelRunner:
         self.env = model.env
         self.max_positions = max_positions
         self.storage = CacheStorage(model.cache_needs(), engine_config.page_size, engine_config.num_pages,
-                                    engine_config.max_reside, self.env)
+                                    engine_config.max_reside, self.env,
+                                    longest_append=min(engine_config.prefill_chunk, max_positions))
         self.manager: CacheManager = self.storage.make_manager()
         self.storage.allocate()
         self.staging = BatchStaging(self.env.device)
         self.vocab_size = model.spec.vocab_size
-        self._kv_groups_cached = 0
-        self._graphs = {}                   # (decode batch size, key splits) -> (graph, static batch, static logits)
+        self.tilings = model.batch_tilings()   # the tables of row blocks that the model's parts read, by name
+        self._graphs = {}                   # (decode batch size, what the parts fixed) -> (graph, static batch, static logits)
         self._graph_pool = None
         self.launches_per_replay = {}       # decode batch size -> kernels of this package in its graph
 
@@ -120,7 +121,7 @@ class ModelRunner:
         ``device_tokens`` (int32 [n], a step of single decoded tokens through a captured graph only): the
         tokens are taken from this device tensor, in stream order, instead of from the entries; this is
         how a step starts before the host has seen the tokens the step before it sampled."""
-        host = build_host_batch(entries, self.manager, self.vocab_size, self.max_positions)
+        host = build_host_batch(entries, self.manager, self.vocab_size, self.max_positions, self.tilings)
         with torch.cuda.device(self.env.device):
             if self.config.use_cuda_graph and host.num_tokens == host.num_segments and self.model.graph_safe:
                 return self._graphed_decode(host, device_tokens)
@@ -137,15 +138,16 @@ class ModelRunner:
     def _graphed_decode(self, host, device_tokens=None) -> torch.Tensor:
         """A step of single decoded tokens replays a graph captured for its batch size, as the
         reference does (rollout/model.py:346-407); graphs are captured on first use.  A captured
-        launch cannot change its grid, so there is one graph per batch size and per number of ways the
-        decode attention splits the keys.  That number follows from the span of context lengths (the
-        longest request's, rounded up to a power of two or one and a half); many spans share one."""
+        launch cannot change its grid, so there is one graph per batch size and per set of choices that
+        the model's parts make from the context lengths (``Part.graph_variant``: the attention's number
+        of key splits).  They are asked with the span of context lengths (the longest request's, rounded
+        up to a power of two or one and a half), so that many steps share a graph."""
         m = host.num_tokens
         n = self.graph_batch_size(m)
-        splits = self._splits(n, int(host.seg_kv_len.max()))
-        entry = self._graphs.get((n, splits))
+        key = self._graph_key(n, int(host.seg_kv_len.max()))
+        entry = self._graphs.get(key)
         if entry is None:
-            entry = self._capture(n, splits)
+            entry = self._capture(key)
         graph, static, logits = entry
         static.fill(host)
         if device_tokens is not None:
@@ -165,25 +167,15 @@ class ModelRunner:
             span += span // 2 if span & (span - 1) == 0 else span // 3     # 512, 768, 1024, 1536, 2048, ...
         return span
 
-    def _splits(self, n: int, longest: int) -> int:
-        return ops.decode_splits(n * self._kv_groups(), self._span(longest))
+    def _graph_key(self, n: int, longest: int):
+        variant = self.model.graph_variant(n, self._span(longest))
+        return (n, tuple(sorted(variant.items(), key=repr)))
 
-    def _kv_groups(self) -> int:
-        """CTAs a decoded token gives the attention kernel per split, at most over the layers."""
-        if self._kv_groups_cached:
-            return self._kv_groups_cached
-        most = 1
-        for layer in self.model.spec.layers:
-            heads, kv = getattr(layer.mixer, "num_heads", None), getattr(layer.mixer, "num_kv_heads", None)
-            if heads and kv:
-                most = max(most, kv * ((heads // kv + 15) // 16))
-        self._kv_groups_cached = most
-        return most
-
-    def _capture(self, n: int, splits: int):
+    def _capture(self, key):
+        n, variant = key
         max_blocks = [(self.max_positions + g.page_size - 1) // g.page_size for g in self.manager.groups]
-        # every mixer of a captured step sees the same fixed split count
-        static = StaticDecodeBatch(n, max_blocks, self.env.device, splits, pad_slot=self.config.max_reside)
+        static = StaticDecodeBatch(n, max_blocks, self.env.device, dict(variant), pad_slot=self.config.max_reside,
+                                   tilings=self.tilings)
         side = torch.cuda.Stream(device=self.env.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):                      # warm-up outside the capture
@@ -197,12 +189,12 @@ class ModelRunner:
         self.launches_per_replay[n] = ops.launch_count - before
         if self._graph_pool is None:
             self._graph_pool = graph.pool()
-        self._graphs[(n, splits)] = (graph, static, logits)
-        return self._graphs[(n, splits)]
+        self._graphs[key] = (graph, static, logits)
+        return self._graphs[key]
 
     def capture_decode_graphs(self, batch_sizes=None) -> int:
         """Captures the decode graphs ahead of the first request (the reference's ``build_graph``): for every
-        batch size that ``graph_batch_size`` can give (or those asked for), one graph per split count that
+        batch size that ``graph_batch_size`` can give (or those asked for), one graph per variant that
         a span of context lengths up to the engine's limit leads to.  Returns how many graphs there are."""
         sizes = batch_sizes or sorted({self.graph_batch_size(m) for m in range(1, self.config.max_reside + 1)})
         spans, span = [], self._span(1)
@@ -212,7 +204,7 @@ class ModelRunner:
                 break
             span = self._span(span + 1)
         for n in sizes:
-            for splits in sorted({self._splits(n, sp) for sp in spans}):
-                if (n, splits) not in self._graphs:
-                    self._capture(n, splits)
+            for key in sorted({self._graph_key(n, sp) for sp in spans}, key=repr):
+                if key not in self._graphs:
+                    self._capture(key)
         return len(self._graphs)

@@ -145,6 +145,12 @@ def library_path(name: str, sources: Sequence[str], defines: Optional[Dict[str, 
             cmd = [find_nvcc()] + flags + ["-shared", "-o", tmp] + [os.path.join(CSRC, s) for s in sources]
             _run_with_heartbeat(cmd, what)
             os.replace(tmp, out)
+            for old in os.listdir(out_dir):          # builds of earlier sources under the same name are of no use now
+                if old.startswith(f"lib{name}-") and old.endswith(".so") and old != fname:
+                    try:
+                        os.remove(os.path.join(out_dir, old))
+                    except OSError:
+                        pass
             print(f"[return_b200] compiled {what} in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
         finally:
             fcntl.flock(lock_file, fcntl.LOCK_UN)

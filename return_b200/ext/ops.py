@@ -63,9 +63,9 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
         raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
-# How kernels of a step overlap through programmatic dependent launch (csrc/common.cuh); a build option.
-import os as _os
-PDL_MODE = int(_os.environ.get("RETURN_B200_PDL_MODE", "2"))
+# How kernels of a step overlap through programmatic dependent launch (csrc/common.cuh): every kernel waits for
+# its predecessor before it touches what that wrote, and lets its successor start when its main loop is done.
+PDL_MODE = 2
 
 _core = None
 
@@ -217,12 +217,7 @@ _TC5_SOURCES = ["gemm_tc5.cu", "gemm_stream.cu"]
 
 
 def _tc5_defines():
-    """Build options of the tcgen05 library; RETURN_B200_TC5_DEFS="NAME=1,OTHER=2" adds tuning macros."""
-    defs = {"RB_PDL_MODE": PDL_MODE}
-    for item in filter(None, _os.environ.get("RETURN_B200_TC5_DEFS", "").split(",")):
-        k, _, v = item.partition("=")
-        defs[k.strip()] = v.strip() or "1"
-    return defs
+    return {"RB_PDL_MODE": PDL_MODE}
 
 
 def tc5_lib() -> ctypes.CDLL:
@@ -253,6 +248,27 @@ def tc5_status(device) -> torch.Tensor:
         t = torch.zeros(1, dtype=torch.int32, device=device)
         _tc5_status[device] = t
     return t
+
+
+_tc5_launched = set()          # devices on which a kernel with bounded waits ran since the status word was last read
+
+
+def check_status(device) -> None:
+    """Reads the status word of the tcgen05 kernels if one of them ran on ``device`` since the last check, and
+    raises ``KernelError`` if a bounded wait gave up (the kernel's output is then not to be trusted).  It
+    synchronises, so callers use it where they wait for the step anyway (after sampling, after a replayed step)."""
+    device = torch.device(device)
+    if device not in _tc5_launched:
+        return
+    _tc5_launched.discard(device)
+    t = _tc5_status.get(device)
+    if t is None:
+        return
+    code = int(t.item())
+    if code != 0:
+        t.zero_()
+        raise KernelError(f"a tcgen05 kernel on {device} gave up a bounded wait or found its shared memory "
+                          f"misaligned (status {code}); the step's output is not valid")
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False, simple_bn: int = 0) -> None:
@@ -375,12 +391,7 @@ _attn_libs = {}
 
 
 def _attn_defines(head_dim: int):
-    """Build options of the mma.sync attention library; RETURN_B200_ATTN_DEFS="NAME=1,OTHER=2" adds tuning macros."""
-    defs = {"HEAD_DIM": head_dim, "RB_PDL_MODE": PDL_MODE}
-    for item in filter(None, _os.environ.get("RETURN_B200_ATTN_DEFS", "").split(",")):
-        k, _, v = item.partition("=")
-        defs[k.strip()] = v.strip() or "1"
-    return defs
+    return {"HEAD_DIM": head_dim, "RB_PDL_MODE": PDL_MODE}
 
 
 def attention_lib(head_dim: int) -> ctypes.CDLL:
@@ -407,16 +418,24 @@ def attention_lib(head_dim: int) -> ctypes.CDLL:
 _attn_tc5_libs = {}
 TC5_ATTENTION_HEAD_DIMS = (64, 128)
 TC5_TILE_ROWS = 256            # query rows of one CTA of the tcgen05 prefill attention kernel
-NUM_SMS = 148
+MMA_TILE_ROWS = 64             # query rows of one CTA of the mma.sync prefill attention kernel
+TILES_TC5, TILES_MMA = "attention.rows256", "attention.rows64"     # the names of their tables in a step's batch
+
+_num_sms = None
+
+
+def num_sms() -> int:
+    """Streaming multiprocessors of the current device (asked of the driver once).  Where no device is
+    visible (the dispatch rules are also tested on the host) the count of a B200 stands in."""
+    global _num_sms
+    if _num_sms is None:
+        _num_sms = (torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+                    if torch.cuda.is_available() else 148)
+    return _num_sms
 
 
 def _attn_tc5_defines(head_dim: int):
-    """Build options of the tcgen05 attention library; RETURN_B200_ATTN_TC5_DEFS="NAME=1" adds tuning macros."""
-    defs = {"HEAD_DIM": head_dim}
-    for item in filter(None, _os.environ.get("RETURN_B200_ATTN_TC5_DEFS", "").split(",")):
-        k, _, v = item.partition("=")
-        defs[k.strip()] = v.strip() or "1"
-    return defs
+    return {"HEAD_DIM": head_dim}
 
 
 def attention_tc5_lib(head_dim: int) -> ctypes.CDLL:
@@ -445,6 +464,7 @@ def attention_prefill_tc5(qkv, k_pool, v_pool, tiles, cu_q, seg_pos0, block_tabl
     assert tiles.dtype == torch.int32 and tiles.is_contiguous()
     lib = attention_tc5_lib(head_dim)
     T = qkv.shape[0]
+    _tc5_launched.add(qkv.device)
     scratch = None
     if num_splits > 1:
         key = ("attention.prefill_split_scratch", num_splits, T, num_heads, head_dim)
@@ -467,7 +487,7 @@ def prefill_splits(n_ctas: int, longest_context: int) -> int:
     """How many ways the keys of the prompt blocks are split: a CTA owns an SM, so blocks x heads below
     the SM count leave SMs idle (a short portion of a long prompt); the keys are then shared out until the
     CTAs fill the GPU once, as long as every share keeps PREFILL_SPLIT_MIN_KEYS keys."""
-    return max(1, min(NUM_SMS // max(1, n_ctas), longest_context // PREFILL_SPLIT_MIN_KEYS, 64))
+    return max(1, min(num_sms() // max(1, n_ctas), longest_context // PREFILL_SPLIT_MIN_KEYS, 64))
 
 
 def _prefill_split_count(batch, num_heads, window) -> int:
@@ -476,10 +496,11 @@ def _prefill_split_count(batch, num_heads, window) -> int:
     if held is not None and key in held:
         return held[key]
     host = batch.host
-    longest = int(host.seg_kv_len[host.prefill_tiles_tc5[:, 0]].max())
+    tiles = host.tiles[TILES_TC5]
+    longest = int(host.seg_kv_len[tiles[:, 0]].max())
     if window:
         longest = min(longest, int(window) + TC5_TILE_ROWS)
-    n = prefill_splits(host.prefill_tiles_tc5.shape[0] * num_heads, longest)
+    n = prefill_splits(tiles.shape[0] * num_heads, longest)
     if held is not None:
         held[key] = n
     return n
@@ -490,7 +511,7 @@ def decode_splits(n_ctas_base: int, max_kv_len: int, ctas_per_sm: int = 2) -> in
     128), so the time of the launch goes with (waves of CTAs) x (keys per CTA); the split count that
     makes this smallest wins, with at least 128 keys per CTA and the smaller count on a tie."""
     tiles = max(1, (max_kv_len + 15) // 16)
-    slots = NUM_SMS * ctas_per_sm
+    slots = num_sms() * ctas_per_sm
     best, best_cost = 1, None
     for s in range(1, 65):
         if s > 1 and (max_kv_len + s - 1) // s < 128:
@@ -560,8 +581,21 @@ def _decode_split_count_now(batch, num_heads, num_kv_heads, window) -> int:
     longest = int(host.seg_kv_len[host.decode_segs].max())
     if window:
         longest = min(longest, int(window))
-    fixed = getattr(batch, "fixed_decode_splits", None)
+    fixed = getattr(batch, "variant", {}).get(decode_splits_key(num_heads, num_kv_heads, window))
     return fixed or decode_splits(base, longest)
+
+
+def decode_splits_key(num_heads, num_kv_heads, window):
+    """Under this key a captured step holds the split count of its decoded tokens (``batch.variant``)."""
+    return ("attention.decode_splits", num_heads, num_kv_heads, window or 0)
+
+
+def decode_splits_for(n_tokens: int, longest: int, num_heads: int, num_kv_heads: int, window=None) -> int:
+    """The split count of a step of ``n_tokens`` single tokens whose contexts reach ``longest`` keys."""
+    group = num_heads // num_kv_heads
+    if window:
+        longest = min(longest, int(window))
+    return decode_splits(n_tokens * num_kv_heads * ((group + 15) // 16), longest)
 
 
 def decode_only(batch, dtype, num_heads, num_kv_heads, window=None) -> bool:
@@ -570,12 +604,12 @@ def decode_only(batch, dtype, num_heads, num_kv_heads, window=None) -> bool:
     pays while the kernel's CTAs fit on the GPU at once; with more, the work added to every CTA costs
     more than the small kernel it replaces (measured: +1 % at 8 requests, -2 % at 64)."""
     host = batch.host
-    if not (dtype == torch.bfloat16 and host.prefill_tiles.shape[0] == 0
+    if not (dtype == torch.bfloat16 and host.num_multi == 0
             and host.decode_segs.shape[0] == host.num_tokens and host.num_tokens > 0):
         return False
     group = num_heads // num_kv_heads
     ctas = host.num_tokens * num_kv_heads * ((group + 15) // 16) * _decode_split_count(batch, num_heads, num_kv_heads, window)
-    return ctas <= 2 * NUM_SMS
+    return ctas <= 2 * num_sms()
 
 
 def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_dim, k_pool, v_pool, batch,
@@ -614,13 +648,13 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
                        num_heads, num_kv_heads, head_dim, scale, window or 0)
         return
     host = batch.host
-    if host.prefill_tiles.shape[0]:
+    if host.num_multi:
         if head_dim in TC5_ATTENTION_HEAD_DIMS:
-            attention_prefill_tc5(qkv, k_pool, v_pool, batch.prefill_tiles_tc5, batch.cu_q, batch.seg_pos0, block_table,
+            attention_prefill_tc5(qkv, k_pool, v_pool, batch.tiles[TILES_TC5], batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0,
                                   _prefill_split_count(batch, num_heads, window), getattr(batch, "scratch", None))
         else:
-            attention_prefill_mma(qkv, k_pool, v_pool, batch.prefill_tiles, batch.cu_q, batch.seg_pos0, block_table,
+            attention_prefill_mma(qkv, k_pool, v_pool, batch.tiles[TILES_MMA], batch.cu_q, batch.seg_pos0, block_table,
                                   page_size, out, num_heads, num_kv_heads, head_dim, scale, window or 0)
     n_dec = host.decode_segs.shape[0]
     if n_dec:

@@ -56,6 +56,22 @@ class DecoderModel:
             self._graph_safe = all(b.graph_safe for b in self.blocks) and self.final_norm.graph_safe
         return self._graph_safe
 
+    def batch_tilings(self):
+        """Every table of query-row blocks that some part of the model reads (``Part.batch_tilings``)."""
+        out = {}
+        for b in self.blocks:
+            for name, tiling in b.batch_tilings().items():
+                if out.setdefault(name, tiling) != tiling:
+                    raise ValueError(f"two parts ask for different tilings under the name {name!r}")
+        return out
+
+    def graph_variant(self, n_tokens: int, longest_context: int):
+        """What a captured step of single tokens fixes beforehand, over all parts (``Part.graph_variant``)."""
+        out = {}
+        for b in self.blocks:
+            out.update(b.graph_variant(n_tokens, longest_context))
+        return out
+
     # ------------------------------------------------------------------ caches
     def cache_needs(self) -> List[object]:
         """Per schedule entry: what the run's mixer wants cached (None if it owns no cache)."""

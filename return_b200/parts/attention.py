@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..ext import ops
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVCacheNeed, Mixer, ParamSpec
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVCacheNeed, Mixer, ParamSpec, Tiling
 
 
 @MIXERS.register("attention")
@@ -51,6 +51,23 @@ class PagedAttention(Mixer):
 
     def cache_need(self):
         return KVCacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+
+    def batch_tilings(self):
+        """The row blocks of the tensor-core kernel for prompt portions that this head size runs on."""
+        if self.env.act_dtype != torch.bfloat16:
+            return {}
+        if self.spec.head_dim in ops.TC5_ATTENTION_HEAD_DIMS:
+            return {ops.TILES_TC5: Tiling(ops.TC5_TILE_ROWS, heaviest_first=True)}
+        return {ops.TILES_MMA: Tiling(ops.MMA_TILE_ROWS)}
+
+    def graph_variant(self, n_tokens, longest_context):
+        """A captured step cannot change the grid of the split-KV decode kernel: the number of key splits
+        is fixed per captured graph."""
+        if self.env.act_dtype != torch.bfloat16:
+            return {}
+        s = self.spec
+        return {ops.decode_splits_key(s.num_heads, s.num_kv_heads, s.window):
+                ops.decode_splits_for(n_tokens, longest_context, s.num_heads, s.num_kv_heads, s.window)}
 
     # ------------------------------------------------------------------ one step
     def forward(self, x, ctx):

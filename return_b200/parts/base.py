@@ -54,6 +54,15 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class Tiling:
+    """A table a part wants in every step's batch: the step's segments of several tokens cut into blocks of
+    ``rows`` query rows, as (segment, first row within it) pairs.  ``heaviest_first``: the blocks with the most
+    keys before them come first (they take longest, so they are launched first)."""
+    rows: int
+    heaviest_first: bool = False
+
+
 @dataclass
 class KVView:
     """One cache layer as a mixer sees it."""
@@ -108,6 +117,19 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for name, t in tensors.items():
             setattr(self, "p_" + name.replace(".", "_"), t)
+
+    def batch_tilings(self) -> Dict[str, "Tiling"]:
+        """Tables of query-row blocks that the part's kernels read, by name; the step's batch then holds
+        ``batch.tiles[name]`` (device, int32 [blocks, 2]) and ``batch.host.tiles[name]``.  A name is the
+        part's own ("attention.rows256"); the engine knows none of them."""
+        return {}
+
+    def graph_variant(self, n_tokens: int, longest_context: int) -> Dict[Any, Any]:
+        """What a captured step of ``n_tokens`` single tokens must fix beforehand because a captured launch
+        cannot change it (a grid size that follows from the context lengths), as {key: value}.  Steps whose
+        variants are equal share a graph; inside the captured step the part finds its value under
+        ``batch.variant[key]``.  ``longest_context`` is an upper bound of the step's context lengths."""
+        return {}
 
 
 class Norm(Part):

@@ -39,6 +39,18 @@ class PreNormBlock(Block):
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def batch_tilings(self):
+        out = {}
+        for part in self._children.values():
+            out.update(part.batch_tilings())
+        return out
+
+    def graph_variant(self, n_tokens, longest_context):
+        out = {}
+        for part in self._children.values():
+            out.update(part.graph_variant(n_tokens, longest_context))
+        return out
+
     def forward(self, stream, delta, ctx):
         T, H = stream.shape
         a = ctx.buffer("block.normed", (T, H), self.env.act_dtype, stream.device)

@@ -142,15 +142,19 @@ def test_host_batch_tables():
     for rid, toks, want in (("a", [7], [0]), ("b", [1, 2, 3, 4, 5], [4]), ("c", [9, 8], [0, 1])):
         start = m.append(rid, len(toks))
         entries.append(StepEntry(rid, toks, want, start))
-    hb = build_host_batch(entries, m, vocab_size=10)
+    from return_b200.parts.base import Tiling
+    hb = build_host_batch(entries, m, vocab_size=10, tilings={"rows2": Tiling(2), "rows4": Tiling(4, heaviest_first=True)})
     assert hb.num_tokens == 8 and hb.num_segments == 3 and hb.num_want == 4
     assert hb.tokens.tolist() == [7, 1, 2, 3, 4, 5, 9, 8]
     assert hb.pos.tolist() == [6, 0, 1, 2, 3, 4, 0, 1]
     assert hb.tok_seg.tolist() == [0, 1, 1, 1, 1, 1, 2, 2]
     assert hb.cu_q.tolist() == [0, 1, 6, 8] and hb.seg_pos0.tolist() == [6, 0, 0] and hb.seg_kv_len.tolist() == [7, 5, 2]
     assert hb.want_rows.tolist() == [0, 5, 6, 7]
-    assert hb.decode_segs.tolist() == [0] and hb.prefill_tiles.tolist() == [[1, 0], [2, 0]]
-    assert hb.prefill_tiles_tc5.tolist() == [[1, 0], [2, 0]]
+    assert hb.decode_segs.tolist() == [0] and hb.num_multi == 2
+    # the tables of row blocks are the ones asked for, by name; no part of the engine knows a kernel's tile
+    assert hb.tiles["rows2"].tolist() == [[1, 0], [1, 2], [1, 4], [2, 0]]
+    assert hb.tiles["rows4"].tolist() == [[1, 4], [1, 0], [2, 0]]           # most keys before them first
+    assert build_host_batch(entries, m, vocab_size=10).tiles == {}
     assert hb.block_tables[0].shape == (3, 2)
     assert hb.block_tables[0][0].tolist() == m.block_table("a", 0)
     assert hb.block_tables[0][2].tolist() == m.block_table("c", 0) + [-1]
@@ -186,3 +190,33 @@ def test_taking_a_slot_calls_the_hooks():
     m.free("a")
     c = m.add("c")                       # the slot of "a", taken again: reset again
     assert seen == [a, b, c] and c == a
+
+
+def test_a_window_group_gets_the_pages_its_requests_can_hold_not_the_whole_pool():
+    import torch
+    from return_b200.cache.storage import CacheStorage
+    from return_b200.parts.base import BuildEnv, KVCacheNeed
+    env = BuildEnv(torch.float32, torch.device("cpu"))
+    needs = [KVCacheNeed(1, 16, None), KVCacheNeed(1, 16, 24), KVCacheNeed(1, 16, None)]
+    st = CacheStorage(needs, 16, 100, 2, env, longest_append=32)
+    full, win = st.group_specs
+    assert (full.window, full.num_pages) == (None, 100)
+    assert (win.window, win.num_pages) == (24, 2 * ((24 + 32 + 15) // 16 + 1))
+    assert CacheStorage(needs, 16, 100, 2, env).group_specs[1].num_pages == 100      # longest append unknown
+    # two requests that append up to 32 tokens at a time never find the window group short
+    m = st.make_manager()
+    rng = random.Random(3)
+    for rid in ("a", "b"):
+        m.add(rid)
+    for _ in range(400):
+        rid = rng.choice("ab")
+        if m.length(rid) > 600:
+            m.free(rid)
+            m.add(rid)
+        n = rng.randint(1, 32)
+        if m.pages_needed(rid, n)[0] > m.pools[0].num_free:
+            m.free(rid)
+            m.add(rid)
+        assert m.pages_needed(rid, n)[1] <= m.pools[1].num_free
+        m.append(rid, n)
+        m.check()

@@ -23,7 +23,7 @@ def test_prefill_key_splits():
     for ctas in range(1, 300):
         for keys in (100, 700, 5000, 70000):
             s = ops.prefill_splits(ctas, keys)
-            assert 1 <= s <= 64 and (s == 1 or (s * ctas <= ops.NUM_SMS and keys // s >= ops.PREFILL_SPLIT_MIN_KEYS))
+            assert 1 <= s <= 64 and (s == 1 or (s * ctas <= ops.num_sms() and keys // s >= ops.PREFILL_SPLIT_MIN_KEYS))
 
 
 def test_decode_key_splits():

@@ -46,9 +46,10 @@ def test_random_configuration_and_trace(tmp_path, seed, dtype):
     rp = TraceReplayer(d, dtype, helpers.pool_tokens(steps), page_size=page, max_reside=4)
     rp.runner.storage.poison()
     got = helpers.collect(steps, [None if (lg := rp.run_step(s)) is None else lg.cpu() for s in steps])
-    tol = 2e-4 if dtype == "float32" else 8e-2
     for rid, ids in reqs.items():
         want = helpers.plain_logits(d, ids)
+        # bfloat16: a twelfth of the logits' standard deviation (the widths differ, so the logits' scale does)
+        tol = 2e-4 if dtype == "float32" else float(want.std()) / 12
         err = (got[rid] - want).abs().max().item()
-        assert err < tol, (raw, rid, len(ids), page, err)
+        assert err < tol, (raw, rid, len(ids), page, err, tol)
     assert rp.runner.manager.pages_used() == [0] * len(rp.runner.manager.groups)

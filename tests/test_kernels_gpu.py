@@ -327,8 +327,9 @@ def test_attention_decode_fused(Hq, Hkv, D, P, window, rot_frac, norm):
                              num_splits=3)
     # the one kernel
     host = types.SimpleNamespace(decode_segs=segs.cpu().numpy(), seg_kv_len=pg.seg_kv_len.cpu().numpy(), num_tokens=n,
-                                 prefill_tiles=torch.zeros(0, 2).numpy())
-    batch = types.SimpleNamespace(decode_segs=segs, cu_q=pg.cu_q, seg_kv_len=pg.seg_kv_len, host=host, fixed_decode_splits=3)
+                                 num_multi=0)
+    batch = types.SimpleNamespace(decode_segs=segs, cu_q=pg.cu_q, seg_kv_len=pg.seg_kv_len, host=host,
+                                  variant={ops.decode_splits_key(Hq, Hkv, window): 3})
     k2, v2, q2 = k0.clone(), v0.clone(), raw.clone()
     got = torch.full_like(want, float("nan"))
     ops.attention_decode_fused(q2, qw, kw, 1e-6, 0.0, cos, sin, rot, k2, v2, batch, pg.bt, P, got, Hq, Hkv, D, scale, window)

@@ -117,7 +117,7 @@ def test_attention_part_and_block_alone(tmp_path, case, dtype):
     got, got_mixer = [], []
     for lo, hi in ((0, 29), (29, T)):
         entry = runner.reserve("r", [0] * (hi - lo))
-        batch = StepBatch(build_host_batch([entry], runner.manager), torch.device(DEV), runner.staging)
+        batch = StepBatch(build_host_batch([entry], runner.manager, tilings=runner.tilings), torch.device(DEV), runner.staging)
         ctx = runner.storage.layer_context(0, batch, write=True)
         got_mixer.append(block.mixer.forward(a[lo:hi].to(dtype).to(DEV), ctx).float().cpu())
         stream = x[lo:hi].clone().to(DEV)
@@ -269,6 +269,41 @@ def test_toy_mixer_with_state_of_its_own(tmp_path):
         for rid, ids in reqs.items():
             assert (got[rid] - _toy_reference(d, cfg, ids)).abs().max() < 1e-4, rid
         assert rp.runner.manager.free_slots == 3
+    finally:
+        registry.unregister_architecture("ToyRunningMeanLM")
+        MIXERS.unregister("running_mean")
+
+
+def test_toy_state_under_the_scheduler_with_reused_slots_and_a_preemption(tmp_path):
+    """The same toy architecture through ``Engine.generate``: two slots for five requests, so slots are taken
+    again, and a pool so small that one request is preempted and computed again.  Every admission must
+    start from zero state, whoever admits: greedy tokens equal the toy reference's."""
+    from return_b200.config import registry
+    from return_b200.engine.config import EngineConfig
+    from return_b200.engine.engine import Engine
+    from return_b200.parts import MIXERS
+    from return_b200.weights import loader
+    _register_toy()
+    try:
+        cfg = ToyConfig(vocab_size=90, hidden_size=24, intermediate_size=40, num_hidden_layers=2, rms_norm_eps=1e-5)
+        d = loader.write_random_model(os.path.join(str(tmp_path), "toy"), cfg, seed=11)
+        prompts = [helpers.random_ids(90, n, 300 + i) for i, n in enumerate((30, 28, 9, 17, 22))]
+        new = 26
+
+        def greedy(ids):
+            ids, out = list(ids), []
+            for _ in range(new):
+                out.append(int(_toy_reference(d, cfg, ids)[-1].argmax()))
+                ids.append(out[-1])
+            return out
+
+        eng = Engine(d, EngineConfig(max_token=96, max_reside=2, page_size=16, prefill_chunk=16, dtype="float32",
+                                     use_cuda_graph=True, max_model_len=80))
+        got = eng.generate(prompts, max_new_tokens=new, temperature=0.0)
+        assert [r.output_ids for r in got] == [greedy(p) for p in prompts]
+        assert eng.stats()["preemptions"] > 0
+        eng.runner.manager.check()
+        assert eng.runner.manager.free_slots == 2
     finally:
         registry.unregister_architecture("ToyRunningMeanLM")
         MIXERS.unregister("running_mean")
