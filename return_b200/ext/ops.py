@@ -104,6 +104,7 @@ def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
     paths.append(build.library_path("return_tc5", _TC5_SOURCES, _tc5_defines()))
+    paths.append(build.library_path("return_chain", ["gemm_chain.cu"], {"RB_PDL_MODE": PDL_MODE}))
     for d in TC5_ATTENTION_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], _attn_tc5_defines(d)))
     for d in PREBUILT_HEAD_DIMS:
@@ -267,8 +268,8 @@ def check_status(device) -> None:
     code = int(t.item())
     if code != 0:
         t.zero_()
-        raise KernelError(f"a tcgen05 kernel on {device} gave up a bounded wait or found its shared memory "
-                          f"misaligned (status {code}); the step's output is not valid")
+        raise KernelError(f"a kernel on {device} gave up a bounded wait (an mbarrier, or the other CTAs of its grid) or "
+                          f"found its shared memory misaligned (status {code}); the step's output is not valid")
 
 
 def gemm_tc5(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool = False, simple_bn: int = 0) -> None:
@@ -347,6 +348,120 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         torch.mm(x, w.t(), out=out)
+
+
+# ------------------------------------------------------------------------------- chains of products for few rows
+
+CHAIN_MAX_ROWS = 8
+_chain = None
+_chain_state = {}               # device -> (barrier words, plan cache)
+
+
+class _ChainOp(ctypes.Structure):
+    _fields_ = [("w", c_void_p), ("x", c_void_p), ("stream_in", c_void_p), ("stream_out", c_void_p),
+                ("delta", c_void_p), ("norm_w", c_void_p), ("out", c_void_p),
+                ("N", c_int), ("K", c_int), ("ldw", c_int), ("ldx", c_int), ("ldo", c_int), ("ld_delta", c_int),
+                ("x_kind", c_int), ("epilogue", c_int), ("out_permuted", c_int), ("norm_w_dtype", c_int),
+                ("eps", c_float), ("offset", c_float)]
+
+
+class _ChainParams(ctypes.Structure):
+    _fields_ = [("op", _ChainOp * 4), ("n_ops", c_int), ("M", c_int), ("n_stages", c_int), ("xs_k", c_int),
+                ("barrier", c_void_p), ("status", c_void_p)]
+
+
+def chain_lib() -> ctypes.CDLL:
+    """The persistent kernel that runs a chain of matrix products for few rows (csrc/gemm_chain.cu)."""
+    global _chain
+    if _chain is None:
+        lib = build.load("return_chain", ["gemm_chain.cu"], {"RB_PDL_MODE": PDL_MODE})
+        lib.rb_gemm_chain.argtypes = [c_void_p, c_void_p]
+        lib.rb_gemm_chain.restype = c_int
+        lib.rb_gemm_chain_plan.argtypes = [c_int]
+        lib.rb_gemm_chain_plan.restype = c_int
+        if lib.rb_gemm_chain_param_bytes() != ctypes.sizeof(_ChainParams) or lib.rb_gemm_chain_op_bytes() != ctypes.sizeof(_ChainOp):
+            raise KernelError("the chain kernel's parameter block is laid out differently than this module expects")
+        _chain = lib
+    return _chain
+
+
+class ChainStep:
+    """One product of a chain: ``out = f(x) @ w^T``.
+
+    ``x``: a bfloat16 tensor [M, K]; or ``("norm", stream_in, stream_out, delta, weight, eps, offset)``:
+    x = rmsnorm(stream_in + delta) * (offset + weight) with the sum written to ``stream_out`` (float32 [M, K],
+    another tensor than ``stream_in``; ``delta`` bfloat16 [M, K] or None); or ``"previous"``: the output of the
+    step before.  ``gated``: ``w`` holds gate and up rows woven in blocks of 8 and ``out`` is [M, N / 2] = silu(gate) * up."""
+
+    def __init__(self, x, w, out, gated=False):
+        self.x, self.w, self.out, self.gated = x, w, out, gated
+
+
+def chain_ok(M: int, steps) -> bool:
+    """Whether the chain kernel takes these products: few rows, bfloat16, k a multiple of 16, aligned rows."""
+    if not (1 <= M <= CHAIN_MAX_ROWS) or not (1 <= len(steps) <= 4):
+        return False
+    for i, st in enumerate(steps):
+        w = st.w
+        if w.dtype != torch.bfloat16 or w.shape[1] % 16 or w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16:
+            return False
+        if st.gated and w.shape[0] % 16:
+            return False
+        if isinstance(st.x, str) and i == 0:
+            return False
+    return True
+
+
+def gemm_chain(M: int, steps, held=None) -> None:
+    """Runs the steps as one persistent kernel (see ``ChainStep``).  The output of a step that the next one takes
+    as ``"previous"`` is kept in an order of the kernel's own and must not be read by anyone else; ``held``: the
+    step's map of work buffers."""
+    lib = chain_lib()
+    dev = steps[0].w.device
+    state = _chain_state.get(dev)
+    if state is None:
+        state = _chain_state[dev] = (torch.zeros(2, dtype=torch.int32, device=dev), {})
+    barrier, plans = state
+    xs_k = 32
+    for st in steps:
+        if not isinstance(st.x, str):
+            xs_k = max(xs_k, (st.w.shape[1] + 31) // 32 * 32)
+    n_stages = plans.get(xs_k)
+    if n_stages is None:
+        with torch.cuda.device(dev):
+            n_stages = plans[xs_k] = lib.rb_gemm_chain_plan(xs_k)
+    if n_stages <= 0:
+        raise KernelError(f"the chain kernel has no room for rows of {xs_k} elements beside its ring")
+    P = _ChainParams()
+    P.n_ops, P.M, P.n_stages, P.xs_k = len(steps), M, n_stages, xs_k
+    P.barrier, P.status = _ptr(barrier), _ptr(tc5_status(dev))
+    _tc5_launched.add(dev)
+    for i, st in enumerate(steps):
+        op = P.op[i]
+        N, K = st.w.shape
+        assert st.out.dtype == torch.bfloat16 and st.out.shape[0] >= M and st.out.stride(1) == 1
+        op.w, op.N, op.K, op.ldw = _ptr(st.w), N, K, st.w.stride(0)
+        op.out, op.ldo, op.epilogue = _ptr(st.out), st.out.stride(0), 1 if st.gated else 0
+        nxt = steps[i + 1] if i + 1 < len(steps) else None
+        op.out_permuted = 1 if (nxt is not None and isinstance(nxt.x, str)) else 0
+        if op.out_permuted:
+            assert st.out.stride(0) % 32 == 0, "an output that the next step takes needs rows of a multiple of 32 elements"
+        if isinstance(st.x, str):
+            prev = steps[i - 1].out
+            assert st.x == "previous" and prev.shape[1] >= K
+            op.x_kind, op.x, op.ldx = 2, _ptr(prev), prev.stride(0)
+        elif isinstance(st.x, tuple):
+            kind, s_in, s_out, delta, weight, eps, offset = st.x
+            assert kind == "norm" and s_in.dtype == torch.float32 and s_in.is_contiguous() and s_in.shape[1] == K
+            assert s_out is None or (s_out.dtype == torch.float32 and s_out.is_contiguous() and s_out.data_ptr() != s_in.data_ptr())
+            assert delta is None or (delta.dtype == torch.bfloat16 and delta.stride(1) == 1)
+            op.x_kind, op.stream_in, op.stream_out = 1, _ptr(s_in), _ptr(s_out)
+            op.delta, op.ld_delta = _ptr(delta), (delta.stride(0) if delta is not None else 0)
+            op.norm_w, op.norm_w_dtype, op.eps, op.offset = _ptr(weight), dtype_code(weight.dtype), eps, offset
+        else:
+            assert st.x.dtype == torch.bfloat16 and st.x.shape[1] == K and st.x.stride(1) == 1
+            op.x_kind, op.x, op.ldx = 0, _ptr(st.x), st.x.stride(0)
+    _check(lib.rb_gemm_chain(ctypes.byref(P), _stream()), "gemm_chain")
 
 
 # ------------------------------------------------------------------------------- attention
@@ -542,7 +657,8 @@ def _split_scratch(lib, n, num_heads, num_splits, device, held=None):
     if held is not None and key in held:
         return held[key]
     floats = lib.rb_attn_decode_scratch_floats(n, num_heads, num_splits)
-    scratch = torch.empty(floats, dtype=torch.float32, device=device) if floats else None
+    # zeroed once: the arrival counters at its end must start at zero, and every launch leaves them so
+    scratch = torch.zeros(floats, dtype=torch.float32, device=device) if floats else None
     if held is not None:
         held[key] = scratch
     return scratch
@@ -558,7 +674,7 @@ def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, blo
     _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
                               _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
                               _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
-                              num_splits, _stream()), "attention_decode", 2 if num_splits > 1 else 1)
+                              num_splits, _stream()), "attention_decode")
 
 
 def _decode_split_count(batch, num_heads, num_kv_heads, window) -> int:
@@ -615,8 +731,8 @@ def decode_only(batch, dtype, num_heads, num_kv_heads, window=None) -> bool:
 def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_dim, k_pool, v_pool, batch,
                            block_table, page_size, out, num_heads, num_kv_heads, head_dim, scale, window=None,
                            write_kv=True) -> None:
-    """A step of single tokens: per-head q/k norm, rotation, cache write and split-KV attention in one kernel
-    (plus the merge of the splits).  ``qkv`` holds the raw projections and is left as it is."""
+    """A step of single tokens: per-head q/k norm, rotation, cache write, split-KV attention and the merge of the
+    splits in one kernel.  ``qkv`` holds the raw projections and is left as it is."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     lib = attention_lib(head_dim)
     n = batch.decode_segs.shape[0]
@@ -633,7 +749,7 @@ def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_d
                                     page_size, _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale,
                                     int(window or 0), splits, _ptr(q_weight), _ptr(k_weight), wd, eps, offset,
                                     _ptr(cos), _ptr(sin), rot_dim, 1 if write_kv else 0, _stream()),
-           "attention_decode_fused", 2 if splits > 1 else 1)
+           "attention_decode_fused")
 
 
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,

@@ -71,26 +71,41 @@ class PagedAttention(Mixer):
 
     # ------------------------------------------------------------------ one step
     def forward(self, x, ctx):
-        s, b, kv = self.spec, ctx.batch, ctx.kv
         T = x.shape[0]
         qkv = ctx.buffer("attention.qkv", (T, self.q_size + 2 * self.kv_size), x.dtype, x.device)
         ops.linear(x, self.p_qkv, qkv)
+        o = self.core(qkv, ctx)
+        y = ctx.buffer("attention.y", (T, self.spec.hidden_size), x.dtype, x.device)
+        ops.linear(o, self.p_o, y)
+        return y
 
+    # A mixer that is "product, something in the middle, product" says so, and a block may then run the two
+    # products in kernels of its own choosing (fused with the norms around them).
+    def in_projection(self):
+        """(weight [q + 2 kv, hidden], name of the buffer its output goes to)."""
+        return self.p_qkv, "attention.qkv"
+
+    def out_projection(self):
+        return self.p_o
+
+    def core(self, qkv, ctx):
+        """From the projections [T, q + 2 kv] to the attention output [T, q]: per-head norm, position encoding,
+        cache write, attention over the block table."""
+        s, b, kv = self.spec, ctx.batch, ctx.kv
+        T = qkv.shape[0]
         qw = self.q_norm.p_weight if self.q_norm is not None else None
         kw = self.k_norm.p_weight if self.k_norm is not None else None
         eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
         offset = s.qk_norm.offset if s.qk_norm is not None else 0.0
         tables = self.position.rotary_tables() if self.position is not None else None
-        o = ctx.buffer("attention.o", (T, self.q_size), x.dtype, x.device)
-        if (tables is not None or self.position is None) and ops.decode_only(b, x.dtype, s.num_heads, s.num_kv_heads, s.window):
+        o = ctx.buffer("attention.o", (T, self.q_size), qkv.dtype, qkv.device)
+        if (tables is not None or self.position is None) and ops.decode_only(b, qkv.dtype, s.num_heads, s.num_kv_heads, s.window):
             # single decoded tokens only: norm, rotation, cache write and attention are one kernel
             cos, sin, rot = tables if tables is not None else (None, None, 0)
             ops.attention_decode_fused(qkv, qw, kw, eps, offset, cos, sin, rot, kv.k, kv.v, b, kv.block_table,
                                        kv.page_size, o, s.num_heads, s.num_kv_heads, s.head_dim, s.scale, s.window,
                                        write_kv=ctx.write_cache)
-            y = ctx.buffer("attention.y", (T, s.hidden_size), x.dtype, x.device)
-            ops.linear(o, self.p_o, y)
-            return y
+            return o
         if tables is not None or self.position is None:
             cos, sin, rot = tables if tables is not None else (None, None, 0)
             ops.qk_norm_rope_write(qkv, qw, kw, eps, cos, sin, rot, b.pos, b.tok_seg, kv.block_table,
@@ -107,9 +122,6 @@ class PagedAttention(Mixer):
                 ops.qk_norm_rope_write(qkv, None, None, 0.0, None, None, 0, b.pos, b.tok_seg, kv.block_table,
                                        kv.page_size, kv.k, kv.v, s.num_heads, s.num_kv_heads, s.head_dim,
                                        write_kv=True)
-
         ops.paged_attention(qkv, kv.k, kv.v, b, kv.block_table, kv.page_size, o, s.num_heads,
                             s.num_kv_heads, s.head_dim, s.scale, s.window)
-        y = ctx.buffer("attention.y", (T, s.hidden_size), x.dtype, x.device)
-        ops.linear(o, self.p_o, y)
-        return y
+        return o

@@ -23,6 +23,11 @@ class SwiGLU(FeedForward):
         return {"gate_up": ParamSpec((2 * s.intermediate_size, s.hidden_size)),
                 "down": ParamSpec((s.hidden_size, s.intermediate_size))}
 
+    def gated_projections(self):
+        """(gate_up weight, down weight, rows of a gate/up block): a feed-forward that is "gated product, then
+        product" says so, and a block may then run the two in a kernel of its own choosing."""
+        return self.p_gate_up, self.p_down, self.spec.interleave
+
     def forward(self, x, ctx):
         s = self.spec
         T = x.shape[0]

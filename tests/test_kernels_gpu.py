@@ -624,3 +624,81 @@ def test_sample_frequencies():
     freq = torch.bincount(toks.long().cpu(), minlength=V).double() / n
     assert (freq[probs == 0] == 0).all()
     assert (freq - probs).abs().max() < 0.03
+
+
+# ------------------------------------------------------------------------------- chains of products for few rows
+
+def _weave8(gate, up):
+    return torch.stack([gate.view(-1, 8, gate.shape[1]), up.view(-1, 8, up.shape[1])], dim=1).reshape(-1, gate.shape[1])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(48, 64), (100, 96), (40, 272), (6144, 4096), (4096, 12288)])
+def test_gemm_chain_single_product(M, N, K):
+    """One product through the persistent kernel: rows that are no multiple of 16, k that is no multiple of
+    the stage, more and fewer units than SMs."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(N + K + M)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert ops.chain_ok(M, [ops.ChainStep(x.to(DEV), w.to(DEV), out)])
+    ops.gemm_chain(M, [ops.ChainStep(x.to(DEV), w.to(DEV), out)])
+    ops.check_status(DEV)
+    want = x.float() @ w.float().T
+    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M", [1, 5, 8])
+@pytest.mark.parametrize("H,Q,I,wdt", [(96, 192, 224, torch.float32), (64, 64, 128, torch.bfloat16), (4096, 4096, 12288, torch.bfloat16)])
+def test_gemm_chain_of_a_block(M, H, Q, I, wdt):
+    """(residual add + norm + first product) and then (product -> residual add + norm -> gated product ->
+    product) as the block runs them, against plain float32 math with the same roundings between the steps."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(H + M)
+    rnd = lambda *s: torch.randn(*s, generator=g)
+    stream0 = rnd(M, H)
+    delta0 = (0.3 * rnd(M, H)).bfloat16()
+    n1, n2 = (1 + 0.1 * rnd(H)).to(wdt), (1 + 0.1 * rnd(H)).to(wdt)
+    w_in = (rnd(Q + 32, H) / math.sqrt(H)).bfloat16()
+    o = rnd(M, Q).bfloat16()
+    w_o = (rnd(H, Q) / math.sqrt(Q)).bfloat16()
+    gate, up = (rnd(I, H) / math.sqrt(H)).bfloat16(), (rnd(I, H) / math.sqrt(H)).bfloat16()
+    down = (rnd(H, I) / math.sqrt(I)).bfloat16()
+    eps, off = 1e-5, 0.0
+    d = lambda t: t.to(DEV)
+    stream, other = d(stream0.clone()), torch.full((M, H), float("nan"), device=DEV)
+    proj = torch.full((M, Q + 32), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_chain(M, [ops.ChainStep(("norm", stream, other, d(delta0), d(n1), eps, off), d(w_in), proj)])
+    # plain
+    s1 = stream0 + delta0.float()
+    a1 = plain.rms_norm(s1, n1.float(), eps).bfloat16().float()
+    assert torch.equal(stream.cpu(), stream0)                                  # the input stream is left as it was
+    assert torch.allclose(other.cpu(), s1, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(proj.float().cpu(), a1 @ w_in.float().T, atol=3e-2, rtol=3e-2)
+
+    y = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    act = torch.full((M, (I + 31) // 32 * 32), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_chain(M, [ops.ChainStep(d(o), d(w_o), y),
+                       ops.ChainStep(("norm", other, stream, y, d(n2), eps, off), d(_weave8(gate, up)), act, gated=True),
+                       ops.ChainStep("previous", d(down), out)])
+    ops.check_status(DEV)
+    y_want = (o.float() @ w_o.float().T).bfloat16()
+    assert torch.allclose(y.float().cpu(), y_want.float(), atol=3e-2, rtol=3e-2)
+    s2 = s1 + y.float().cpu()
+    assert torch.allclose(stream.cpu(), s2, atol=1e-5, rtol=1e-5)
+    a2 = plain.rms_norm(s2, n2.float(), eps).bfloat16().float()
+    gg, uu = a2 @ gate.float().T, a2 @ up.float().T
+    act_want = (gg * torch.sigmoid(gg) * uu).bfloat16().float()
+    want = act_want @ down.float().T
+    scale = float(want.abs().max())
+    assert torch.allclose(out.float().cpu(), want, atol=3e-2 * max(1.0, scale), rtol=3e-2)
+    # again on the same buffers: the grid barrier and the ring are left ready for the next launch
+    out2 = torch.full_like(out, float("nan"))
+    stream_b = stream.clone()
+    ops.gemm_chain(M, [ops.ChainStep(d(o), d(w_o), y),
+                       ops.ChainStep(("norm", other, stream_b, y, d(n2), eps, off), d(_weave8(gate, up)), act, gated=True),
+                       ops.ChainStep("previous", d(down), out2)])
+    ops.check_status(DEV)
+    assert torch.equal(out2, out) and torch.equal(stream_b, stream)
