@@ -3,9 +3,8 @@
 //
 //   rb_attn_prefill   prompt portions: one CTA per (tile of 64 query rows of one segment, q head).
 //   rb_attn_decode    single decoded tokens: one CTA per (segment, kv head, split of the keys); the
-//                     G query heads of the kv head share every K/V tile (rows of one MMA tile).  The CTA
-//                     that finishes last among the splits of a (segment, kv head) merges them, so the
-//                     merge needs no launch of its own.
+//                     G query heads of the kv head share every K/V tile (rows of one MMA tile).
+//   rb_attn_combine   merges the splits of rb_attn_decode.
 //
 // Same contract as the reference's kernels (rollout/attention.py:45-142 prefill, :430-514 split
 // decode, :517-540 combine): online softmax with float32 running maximum and sum, probabilities
@@ -395,15 +394,19 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
                    const bf16* __restrict__ vpool, const int* __restrict__ dec_segs,
                    const int* __restrict__ cu_q, const int* __restrict__ seg_kv_len,
                    const int* __restrict__ block_table, int bt_stride, int page_size,
-                   float* __restrict__ part_o, float* __restrict__ part_ml, unsigned* __restrict__ arrivals,
-                   bf16* __restrict__ out,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, bf16* __restrict__ out,
                    int Hq, int Hkv, int m_tiles, float scale_log2, int window, int num_splits, FusedRope fr) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                    // 16 x D
     int* sBT = reinterpret_cast<int*>(sQ + 16 * D);                  // the block-table entries this CTA walks
     bf16* sKV = reinterpret_cast<bf16*>(sBT + BT_CAP);               // [warp][stage][K 16xD | V 16xD]
     pdl_launch_dependents();
-    pdl_wait();
+    // When this kernel itself puts the new token into the cache, every key it asks for before that was written
+    // by an earlier step, and the step's tables were uploaded before its first kernel: the first tiles can be on
+    // their way while the kernel before this one (the projections) still runs.  Otherwise the kernel before it
+    // wrote the new token's key and value, and everything waits for it.
+    const bool wait_first = !(FUSED && fr.write_kv);
+    if (wait_first) pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const int G = Hq / Hkv;
@@ -480,6 +483,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
         }
     }
 
+    if (!wait_first) pdl_wait();                                     // the projections come from the kernel before
     if (FUSED) {
         const bf16* tok = q + (size_t)tok_row * ld;                  // the raw projections of this token
         // the CTA whose keys end at the new token puts that token into the cache; the barrier below
@@ -664,47 +668,31 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
             if (d == 0) { part_ml[pidx * 2] = mg; part_ml[pidx * 2 + 1] = lg; }
         }
     }
-    if (num_splits == 1) return;
+}
 
-    // The splits of one (segment, kv head) count themselves; the one that arrives last merges them all
-    // (m_g = max m, l_g = sum l e^(m - m_g), O = sum O_s e^(m_s - m_g) / l_g; an empty split has m = -inf and
-    // drops out), in the order of the splits, whoever arrives last.  The counter is back at zero afterwards.
-    __shared__ int s_last;
-    __threadfence();                                              // this CTA's partial results, before its arrival
-    __syncthreads();
-    if (tid == 0) {
-        unsigned* cnt = arrivals + (size_t)blockIdx.x * gridDim.y + blockIdx.y;
-        const unsigned prev = atomicAdd(cnt, 1u);
-        s_last = prev == (unsigned)num_splits - 1;
-        if (s_last) atomicExch(cnt, 0u);
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    const int* __restrict__ dec_segs, const int* __restrict__ cu_q,
+                    bf16* __restrict__ out, int Hq, int num_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x, h = blockIdx.y;
+    const int tok_row = cu_q[dec_segs[i]];
+    const size_t base = ((size_t)i * Hq + h) * num_splits;
+    float mg = -INFINITY;
+    for (int s = 0; s < num_splits; ++s) mg = fmaxf(mg, part_ml[(base + s) * 2]);
+    float lg = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+        const float ms = part_ml[(base + s) * 2];
+        lg += ms == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(ms - mg);
     }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    float* wgt = reinterpret_cast<float*>(sKV);                   // [16][num_splits]: e^(m_s - m_g) / l_g
-    for (int r = warp; r < rows_valid; r += DC_WARPS) {
-        const size_t base = ((size_t)blockIdx.x * Hq + h0 + r) * num_splits;
-        float mg = -INFINITY;
-        for (int sp = lane; sp < num_splits; sp += 32) mg = fmaxf(mg, __ldcg(part_ml + (base + sp) * 2));
-        mg = warp_max(mg);
-        float lg = 0.f;
-        for (int sp = lane; sp < num_splits; sp += 32) {
-            const float ms = __ldcg(part_ml + (base + sp) * 2);
-            const float e = ms == -INFINITY ? 0.f : exp2f(ms - mg);
-            lg += __ldcg(part_ml + (base + sp) * 2 + 1) * e;
-            wgt[r * num_splits + sp] = e;
-        }
-        lg = warp_sum(lg);
-        __syncwarp();
-        for (int sp = lane; sp < num_splits; sp += 32) wgt[r * num_splits + sp] /= lg;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < rows_valid * D; idx += DC_WARPS * 32) {
-        const int r = idx / D, d = idx - r * D;
-        const size_t base = ((size_t)blockIdx.x * Hq + h0 + r) * num_splits;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float acc = 0.f;
-        for (int sp = 0; sp < num_splits; ++sp) acc += __ldcg(part_o + (base + sp) * D + d) * wgt[r * num_splits + sp];
-        out[(size_t)tok_row * Hq * D + (size_t)(h0 + r) * D + d] = __float2bfloat16_rn(acc);
+        for (int s = 0; s < num_splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            if (ms != -INFINITY) acc += part_o[(base + s) * D + d] * exp2f(ms - mg);
+        }
+        out[(size_t)tok_row * Hq * D + (size_t)h * D + d] = __float2bfloat16_rn(acc / lg);
     }
 }
 
@@ -736,11 +724,9 @@ RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const vo
                          Hq, Hkv, scale * LOG2E, window);
 }
 
-// 32-bit words of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D] and part_ml [n_dec, Hq, splits, 2]
-// as floats, then one arrival counter per (token, kv head) (at most Hq of them a token).  The counters must be
-// zero before the first launch that uses the buffer; every launch leaves them at zero.
+// Floats of scratch that rb_attn_decode needs: part_o [n_dec, Hq, splits, D], part_ml [n_dec, Hq, splits, 2].
 RB_EXPORT long long rb_attn_decode_scratch_floats(int n_dec, int Hq, int num_splits) {
-    return num_splits <= 1 ? 0 : (long long)n_dec * Hq * num_splits * (D + 2) + (long long)n_dec * Hq;
+    return num_splits <= 1 ? 0 : (long long)n_dec * Hq * num_splits * (D + 2);
 }
 
 namespace {
@@ -749,7 +735,7 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
                   int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
                   float scale, int window, int num_splits, const FusedRope* fused, cudaStream_t st) {
     if (n_dec <= 0) return 0;
-    if (num_splits < 1 || num_splits > 64 || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
+    if (num_splits < 1 || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
     const size_t pipe = (size_t)DC_WARPS * DC_STAGES * 2 * DC_N * D * sizeof(bf16);
     const size_t merge = (size_t)DC_WARPS * 16 * (D + 2) * sizeof(float);
@@ -770,19 +756,21 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
     }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_dec * Hq * num_splits * D : nullptr;
-    unsigned* arrivals = scratch ? reinterpret_cast<unsigned*>(scratch + (size_t)n_dec * Hq * num_splits * (D + 2)) : nullptr;
     dim3 grid(n_dec, Hkv * m_tiles, num_splits);
     FusedRope none = {};
     int rc;
     if (fused != nullptr)
         rc = rb_launch_pdl(attn_decode_kernel<true>, grid, dim3(DC_WARPS * 32), smem, st,
             (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
-            bt_stride, page_size, part_o, part_ml, arrivals, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused);
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, *fused);
     else
         rc = rb_launch_pdl(attn_decode_kernel<false>, grid, dim3(DC_WARPS * 32), smem, st,
             (const bf16*)q, ld, (const bf16*)kpool, (const bf16*)vpool, dec_segs, cu_q, seg_kv_len, block_table,
-            bt_stride, page_size, part_o, part_ml, arrivals, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none);
-    return rc;
+            bt_stride, page_size, part_o, part_ml, (bf16*)out, Hq, Hkv, m_tiles, scale * LOG2E, window, num_splits, none);
+    if (rc != 0 || num_splits == 1) return rc;
+    dim3 cgrid(n_dec, Hq);
+    return rb_launch_pdl(attn_combine_kernel, cgrid, dim3(128), 0, st, (const float*)part_o, (const float*)part_ml,
+                         dec_segs, cu_q, (bf16*)out, Hq, num_splits);
 }
 }  // namespace
 

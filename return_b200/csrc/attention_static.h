@@ -14,8 +14,8 @@
 // (4 MiB), which every GPU that loads the library holds until the process exits.
 //
 // Arguments are those of rb_attn_decode without `scratch`.  Returns 0, a cudaError_t of the
-// launch, or RB_ERR_SCRATCH_TOO_LARGE when n_dec * Hq * (num_splits * (HEAD_DIM + 2) + 1) exceeds
-// the array (use fewer splits or fewer tokens per call).  It calls no cudaMalloc, cudaFree or any
+// launch, or RB_ERR_SCRATCH_TOO_LARGE when n_dec * Hq * num_splits * (HEAD_DIM + 2) exceeds the
+// array (use fewer splits or fewer tokens per call).  It calls no cudaMalloc, cudaFree or any
 // allocating library routine.
 //
 // The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
@@ -23,11 +23,8 @@
 // per device and guarded by a lock, so any device and any host thread may make the first call.
 // Make that first call before any stream capture begins.
 //
-// All calls share the one array, which keeps the last call's contents.  The partial results need
-// no clearing: every slot that the merge reads was written earlier in the same call.  The
-// arrival counters behind them (one per token and kv head, by which the last split to finish
-// knows that it merges) must be zero at a call's start: the array starts zeroed when the library
-// is loaded and every call leaves the counters it used at zero again.
+// All calls share the one array, which keeps the last call's contents.  Nothing in it has to
+// start at zero: every slot that the merge step reads was written earlier in the same call.
 // Two calls that overlap on the GPU (different streams, or the same stream from two threads
 // without ordering) race on the array: keep calls of this entry point ordered on one stream.
 #pragma once

@@ -9,6 +9,14 @@
 // order, the same for both operands, which leaves the dot product unchanged and makes all loads
 // full 16-byte vectors without shared-memory staging.  Accumulation is float32.
 //
+// The RMSNorm and the residual add around a product cost no kernel of their own (rb_gemm_skinny_fused, up to 8
+// rows).  With v = stream + x W^T the norm's output is v * rstd * w, where rstd is one number per token.  The
+// product before the norm ("residual" form) stores v into the float32 stream, v * (offset + w) in bfloat16 for the
+// next product, and each CTA's share of sum(v^2); the product after it multiplies its accumulators by
+// rstd = 1 / sqrt(sum(v^2) / H + eps) in its epilogue, which gives the same number:
+// (v * rstd * w) W^T = rstd * ((v * w) W^T).  The shares are added in the order of the CTAs, so the result does not
+// depend on timing.
+//
 // Needs K % 8 == 0 and 16-byte aligned rows (ldx, ldw multiples of 8 elements).
 #include "common.cuh"
 
@@ -36,6 +44,20 @@ template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
 template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
+// What the fused forms need beside the product itself.
+struct SkinnyFused {
+    const float* ssq_in;      // [8, ssq_ld] shares of sum(v^2) of each token, or null: no scaling
+    int ssq_in_count;         // shares per token
+    int norm_dim;             // length of the normed row
+    float eps;
+    float* stream;            // residual form: [M, N] float32, contiguous
+    const void* norm_w;       // residual form: weight [N] of the norm that follows, or null: no normed rows wanted
+    int norm_w_dtype;
+    float offset;
+    float* ssq_out;           // residual form: [8, ssq_ld], this CTA writes column blockIdx.x; or null
+    int ssq_ld;
+};
+
 template <int MT, int U>
 struct Regs {                         // one buffer: U blocks of 32 k of the weight rows and of the tokens
     uint4 a0[U], a1[U], b[U][MT];
@@ -49,12 +71,16 @@ struct Regs {                         // one buffer: U blocks of 32 k of the wei
 // one sequence, and the loads of buffer i + 1 are in flight while buffer i is multiplied, also
 // across the boundary between two groups, so the weight stream never drains while a group's
 // partial sums are added up and stored.
-template <int MT, typename TOut, bool GATED>
+// FUSED 0: plain.  1: the accumulators are scaled by each token's rstd (F.ssq_in).  2: the same and the residual
+// form: out gets the normed rows for the next product (if F.norm_w), the stream gets v.  MT == 1 for FUSED != 0.
+template <int MT, typename TOut, bool GATED, int FUSED>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* __restrict__ out,
-                   int M, int N, int K, int ldx, int ldw, int ldo) {
+                   int M, int N, int K, int ldx, int ldw, int ldo, const SkinnyFused F) {
     constexpr int U = MT == 1 ? 4 : 2;                    // k32 blocks per buffer; two buffers in flight
     __shared__ float red[SK_WARPS][SK_ROWS][8 * MT + 1];
+    __shared__ float s_scale[8];
+    float ssq_acc = 0.f;                                  // residual form: this thread's part of sum(v^2) of its token
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
     const bf16* xr[MT];
@@ -134,6 +160,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
                     float gate = 0.f, up = 0.f;
 #pragma unroll
                     for (int wi = 0; wi < SK_WARPS; ++wi) { gate += red[wi][j][m]; up += red[wi][8 + j][m]; }
+                    if constexpr (FUSED != 0) { gate *= s_scale[m]; up *= s_scale[m]; }
                     store_out<TOut>(out + (size_t)m * ldo + (n0 >> 1) + j, gate / (1.0f + expf(-gate)) * up);
                 }
             }
@@ -144,7 +171,18 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
                     float s = 0.f;
 #pragma unroll
                     for (int wi = 0; wi < SK_WARPS; ++wi) s += red[wi][n][m];
-                    store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
+                    if constexpr (FUSED == 2) {
+                        float* sp = F.stream + (size_t)m * N + n0 + n;
+                        const float v = *sp + s * s_scale[m];
+                        *sp = v;
+                        ssq_acc += v * v;
+                        if (F.norm_w != nullptr)
+                            store_out<TOut>(out + (size_t)m * ldo + n0 + n,
+                                            v * (F.offset + load_as_f32(F.norm_w, F.norm_w_dtype, (size_t)(n0 + n))));
+                    } else {
+                        if constexpr (FUSED == 1) s *= s_scale[m];
+                        store_out<TOut>(out + (size_t)m * ldo + n0 + n, s);
+                    }
                 }
             }
         }
@@ -155,6 +193,19 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
     pdl_launch_dependents();
     load_w(ra, 0);                                       // weights are nobody's output: stream them at once
     pdl_wait();                                          // the tokens come from the kernel before
+    if constexpr (FUSED != 0) {
+        // warp m adds up the shares of token m, in the order of the CTAs that wrote them; the barrier inside the first
+        // finish_group stands between this and the first use
+        float scale = 1.0f;
+        if (F.ssq_in != nullptr) {
+            float part = 0.f;
+            if (warp < M)
+                for (int c = lane; c < F.ssq_in_count; c += 32) part += F.ssq_in[(size_t)warp * F.ssq_ld + c];
+            part = warp_sum(part);
+            scale = 1.0f / sqrtf(part / (float)F.norm_dim + F.eps);
+        }
+        if (lane == 0) s_scale[warp] = scale;
+    }
     load_x(ra, 0);
     for (int i = 0; i < total; i += 2) {                 // buffer i + 1 is in flight while buffer i is used
         load_w(rb, i + 1);
@@ -168,30 +219,84 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
             if ((i + 2) % nbuf == 0) finish_group(i + 1);
         }
     }
+    if constexpr (FUSED == 2) {
+        if (F.ssq_out != nullptr) {
+            // threads 0..127 hold the part of one token each (m = tid / 16) over the columns they stored
+            float s = ssq_acc;
+            s += __shfl_xor_sync(0xffffffffu, s, 8);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            if (tid < SK_ROWS * 8 && (tid & 15) == 0) F.ssq_out[(size_t)(tid >> 4) * F.ssq_ld + blockIdx.x] = s;
+        }
+    }
+}
+
+int resident_ctas() {                                     // CTAs that fit the current GPU at once
+    static int of_device[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    if (of_device[dev] == 0) {
+        int sms = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        of_device[dev] = sms * SK_CTAS_PER_SM;
+    }
+    return of_device[dev];
+}
+
+int grid_for(int N) {
+    const int groups = (N + SK_ROWS - 1) / SK_ROWS, resident = resident_ctas();
+    return groups < resident ? groups : resident;
 }
 
 template <int MT>
 int launch(const bf16* x, const bf16* w, void* out, int out_f32, int gated, int M, int N, int K, int ldx, int ldw,
            int ldo, cudaStream_t st) {
-    static int resident = 0;                              // CTAs that fit the GPU at once
-    if (resident == 0) {
-        int dev = 0, sms = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        resident = sms * SK_CTAS_PER_SM;
-    }
-    const int groups = (N + SK_ROWS - 1) / SK_ROWS;
-    const int grid = groups < resident ? groups : resident;
+    const int grid = grid_for(N);
+    if (grid <= 0) return (int)cudaErrorInvalidDevice;
+    const SkinnyFused none = {};
     if (gated)
-        return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, true>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
+        return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, true, 0>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo, none);
     if (out_f32)
-        return rb_launch_pdl(gemm_skinny_kernel<MT, float, false>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (float*)out, M, N, K, ldx, ldw, ldo);
-    return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, false>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo);
+        return rb_launch_pdl(gemm_skinny_kernel<MT, float, false, 0>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (float*)out, M, N, K, ldx, ldw, ldo, none);
+    return rb_launch_pdl(gemm_skinny_kernel<MT, bf16, false, 0>, dim3(grid), dim3(SK_WARPS * 32), 0, st, x, w, (bf16*)out, M, N, K, ldx, ldw, ldo, none);
 }
 
 }  // namespace
 
 RB_EXPORT int rb_gemm_skinny_max_rows() { return 32; }
+
+// CTAs that a product with N weight rows is launched with on the current device: the number of shares of sum(v^2)
+// that its residual form writes per token.
+RB_EXPORT int rb_gemm_skinny_ctas(int N) { return grid_for(N); }
+
+// The fused forms, for up to 8 rows, bfloat16 out.  form 0: out[M, N] = rstd * acc (or silu(rstd gate) * (rstd up) into
+// out[M, N / 2] with gated = 1), rstd from ssq_in (null: 1).  form 1 (residual): v = stream[M, N] + rstd * acc goes to the
+// stream; out[M, N] = v * (offset + norm_w) if norm_w is given; ssq_out[m][cta] = this CTA's share of sum_n v^2.
+RB_EXPORT int rb_gemm_skinny_fused(const void* x, const void* w, void* out, int form, int gated, int M, int N, int K,
+                                   int ldx, int ldw, int ldo, const float* ssq_in, int ssq_in_count, int norm_dim, float eps,
+                                   float* stream, const void* norm_w, int norm_w_dtype, float offset, float* ssq_out,
+                                   int ssq_ld, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 8 || K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return (int)cudaErrorInvalidValue;
+    if (gated && (N % 16 || form != 0)) return (int)cudaErrorInvalidValue;
+    if (form == 1 && (stream == nullptr || (norm_w != nullptr && out == nullptr))) return (int)cudaErrorInvalidValue;
+    if (form == 0 && out == nullptr) return (int)cudaErrorInvalidValue;
+    const int grid = grid_for(N);
+    if (grid <= 0) return (int)cudaErrorInvalidDevice;
+    if ((ssq_in != nullptr && (ssq_in_count < 1 || ssq_in_count > ssq_ld || norm_dim < 1)) || (ssq_out != nullptr && ssq_ld < grid))
+        return (int)cudaErrorInvalidValue;
+    SkinnyFused F;
+    F.ssq_in = ssq_in; F.ssq_in_count = ssq_in_count; F.norm_dim = norm_dim; F.eps = eps; F.stream = stream;
+    F.norm_w = norm_w; F.norm_w_dtype = norm_w_dtype; F.offset = offset; F.ssq_out = ssq_out; F.ssq_ld = ssq_ld;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)w;
+    if (form == 1)
+        return rb_launch_pdl(gemm_skinny_kernel<1, bf16, false, 2>, dim3(grid), dim3(SK_WARPS * 32), 0, st, xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, F);
+    if (gated)
+        return rb_launch_pdl(gemm_skinny_kernel<1, bf16, true, 1>, dim3(grid), dim3(SK_WARPS * 32), 0, st, xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, F);
+    return rb_launch_pdl(gemm_skinny_kernel<1, bf16, false, 1>, dim3(grid), dim3(SK_WARPS * 32), 0, st, xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, F);
+}
 
 // gated = 1: w holds gate and up rows interleaved in blocks of 8 (N % 16 == 0) and out is
 // bfloat16 [M, N / 2] = silu(gate) * up.

@@ -53,6 +53,7 @@ class ModelRunner:
         self.vocab_size = model.spec.vocab_size
         self.tilings = model.batch_tilings()   # the tables of row blocks that the model's parts read, by name
         self._graphs = {}                   # (decode batch size, what the parts fixed) -> (graph, static batch, static logits)
+        self._graph_keys = {}               # (decode batch size, span of context lengths) -> key of _graphs
         self._graph_pool = None
         self.launches_per_replay = {}       # decode batch size -> kernels of this package in its graph
 
@@ -168,8 +169,12 @@ class ModelRunner:
         return span
 
     def _graph_key(self, n: int, longest: int):
-        variant = self.model.graph_variant(n, self._span(longest))
-        return (n, tuple(sorted(variant.items(), key=repr)))
+        span = self._span(longest)
+        key = self._graph_keys.get((n, span))
+        if key is None:                      # asked of every part of every layer: once per (batch size, span), not per step
+            variant = self.model.graph_variant(n, span)
+            key = self._graph_keys[(n, span)] = (n, tuple(sorted(variant.items(), key=repr)))
+        return key
 
     def _capture(self, key):
         n, variant = key

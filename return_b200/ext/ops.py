@@ -85,6 +85,10 @@ def core() -> ctypes.CDLL:
         lib.rb_gemm_f32.argtypes = [P, P, P, I, I, I, I, I, I, P]
         lib.rb_gemm_skinny.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P]
         lib.rb_gemm_skinny.restype = c_int
+        lib.rb_gemm_skinny_fused.argtypes = [P, P, P, I, I, I, I, I, I, I, I, P, I, I, F, P, P, I, F, P, I, P]
+        lib.rb_gemm_skinny_fused.restype = c_int
+        lib.rb_gemm_skinny_ctas.argtypes = [I]
+        lib.rb_gemm_skinny_ctas.restype = c_int
         lib.rb_qk_norm_rope_write.argtypes = [P, I, P, P, I, F, F, P, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P]
         lib.rb_attention_simt.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, P]
         lib.rb_sample.argtypes = [P, I, I, I, P, P, P, P, P, P, P]
@@ -104,7 +108,6 @@ def build_all():
     """Compiles every library of the package (nvcc cross-compiles, no GPU needed); returns the paths."""
     paths = [build.library_path("return_core", _CORE_SOURCES, {"RB_PDL_MODE": PDL_MODE})]
     paths.append(build.library_path("return_tc5", _TC5_SOURCES, _tc5_defines()))
-    paths.append(build.library_path("return_chain", ["gemm_chain.cu"], {"RB_PDL_MODE": PDL_MODE}))
     for d in TC5_ATTENTION_HEAD_DIMS:
         paths.append(build.library_path(f"return_attn_tc5_d{d}", ["attention_tc5.cu"], _attn_tc5_defines(d)))
     for d in PREBUILT_HEAD_DIMS:
@@ -189,6 +192,61 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, gated: bool
     _check(core().rb_gemm_skinny(_ptr(x), _ptr(w), _ptr(out), 1 if out.dtype == torch.float32 else 0,
                                  1 if gated else 0, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream()),
            "gemm_skinny")
+
+
+class RowSums:
+    """Where a product in its residual form leaves each CTA's share of sum(v^2) per token, for the norm that follows:
+    the product that takes the normed rows multiplies its result by rstd = 1 / sqrt(sum / dim + eps) instead of
+    anyone norming them.  ``parts``: float32 [8, width]; ``count``: the shares that were written; ``dim``: the length
+    of the normed row."""
+    WIDTH = 512
+
+    def __init__(self, parts: torch.Tensor, dim: int, count: int = 0):
+        self.parts, self.dim, self.count = parts, dim, count
+
+
+def gemm_skinny_fused(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], gated: bool = False, scale=None,
+                      residual=None) -> None:
+    """The weight-streaming product for up to 8 rows with the norm and the residual add around it folded in.
+
+    ``scale`` = (RowSums, eps): the accumulators are multiplied by each token's rstd, the factor that the norm
+    before this product would have applied (its input rows are v * (offset + weight), not normed).
+    ``residual`` = (stream, next_norm, sums): v = stream + acc goes to ``stream`` (float32 [M, N]); with
+    ``next_norm`` = (weight, offset), ``out`` [M, N] gets v * (offset + weight) for the next product; ``sums``
+    (a RowSums, or None) gets the shares of sum(v^2)."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert x.dtype == w.dtype == torch.bfloat16 and M <= 8 and w.shape[1] == K
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    lib = core()
+    ssq_in, ssq_in_count, norm_dim, eps = None, 0, 0, 0.0
+    if scale is not None:
+        sums_in, eps = scale
+        assert sums_in.count > 0 and sums_in.parts.dtype == torch.float32 and sums_in.parts.is_contiguous()
+        ssq_in, ssq_in_count, norm_dim = sums_in.parts, sums_in.count, sums_in.dim
+    stream = norm_w = ssq_out = None
+    norm_w_dtype, offset = F32, 0.0
+    if residual is not None:
+        stream, next_norm, sums_out = residual
+        assert not gated and stream.dtype == torch.float32 and stream.is_contiguous() and stream.shape == (M, N)
+        if next_norm is not None:
+            norm_w, offset = next_norm
+            assert out is not None and norm_w.numel() == N
+            norm_w_dtype = dtype_code(norm_w.dtype)
+        if sums_out is not None:
+            assert sums_out.parts.dtype == torch.float32 and sums_out.parts.is_contiguous() and sums_out.dim == N
+            sums_out.count = lib.rb_gemm_skinny_ctas(N)
+            assert sums_out.count <= sums_out.parts.shape[1]
+            ssq_out = sums_out.parts
+    if out is not None:
+        assert out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.shape == (M, N // 2 if gated else N)
+    ld_sums = (ssq_in if ssq_in is not None else ssq_out).shape[1] if (ssq_in is not None or ssq_out is not None) else 0
+    if ssq_in is not None and ssq_out is not None:
+        assert ssq_in.shape[1] == ssq_out.shape[1]
+    _check(lib.rb_gemm_skinny_fused(_ptr(x), _ptr(w), _ptr(out), 1 if residual is not None else 0, 1 if gated else 0,
+                                    M, N, K, x.stride(0), w.stride(0), out.stride(0) if out is not None else 0,
+                                    _ptr(ssq_in), ssq_in_count, norm_dim, eps, _ptr(stream), _ptr(norm_w), norm_w_dtype,
+                                    offset, _ptr(ssq_out), ld_sums, _stream()), "gemm_skinny_fused")
 
 
 def skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -348,120 +406,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
     else:
         torch.mm(x, w.t(), out=out)
-
-
-# ------------------------------------------------------------------------------- chains of products for few rows
-
-CHAIN_MAX_ROWS = 8
-_chain = None
-_chain_state = {}               # device -> (barrier words, plan cache)
-
-
-class _ChainOp(ctypes.Structure):
-    _fields_ = [("w", c_void_p), ("x", c_void_p), ("stream_in", c_void_p), ("stream_out", c_void_p),
-                ("delta", c_void_p), ("norm_w", c_void_p), ("out", c_void_p),
-                ("N", c_int), ("K", c_int), ("ldw", c_int), ("ldx", c_int), ("ldo", c_int), ("ld_delta", c_int),
-                ("x_kind", c_int), ("epilogue", c_int), ("out_permuted", c_int), ("norm_w_dtype", c_int),
-                ("eps", c_float), ("offset", c_float)]
-
-
-class _ChainParams(ctypes.Structure):
-    _fields_ = [("op", _ChainOp * 4), ("n_ops", c_int), ("M", c_int), ("n_stages", c_int), ("xs_k", c_int),
-                ("barrier", c_void_p), ("status", c_void_p)]
-
-
-def chain_lib() -> ctypes.CDLL:
-    """The persistent kernel that runs a chain of matrix products for few rows (csrc/gemm_chain.cu)."""
-    global _chain
-    if _chain is None:
-        lib = build.load("return_chain", ["gemm_chain.cu"], {"RB_PDL_MODE": PDL_MODE})
-        lib.rb_gemm_chain.argtypes = [c_void_p, c_void_p]
-        lib.rb_gemm_chain.restype = c_int
-        lib.rb_gemm_chain_plan.argtypes = [c_int]
-        lib.rb_gemm_chain_plan.restype = c_int
-        if lib.rb_gemm_chain_param_bytes() != ctypes.sizeof(_ChainParams) or lib.rb_gemm_chain_op_bytes() != ctypes.sizeof(_ChainOp):
-            raise KernelError("the chain kernel's parameter block is laid out differently than this module expects")
-        _chain = lib
-    return _chain
-
-
-class ChainStep:
-    """One product of a chain: ``out = f(x) @ w^T``.
-
-    ``x``: a bfloat16 tensor [M, K]; or ``("norm", stream_in, stream_out, delta, weight, eps, offset)``:
-    x = rmsnorm(stream_in + delta) * (offset + weight) with the sum written to ``stream_out`` (float32 [M, K],
-    another tensor than ``stream_in``; ``delta`` bfloat16 [M, K] or None); or ``"previous"``: the output of the
-    step before.  ``gated``: ``w`` holds gate and up rows woven in blocks of 8 and ``out`` is [M, N / 2] = silu(gate) * up."""
-
-    def __init__(self, x, w, out, gated=False):
-        self.x, self.w, self.out, self.gated = x, w, out, gated
-
-
-def chain_ok(M: int, steps) -> bool:
-    """Whether the chain kernel takes these products: few rows, bfloat16, k a multiple of 16, aligned rows."""
-    if not (1 <= M <= CHAIN_MAX_ROWS) or not (1 <= len(steps) <= 4):
-        return False
-    for i, st in enumerate(steps):
-        w = st.w
-        if w.dtype != torch.bfloat16 or w.shape[1] % 16 or w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16:
-            return False
-        if st.gated and w.shape[0] % 16:
-            return False
-        if isinstance(st.x, str) and i == 0:
-            return False
-    return True
-
-
-def gemm_chain(M: int, steps, held=None) -> None:
-    """Runs the steps as one persistent kernel (see ``ChainStep``).  The output of a step that the next one takes
-    as ``"previous"`` is kept in an order of the kernel's own and must not be read by anyone else; ``held``: the
-    step's map of work buffers."""
-    lib = chain_lib()
-    dev = steps[0].w.device
-    state = _chain_state.get(dev)
-    if state is None:
-        state = _chain_state[dev] = (torch.zeros(2, dtype=torch.int32, device=dev), {})
-    barrier, plans = state
-    xs_k = 32
-    for st in steps:
-        if not isinstance(st.x, str):
-            xs_k = max(xs_k, (st.w.shape[1] + 31) // 32 * 32)
-    n_stages = plans.get(xs_k)
-    if n_stages is None:
-        with torch.cuda.device(dev):
-            n_stages = plans[xs_k] = lib.rb_gemm_chain_plan(xs_k)
-    if n_stages <= 0:
-        raise KernelError(f"the chain kernel has no room for rows of {xs_k} elements beside its ring")
-    P = _ChainParams()
-    P.n_ops, P.M, P.n_stages, P.xs_k = len(steps), M, n_stages, xs_k
-    P.barrier, P.status = _ptr(barrier), _ptr(tc5_status(dev))
-    _tc5_launched.add(dev)
-    for i, st in enumerate(steps):
-        op = P.op[i]
-        N, K = st.w.shape
-        assert st.out.dtype == torch.bfloat16 and st.out.shape[0] >= M and st.out.stride(1) == 1
-        op.w, op.N, op.K, op.ldw = _ptr(st.w), N, K, st.w.stride(0)
-        op.out, op.ldo, op.epilogue = _ptr(st.out), st.out.stride(0), 1 if st.gated else 0
-        nxt = steps[i + 1] if i + 1 < len(steps) else None
-        op.out_permuted = 1 if (nxt is not None and isinstance(nxt.x, str)) else 0
-        if op.out_permuted:
-            assert st.out.stride(0) % 32 == 0, "an output that the next step takes needs rows of a multiple of 32 elements"
-        if isinstance(st.x, str):
-            prev = steps[i - 1].out
-            assert st.x == "previous" and prev.shape[1] >= K
-            op.x_kind, op.x, op.ldx = 2, _ptr(prev), prev.stride(0)
-        elif isinstance(st.x, tuple):
-            kind, s_in, s_out, delta, weight, eps, offset = st.x
-            assert kind == "norm" and s_in.dtype == torch.float32 and s_in.is_contiguous() and s_in.shape[1] == K
-            assert s_out is None or (s_out.dtype == torch.float32 and s_out.is_contiguous() and s_out.data_ptr() != s_in.data_ptr())
-            assert delta is None or (delta.dtype == torch.bfloat16 and delta.stride(1) == 1)
-            op.x_kind, op.stream_in, op.stream_out = 1, _ptr(s_in), _ptr(s_out)
-            op.delta, op.ld_delta = _ptr(delta), (delta.stride(0) if delta is not None else 0)
-            op.norm_w, op.norm_w_dtype, op.eps, op.offset = _ptr(weight), dtype_code(weight.dtype), eps, offset
-        else:
-            assert st.x.dtype == torch.bfloat16 and st.x.shape[1] == K and st.x.stride(1) == 1
-            op.x_kind, op.x, op.ldx = 0, _ptr(st.x), st.x.stride(0)
-    _check(lib.rb_gemm_chain(ctypes.byref(P), _stream()), "gemm_chain")
 
 
 # ------------------------------------------------------------------------------- attention
@@ -657,8 +601,7 @@ def _split_scratch(lib, n, num_heads, num_splits, device, held=None):
     if held is not None and key in held:
         return held[key]
     floats = lib.rb_attn_decode_scratch_floats(n, num_heads, num_splits)
-    # zeroed once: the arrival counters at its end must start at zero, and every launch leaves them so
-    scratch = torch.zeros(floats, dtype=torch.float32, device=device) if floats else None
+    scratch = torch.empty(floats, dtype=torch.float32, device=device) if floats else None
     if held is not None:
         held[key] = scratch
     return scratch
@@ -674,7 +617,7 @@ def attention_decode_mma(qkv, k_pool, v_pool, decode_segs, cu_q, seg_kv_len, blo
     _check(lib.rb_attn_decode(_ptr(qkv), qkv.stride(0), _ptr(k_pool), _ptr(v_pool), _ptr(decode_segs), n,
                               _ptr(cu_q), _ptr(seg_kv_len), _ptr(block_table), block_table.stride(0), page_size,
                               _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale, int(window or 0),
-                              num_splits, _stream()), "attention_decode")
+                              num_splits, _stream()), "attention_decode", 2 if num_splits > 1 else 1)
 
 
 def _decode_split_count(batch, num_heads, num_kv_heads, window) -> int:
@@ -731,8 +674,8 @@ def decode_only(batch, dtype, num_heads, num_kv_heads, window=None) -> bool:
 def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_dim, k_pool, v_pool, batch,
                            block_table, page_size, out, num_heads, num_kv_heads, head_dim, scale, window=None,
                            write_kv=True) -> None:
-    """A step of single tokens: per-head q/k norm, rotation, cache write, split-KV attention and the merge of the
-    splits in one kernel.  ``qkv`` holds the raw projections and is left as it is."""
+    """A step of single tokens: per-head q/k norm, rotation, cache write and split-KV attention in one kernel
+    (plus the merge of the splits).  ``qkv`` holds the raw projections and is left as it is."""
     assert qkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and out.is_contiguous()
     lib = attention_lib(head_dim)
     n = batch.decode_segs.shape[0]
@@ -749,7 +692,7 @@ def attention_decode_fused(qkv, q_weight, k_weight, eps, offset, cos, sin, rot_d
                                     page_size, _ptr(scratch), _ptr(out), num_heads, num_kv_heads, scale,
                                     int(window or 0), splits, _ptr(q_weight), _ptr(k_weight), wd, eps, offset,
                                     _ptr(cos), _ptr(sin), rot_dim, 1 if write_kv else 0, _stream()),
-           "attention_decode_fused")
+           "attention_decode_fused", 2 if splits > 1 else 1)
 
 
 def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num_heads, num_kv_heads,

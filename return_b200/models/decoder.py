@@ -89,9 +89,12 @@ class DecoderModel:
         stream = torch.empty((T, H), dtype=torch.float32, device=dev)
         ops.embedding(self.embed, batch.tokens, stream)
         delta = None
-        for index, entry in enumerate(self.spec.schedule):
+        schedule = self.spec.schedule
+        for index, entry in enumerate(schedule):
             owner = index if entry.cache_of is None else entry.cache_of
             ctx = storage.layer_context(owner, batch, write=entry.cache_of is None)
+            ctx.position = index
+            ctx.next_block = self.blocks[schedule[index + 1].layer] if index + 1 < len(schedule) else None
             delta = self.blocks[entry.layer].forward(stream, delta, ctx)
         n_want = batch.num_want
         logits = torch.empty((n_want, self.spec.vocab_size), dtype=torch.float32, device=dev)

@@ -79,6 +79,9 @@ class LayerContext:
     kv: Optional[KVView] = None
     state: Optional[torch.Tensor] = None      # [num_slots, *StateNeed.shape]; row = batch.seg_slot
     write_cache: bool = True
+    position: int = -1                        # index of this run in the model's schedule
+    next_block: Any = None                    # the block that runs after this one in this step, or None (a block may
+                                              # prepare what its successor's first norm needs)
 
     def buffer(self, name: str, shape, dtype, device) -> torch.Tensor:
         """An uninitialised work buffer for the part that asks.  The layers of a step run one after the
@@ -163,6 +166,10 @@ class FeedForward(Part):
 
 class Block(Part):
     def cache_need(self):
+        return None
+
+    def first_norm(self):
+        """(weight, eps, offset, size) if the block's first act is an RMSNorm of the residual stream, else None."""
         return None
 
     def forward(self, stream, delta, ctx: LayerContext):

@@ -626,79 +626,62 @@ def test_sample_frequencies():
     assert (freq - probs).abs().max() < 0.03
 
 
-# ------------------------------------------------------------------------------- chains of products for few rows
+# ------------------------------------------------------------------------------- norms and residual adds inside the products
 
 def _weave8(gate, up):
     return torch.stack([gate.view(-1, 8, gate.shape[1]), up.view(-1, 8, up.shape[1])], dim=1).reshape(-1, gate.shape[1])
 
 
-@pytest.mark.parametrize("M", [1, 3, 8])
-@pytest.mark.parametrize("N,K", [(48, 64), (100, 96), (40, 272), (6144, 4096), (4096, 12288)])
-def test_gemm_chain_single_product(M, N, K):
-    """One product through the persistent kernel: rows that are no multiple of 16, k that is no multiple of
-    the stage, more and fewer units than SMs."""
-    ops = _ops()
-    g = torch.Generator().manual_seed(N + K + M)
-    x = torch.randn(M, K, generator=g).bfloat16()
-    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).bfloat16()
-    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    assert ops.chain_ok(M, [ops.ChainStep(x.to(DEV), w.to(DEV), out)])
-    ops.gemm_chain(M, [ops.ChainStep(x.to(DEV), w.to(DEV), out)])
-    ops.check_status(DEV)
-    want = x.float() @ w.float().T
-    assert torch.allclose(out.float().cpu(), want, atol=2e-2, rtol=2e-2)
-
-
 @pytest.mark.parametrize("M", [1, 5, 8])
 @pytest.mark.parametrize("H,Q,I,wdt", [(96, 192, 224, torch.float32), (64, 64, 128, torch.bfloat16), (4096, 4096, 12288, torch.bfloat16)])
-def test_gemm_chain_of_a_block(M, H, Q, I, wdt):
-    """(residual add + norm + first product) and then (product -> residual add + norm -> gated product ->
-    product) as the block runs them, against plain float32 math with the same roundings between the steps."""
+def test_gemm_skinny_fused_forms_of_a_block(M, H, Q, I, wdt):
+    """(product + residual add) -> (gated product scaled by the norm's rstd) -> (product + residual add), then the
+    next block's first product from what was left for its norm, as the block runs them for a step of few rows;
+    against plain float32 math: stream, norms, SwiGLU and all."""
     ops = _ops()
     g = torch.Generator().manual_seed(H + M)
     rnd = lambda *s: torch.randn(*s, generator=g)
     stream0 = rnd(M, H)
-    delta0 = (0.3 * rnd(M, H)).bfloat16()
-    n1, n2 = (1 + 0.1 * rnd(H)).to(wdt), (1 + 0.1 * rnd(H)).to(wdt)
-    w_in = (rnd(Q + 32, H) / math.sqrt(H)).bfloat16()
+    n2, n_next = (1 + 0.1 * rnd(H)).to(wdt), (1 + 0.1 * rnd(H)).to(wdt)
     o = rnd(M, Q).bfloat16()
     w_o = (rnd(H, Q) / math.sqrt(Q)).bfloat16()
     gate, up = (rnd(I, H) / math.sqrt(H)).bfloat16(), (rnd(I, H) / math.sqrt(H)).bfloat16()
     down = (rnd(H, I) / math.sqrt(I)).bfloat16()
-    eps, off = 1e-5, 0.0
+    w_in = (rnd(Q + 32, H) / math.sqrt(H)).bfloat16()
+    eps = 1e-5
     d = lambda t: t.to(DEV)
-    stream, other = d(stream0.clone()), torch.full((M, H), float("nan"), device=DEV)
-    proj = torch.full((M, Q + 32), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.gemm_chain(M, [ops.ChainStep(("norm", stream, other, d(delta0), d(n1), eps, off), d(w_in), proj)])
-    # plain
-    s1 = stream0 + delta0.float()
-    a1 = plain.rms_norm(s1, n1.float(), eps).bfloat16().float()
-    assert torch.equal(stream.cpu(), stream0)                                  # the input stream is left as it was
-    assert torch.allclose(other.cpu(), s1, atol=1e-6, rtol=1e-6)
-    assert torch.allclose(proj.float().cpu(), a1 @ w_in.float().T, atol=3e-2, rtol=3e-2)
+    nan = lambda *shape, dt=torch.bfloat16: torch.full(shape, float("nan"), dtype=dt, device=DEV)
 
-    y = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
-    act = torch.full((M, (I + 31) // 32 * 32), float("nan"), dtype=torch.bfloat16, device=DEV)
-    out = torch.full((M, H), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.gemm_chain(M, [ops.ChainStep(d(o), d(w_o), y),
-                       ops.ChainStep(("norm", other, stream, y, d(n2), eps, off), d(_weave8(gate, up)), act, gated=True),
-                       ops.ChainStep("previous", d(down), out)])
-    ops.check_status(DEV)
-    y_want = (o.float() @ w_o.float().T).bfloat16()
-    assert torch.allclose(y.float().cpu(), y_want.float(), atol=3e-2, rtol=3e-2)
-    s2 = s1 + y.float().cpu()
-    assert torch.allclose(stream.cpu(), s2, atol=1e-5, rtol=1e-5)
-    a2 = plain.rms_norm(s2, n2.float(), eps).bfloat16().float()
+    def run(stream):
+        rows2, act, rows3, proj = nan(M, H), nan(M, I), nan(M, H), nan(M, Q + 32)
+        sums2 = ops.RowSums(nan(8, ops.RowSums.WIDTH, dt=torch.float32), H)
+        sums3 = ops.RowSums(nan(8, ops.RowSums.WIDTH, dt=torch.float32), H)
+        ops.gemm_skinny_fused(d(o), d(w_o), rows2, residual=(stream, (d(n2), 0.0), sums2))
+        ops.gemm_skinny_fused(rows2, d(_weave8(gate, up)), act, gated=True, scale=(sums2, eps))
+        ops.gemm_skinny_fused(act, d(down), rows3, residual=(stream, (d(n_next), 0.0), sums3))
+        ops.gemm_skinny_fused(rows3, d(w_in), proj, scale=(sums3, eps))
+        return act, rows3, sums3, proj
+
+    stream = d(stream0.clone())
+    act, rows3, sums3, proj = run(stream)
+    # plain
+    s1 = stream0 + o.float() @ w_o.float().T
+    a2 = plain.rms_norm(s1, n2.float(), eps)
     gg, uu = a2 @ gate.float().T, a2 @ up.float().T
-    act_want = (gg * torch.sigmoid(gg) * uu).bfloat16().float()
-    want = act_want @ down.float().T
-    scale = float(want.abs().max())
-    assert torch.allclose(out.float().cpu(), want, atol=3e-2 * max(1.0, scale), rtol=3e-2)
-    # again on the same buffers: the grid barrier and the ring are left ready for the next launch
-    out2 = torch.full_like(out, float("nan"))
-    stream_b = stream.clone()
-    ops.gemm_chain(M, [ops.ChainStep(d(o), d(w_o), y),
-                       ops.ChainStep(("norm", other, stream_b, y, d(n2), eps, off), d(_weave8(gate, up)), act, gated=True),
-                       ops.ChainStep("previous", d(down), out2)])
-    ops.check_status(DEV)
-    assert torch.equal(out2, out) and torch.equal(stream_b, stream)
+    act_want = gg * torch.sigmoid(gg) * uu
+    s2 = s1 + act_want @ down.float().T
+    assert torch.allclose(act.float().cpu(), act_want, atol=3e-2 * max(1.0, float(act_want.abs().max())), rtol=3e-2)
+    assert torch.allclose(stream.cpu(), s2, atol=2e-2 * max(1.0, float(s2.abs().max())), rtol=2e-2)
+    # the sums left for the next norm are those of the stream as the kernel left it
+    got_ssq = sums3.parts[:M, :sums3.count].sum(dim=1).cpu()
+    assert torch.allclose(got_ssq, (stream.cpu() ** 2).sum(dim=1), rtol=1e-5)
+    want = plain.rms_norm(stream.cpu(), n_next.float(), eps) @ w_in.float().T
+    assert torch.allclose(proj.float().cpu(), want, atol=3e-2 * max(1.0, float(want.abs().max())), rtol=3e-2)
+    # a last product with nothing behind it: only the stream
+    only = d(stream0.clone())
+    ops.gemm_skinny_fused(d(o), d(w_o), None, residual=(only, None, None))
+    assert torch.allclose(only.cpu(), s1, atol=2e-2 * max(1.0, float(s1.abs().max())), rtol=2e-2)
+    # again from the same start: nothing depends on timing
+    stream_b = d(stream0.clone())
+    act_b, rows3_b, _, proj_b = run(stream_b)
+    assert torch.equal(stream_b, stream) and torch.equal(act_b, act) and torch.equal(rows3_b, rows3) and torch.equal(proj_b, proj)
