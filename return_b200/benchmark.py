@@ -80,6 +80,67 @@ def prefill_throughput(runner, tokens: int, iters: int, warmup: int, seed: int =
     return {"tokens_per_s": tokens * 1000.0 / ms, "ms": ms, "tokens": tokens}
 
 
+# Kernel names of a decode step by kind, after the reference's table (rollout/utils/prof_graph.py:27-43): its
+# kinds, the names of this engine's kernels (and of the library's matrix products).
+PROFILE_BUCKETS = [
+    ("decode_attn", ["attn_decode", "attn_combine"]),
+    ("prefill_attn", ["attn_prefill", "attention_simt", "tc5_merge"]),
+    ("gemm/matmul", ["gemm", "nvjet", "cutlass", "cublas", "matmul"]),
+    ("rmsnorm", ["rmsnorm", "norm_rows"]),
+    ("rope", ["rope"]),
+    ("elementwise", ["swiglu", "embedding", "elementwise", "copy", "fill"]),
+    ("softmax/sample", ["sample", "argmax"]),
+]
+
+
+def profile_bucket(kernel_name: str) -> str:
+    low = kernel_name.lower()
+    for label, keys in PROFILE_BUCKETS:
+        if any(k in low for k in keys):
+            return label
+    return "other"
+
+
+def profile_decode(runner, batch: int, ctx: int, steps: int, warmup: int, seed: int = 1) -> Dict[str, object]:
+    """Where the device time of decode steps goes, by kind of kernel: the table that the reference prints with
+    ``torch.profiler`` over graph-replayed decode steps (rollout/utils/prof_graph.py:76-107).  CUDA activity only;
+    times are each kernel's own device time summed, so kernels that overlap count twice and the sum may exceed
+    the step's wall time."""
+    from collections import defaultdict
+    from torch.profiler import ProfilerActivity, profile
+    rids = fill_requests(runner, batch, ctx, seed, prefix="prof")
+    gen = torch.Generator().manual_seed(seed + 1)
+    toks = [_random_ids(runner.vocab_size, batch, gen) for _ in range(steps + warmup)]
+
+    def one(k):
+        return runner.step([runner.reserve(rid, [toks[k][i]], [0]) for i, rid in enumerate(rids)])
+
+    for k in range(warmup):
+        one(k)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA], record_shapes=False) as prof:
+        for k in range(warmup, warmup + steps):
+            one(k)
+        torch.cuda.synchronize()
+    for rid in rids:
+        runner.free_request(rid)
+    bucket, count, per_kernel = defaultdict(float), defaultdict(int), defaultdict(float)
+    for e in prof.key_averages():
+        us = getattr(e, "self_device_time_total", 0) or getattr(e, "self_cuda_time_total", 0)
+        if us <= 0:
+            continue
+        b = profile_bucket(e.key)
+        bucket[b] += us
+        count[b] += e.count
+        per_kernel[e.key] += us
+    total = sum(bucket.values()) or 1.0
+    return {"batch": batch, "ctx": ctx, "steps": steps, "gpu_ms_per_step": total / 1e3 / steps,
+            "buckets": [{"bucket": b, "ms_per_step": us / 1e3 / steps, "share": us / total, "kernels_per_step": count[b] / steps}
+                        for b, us in sorted(bucket.items(), key=lambda kv: -kv[1])],
+            "top_kernels": [{"kernel": k[:80], "ms_per_step": us / 1e3 / steps, "share": us / total}
+                            for k, us in sorted(per_kernel.items(), key=lambda kv: -kv[1])[:12]]}
+
+
 def decode_step_bytes(cfg, batch: int, kv_tokens_total: int, dtype_bytes: int = 2) -> int:
     """Bytes a decode step has to read: every weight it uses once (the embedding rows it gathers
     are negligible and left out; a tied head is counted once, as the head), plus the cached keys and
@@ -215,6 +276,32 @@ def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> D
     ms = _time_kernels(fns, iters, warmup)
     return {"kernel": ("linear", "gemm_tc5", "cublas", "gemm_stream", "gemm_skinny")[impl], "M": M, "N": N, "K": K, "ms": ms, "GBps": N * K * 2 / ms / 1e6,
             "TFLOPs": 2.0 * M * N * K / ms / 1e9}
+
+
+def kernel_elementwise(rows=2048, hidden=4096, intermediate=12288, iters=10, warmup=3) -> Dict[str, object]:
+    """The residual add + RMSNorm kernel and the SwiGLU kernel alone, over buffers larger than L2: device time and
+    the bandwidth of what each must read and write (norm: stream in and out in float32, delta in, normed rows out;
+    SwiGLU: [rows, 2 I] in, [rows, I] out)."""
+    from .ext import ops
+    dev = torch.device("cuda:0")
+    w = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+    norm_bytes = rows * hidden * (4 + 4 + 2 + 2)
+    fns = []
+    for _ in range(_copies_beyond_l2(norm_bytes)):
+        stream = torch.randn(rows, hidden, device=dev)
+        delta = torch.randn(rows, hidden, device=dev).bfloat16()
+        out = torch.empty(rows, hidden, device=dev, dtype=torch.bfloat16)
+        fns.append(lambda a=(stream, delta, out): ops.add_rmsnorm(a[0], a[1], w, 1e-6, a[2]))
+    ms_norm = _time_kernels(fns, iters, warmup)
+    act_bytes = rows * intermediate * 3 * 2
+    fns = []
+    for _ in range(_copies_beyond_l2(act_bytes)):
+        gu = torch.randn(rows, 2 * intermediate, device=dev).bfloat16()
+        out = torch.empty(rows, intermediate, device=dev, dtype=torch.bfloat16)
+        fns.append(lambda a=(gu, out): ops.swiglu(a[0], a[1], 8))
+    ms_act = _time_kernels(fns, iters, warmup)
+    return {"rows": rows, "add_rmsnorm": {"ms": ms_norm, "GBps": norm_bytes / ms_norm / 1e6},
+            "swiglu": {"ms": ms_act, "GBps": act_bytes / ms_act / 1e6}}
 
 
 def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[str, float]:

@@ -88,6 +88,15 @@ def cmd_bench(args) -> int:
     for b in [int(x) for x in args.batch.split(",")]:
         r = benchmark.decode_throughput(engine.runner, b, args.ctx, args.steps, args.warmup)
         print(json.dumps({"batch": b, "ctx": args.ctx, **r}))
+        if args.profile:
+            p = benchmark.profile_decode(engine.runner, b, args.ctx, args.steps, args.warmup)
+            print(f"bs={b} ctx={args.ctx}  GPU busy {p['gpu_ms_per_step']:.3f} ms/step")
+            print(f"{'bucket':<18}{'ms/step':>10}{'%GPU':>8}{'kern/step':>11}")
+            for row in p["buckets"]:
+                print(f"{row['bucket']:<18}{row['ms_per_step']:>10.3f}{row['share'] * 100:>7.1f}%{row['kernels_per_step']:>11.1f}")
+            print("--- top kernels (own device time) ---")
+            for row in p["top_kernels"]:
+                print(f"{row['ms_per_step']:>8.3f} ms {row['share'] * 100:>5.1f}%  {row['kernel']}")
     r = benchmark.prefill_throughput(engine.runner, args.prompt_len, max(1, args.steps // 4), max(1, args.warmup // 2))
     print(json.dumps({"prefill_tokens": args.prompt_len, **r}))
     return 0
@@ -102,7 +111,7 @@ def cmd_workload(args) -> int:
 def cmd_kernel_bench(args) -> int:
     from . import benchmark
     fn = {"attention_decode": benchmark.kernel_attention_decode, "attention_prefill": benchmark.kernel_attention_prefill,
-          "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated}[args.kernel]
+          "gemm": benchmark.kernel_gemm, "gated": benchmark.kernel_gated, "elementwise": benchmark.kernel_elementwise}[args.kernel]
     kw = {}
     for item in args.set or []:
         k, v = item.split("=")
@@ -160,6 +169,8 @@ def main(argv=None) -> int:
     b.add_argument("--prompt-len", type=int, default=2048)
     b.add_argument("--steps", type=int, default=50)
     b.add_argument("--warmup", type=int, default=10)
+    b.add_argument("--profile", action="store_true",
+                   help="after each batch size, the share of device time by kind of kernel (GEMM, decode attention, norm, ...)")
     b.set_defaults(fn=cmd_bench)
 
     wl = sub.add_parser("workload", help="a named workload through the engine, random weights of that shape")
@@ -169,7 +180,7 @@ def main(argv=None) -> int:
     wl.set_defaults(fn=cmd_workload)
 
     k = sub.add_parser("kernel-bench", help="time one kernel alone on random data (for profiles)")
-    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated"])
+    k.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm", "gated", "elementwise"])
     k.add_argument("--set", action="append", help="an integer argument of the kernel case, e.g. batch=64 ctx=2048 M=8")
     k.set_defaults(fn=cmd_kernel_bench)
 

@@ -35,3 +35,18 @@ def test_decode_key_splits():
             assert s == 1 or (keys + s - 1) // s >= 128            # a share keeps at least 128 keys
     assert ops.decode_splits(512, 2048) == 1                      # more CTAs than the GPU holds at once: no split
     assert ops.decode_splits(8, 32768) > ops.decode_splits(8, 2048) >= 2
+
+
+def test_profile_buckets_know_the_engines_kernels():
+    from return_b200 import benchmark
+    names = {"void (anonymous namespace)::gemm_skinny_kernel<1, __nv_bfloat16, 0, 2>(...)": "gemm/matmul",
+             "nvjet_tst_64x32_64x8_4x1_v_bz_TNT": "gemm/matmul",
+             "void (anonymous namespace)::attn_decode_kernel<true>(...)": "decode_attn",
+             "(anonymous namespace)::attn_combine_kernel(...)": "decode_attn",
+             "attn_prefill_tc5_kernel": "prefill_attn",
+             "void add_rmsnorm_vec_kernel<__nv_bfloat16, __nv_bfloat16, 4>(...)": "rmsnorm",
+             "void qk_norm_rope_write_vec_kernel<8>(...)": "rope",
+             "void swiglu_bf16x8_kernel(...)": "elementwise",
+             "void sample_kernel(...)": "softmax/sample", "something_else": "other"}
+    for kernel, want in names.items():
+        assert benchmark.profile_bucket(kernel) == want, kernel
