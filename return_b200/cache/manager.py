@@ -95,6 +95,9 @@ class CacheManager:
         self.max_requests = max_requests
         self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._req: Dict[Hashable, _RequestState] = {}
+        # False when something beside the pages depends on every token a request has run (per-request state on the
+        # device): a request's length can then not be taken back
+        self.truncatable = True
         # called with the slot whenever a request takes one: whoever keeps per-request state on the device
         # starts the slot from zero here, so that every way of admitting a request (replay, scheduler,
         # re-admission after a preemption) resets it
@@ -198,6 +201,23 @@ class CacheManager:
         old = st.length
         st.length += n_tokens
         return old
+
+    def truncate(self, rid, length: int) -> None:
+        """Takes the last tokens of a request back: its length becomes ``length`` (not more than it is) and the
+        pages behind it return to their pools.  What lies in the kept pages beyond ``length`` is overwritten by
+        the tokens that come next."""
+        st = self._req[rid]
+        if not (0 <= length <= st.length):
+            raise ValueError(f"request {rid!r} holds {st.length} tokens; cannot truncate to {length}")
+        if length < st.length and not self.truncatable:
+            raise ValueError("per-request state depends on the tokens that were run: nothing can be taken back")
+        for g, pool, blocks in zip(self.groups, self.pools, st.blocks):
+            keep = (length + g.page_size - 1) // g.page_size
+            gone = [p for p in blocks[keep:] if p >= 0]
+            if gone:
+                pool.give_back(gone)
+            del blocks[keep:]
+        st.length = length
 
     # ------------------------------------------------------------------ accounting, for tests and stats
     def pages_used(self) -> List[int]:

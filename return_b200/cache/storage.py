@@ -71,6 +71,7 @@ class CacheStorage:
     def make_manager(self) -> CacheManager:
         manager = CacheManager(self.group_specs, self.max_reside)
         manager.on_slot_taken.append(self.reset_slot)
+        manager.truncatable = not self._state_needs
         return manager
 
     def allocate(self) -> None:

@@ -6,7 +6,9 @@
 ``prefill_chunk`` most tokens one step runs (PREFILL_CHUNK, rollout/constant.py:5);
 ``use_cuda_graph`` replay captured graphs for steps that only decode (USE_CUDA_GRAPH, :3);
 ``capture_at_start`` capture them all when the engine is built, as the reference does
-(rollout/model.py:346-407), instead of each on its first use.
+(rollout/model.py:346-407), instead of each on its first use;
+``keep_sessions`` a request that ends keeps its cache for a follow-up request with the same id, until
+``release`` or until the pages are needed (the reference always keeps, rollout/engine.py:286-306).
 """
 from __future__ import annotations
 
@@ -26,6 +28,7 @@ class EngineConfig:
     max_model_len: Optional[int] = None   # longest sequence; default min(max_position_embeddings, max_token)
     use_cuda_graph: bool = True
     capture_at_start: bool = False
+    keep_sessions: bool = False
     seed: int = 0
     device: str = "cuda:0"
 

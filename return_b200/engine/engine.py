@@ -36,7 +36,8 @@ class Engine:
             import dataclasses
             self.config = dataclasses.replace(config or EngineConfig(), **overrides)
             self.runner = ModelRunner.from_model_dir(model, self.config)
-        self.scheduler = Scheduler(self.runner.manager, self.config.prefill_chunk, self.runner.max_positions)
+        self.scheduler = Scheduler(self.runner.manager, self.config.prefill_chunk, self.runner.max_positions,
+                                   keep_sessions=self.config.keep_sessions)
         self.sampler = Sampler(self.runner.env.device, max(16, self.config.max_reside))
         if self.config.capture_at_start and self.runner.runs_ahead():
             self.runner.capture_decode_graphs()
@@ -54,6 +55,11 @@ class Engine:
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()
+
+    def release(self, rid) -> bool:
+        """Gives back the cache that an ended request kept (``keep``), as the reference's ``release`` does
+        (rollout/engine.py:276-284)."""
+        return self.scheduler.release(rid)
 
     def step(self) -> List[Request]:
         """One scheduling decision and one step of the model.  Returns the requests that ended in it
@@ -154,8 +160,7 @@ class Engine:
             self._steps += 1
             self._dc_tok += n
         for r in ended:
-            mgr.free(r.id)
-            sch.running.remove(r)
+            sch.finish(r)
         self._acc_decode += time.perf_counter() - t0
         return ended
 
@@ -181,10 +186,13 @@ class Engine:
     def generate(self, prompts: Sequence[Union[Request, Sequence[int]]], max_new_tokens: int = 32,
                  temperature: float = 1.0, top_p: float = 1.0, top_k: int = 0,
                  stop_ids: Optional[List[List[int]]] = None, seed: Optional[int] = None,
-                 eos_token_id: Optional[int] = None) -> List[GenerationResult]:
+                 eos_token_id: Optional[int] = None, keep: Optional[bool] = None,
+                 ids: Optional[Sequence[Hashable]] = None) -> List[GenerationResult]:
         """Generates for every prompt (token ids, or ``Request`` records with their own options) and
         returns the results in the order given.  ``eos_token_id`` is a stop sequence of one token.  A
-        request that cannot fit the pool raises ``KVCapacityError``."""
+        request that cannot fit the pool raises ``KVCapacityError``.  ``ids`` names the requests (sessions);
+        with ``keep`` a request's cache stays when it ends, and a later call whose prompt for the same id
+        begins with that request's prompt and output runs only what is new."""
         stop_ids = list(stop_ids or [])
         if eos_token_id is not None:
             stop_ids.append([int(eos_token_id)])
@@ -193,9 +201,9 @@ class Engine:
             if isinstance(p, Request):
                 r = p
             else:
-                r = Request(id=f"gen-{self._auto_id}", prompt_ids=list(p), max_new_tokens=max_new_tokens,
-                            temperature=temperature, top_p=top_p, top_k=top_k, stop_ids=list(stop_ids or []),
-                            seed=None if seed is None else seed + i)
+                r = Request(id=ids[i] if ids is not None else f"gen-{self._auto_id}", prompt_ids=list(p),
+                            max_new_tokens=max_new_tokens, temperature=temperature, top_p=top_p, top_k=top_k,
+                            stop_ids=list(stop_ids or []), seed=None if seed is None else seed + i, keep=keep)
                 self._auto_id += 1
             self.add_request(r)
             reqs.append(r)
@@ -228,7 +236,7 @@ class Engine:
             "decode_tps": self.decode_tps, "prefill_tps": self.prefill_tps,
             "decode_duty": self._acc_decode / rt if rt > 0 else 0.0,
             "prefill_duty": self._acc_prefill / rt if rt > 0 else 0.0,
-            "preemptions": self._preemptions,
+            "preemptions": self._preemptions, "kept_sessions": len(self.scheduler.kept),
             # the pages of every group of layers (a model with full and window layers has two pools)
             "page_used": sum(m.pages_used()), "page_total": sum(g.num_pages for g in m.groups),
             "page_groups": [{"name": g.name, "used": u, "total": g.num_pages, "window": g.window}
@@ -241,8 +249,8 @@ class AsyncEngine:
 
     ``submit`` resolves when the request has finished and returns it; a request that cannot fit
     raises ``KVCapacityError`` from ``submit``.  Steps run in a worker thread, as the reference runs
-    its model calls (rollout/engine.py:370,394).  A finished request holds nothing here, so
-    ``release`` has nothing to give back and exists for callers written against the reference."""
+    its model calls (rollout/engine.py:370,394).  ``release`` gives back what a finished request kept
+    (``Request.keep`` or ``EngineConfig.keep_sessions``); without either a finished request holds nothing."""
 
     def __init__(self, engine: Engine):
         self.engine = engine
@@ -274,7 +282,7 @@ class AsyncEngine:
         return await fut
 
     def release(self, rid) -> None:
-        return None
+        self.engine.release(rid)
 
     def stats(self) -> dict:
         return self.engine.stats()

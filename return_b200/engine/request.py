@@ -6,6 +6,9 @@ token *sequences*; generation ends when the output ends with one of them, and th
 stay in the output, :49-57), ``output``, ``output_logprobs``.  The paragraph fields of the reference
 (``split_ids``, ``subs``, ``swap``, ...) belong to its context-folding feature and have no counterpart.
 ``seed`` is new: the random draws of a request come from (seed, index of the output token) alone.
+``keep``: what the request holds in the cache stays when it ends, for a later request with the same id
+whose prompt begins with this one's prompt and output (the reference keeps every session until
+``release``, rollout/engine.py:266-306; here None takes the engine's setting).
 """
 from __future__ import annotations
 
@@ -23,6 +26,7 @@ class Request:
     top_k: int = 0
     stop_ids: List[List[int]] = field(default_factory=list)
     seed: Optional[int] = None
+    keep: Optional[bool] = None
     output: List[int] = field(default_factory=list)
     output_logprobs: List[float] = field(default_factory=list)
     finish_reason: Optional[str] = None          # "length" | "stop" | "error"

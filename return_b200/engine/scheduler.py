@@ -15,13 +15,18 @@ allows it:
   go back and it returns to the head of the queue with prompt + output as its new prompt
   (recompute), so the oldest requests always make progress and nothing deadlocks;
 * a request that does not fit the empty pool on its own gets ``KVCapacityError``
-  (at submit if the prompt alone is too long, else when it has grown that far).
+  (at submit if the prompt alone is too long, else when it has grown that far);
+* a request that ends may keep what it holds (``keep``), as every session of the reference does until
+  ``release`` (rollout/engine.py:266-306): a later request with the same id whose prompt begins with
+  the kept tokens starts behind them.  Kept sessions are a cache, not a promise: when pages or slots run
+  short the one kept longest gives them back before any running request is preempted, and a follow-up
+  whose prompt does not continue the kept tokens starts from nothing.
 """
 from __future__ import annotations
 
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
-from typing import Deque, List, Optional
+from typing import Deque, Hashable, List, Optional
 
 from ..cache.manager import CacheManager, KVCapacityError
 from .request import Request
@@ -51,12 +56,14 @@ class StepPlan:
 
 
 class Scheduler:
-    def __init__(self, manager: CacheManager, prefill_chunk: int, max_model_len: int):
+    def __init__(self, manager: CacheManager, prefill_chunk: int, max_model_len: int, keep_sessions: bool = False):
         self.manager = manager
         self.prefill_chunk = prefill_chunk
         self.max_model_len = max_model_len
+        self.keep_sessions = keep_sessions
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []         # in order of admission: the last is the youngest
+        self.kept: "OrderedDict[Hashable, List[int]]" = OrderedDict()    # ended requests that kept their cache: id -> cached tokens
         self._arrivals = 0
 
     # ------------------------------------------------------------------ requests
@@ -73,9 +80,52 @@ class Scheduler:
             raise KVCapacityError(f"prompt of {len(req.prompt_ids)} tokens exceeds the engine's sequence limit {self.max_model_len}")
         if len(req.prompt_ids) > self.pool_tokens():
             raise KVCapacityError('Request prefill exceeds the GPU KV page capacity')     # rollout/engine.py:219-221
+        if any(r.id == req.id for r in self.running) or any(r.id == req.id for r in self.waiting):
+            raise ValueError(f"request {req.id!r} is still running")
         req.arrival = self._arrivals
         self._arrivals += 1
+        cached = self.kept.pop(req.id, None)
+        if cached is not None:
+            # a follow-up of a kept session starts behind the cached tokens if its prompt continues them
+            if len(req.prompt_ids) > len(cached) and req.prompt_ids[:len(cached)] == cached:
+                req.num_computed = len(cached)
+            else:
+                self.manager.free(req.id)
         self.waiting.append(req)
+
+    def release(self, rid) -> bool:
+        """Gives back what an ended request kept (rollout/engine.py:276-284); a request that still runs keeps
+        nothing when it ends.  Returns whether anything was given back or marked."""
+        if rid in self.kept:
+            del self.kept[rid]
+            self.manager.free(rid)
+            return True
+        for r in list(self.running) + list(self.waiting):
+            if r.id == rid:
+                r.keep = False
+                return True
+        return False
+
+    def _evict_kept(self) -> bool:
+        """The session that was kept longest gives back its pages and its slot; False if none is kept."""
+        if not self.kept:
+            return False
+        rid, _ = self.kept.popitem(last=False)
+        self.manager.free(rid)
+        return True
+
+    def finish(self, req: Request) -> None:
+        """The request has ended: it leaves the running list and gives back what it holds, or keeps it."""
+        self.running.remove(req)
+        keep = self.keep_sessions if req.keep is None else req.keep
+        # steps that ran ahead of the host may have cached a token or two past the request's end
+        overrun = self.manager.length(req.id) > req.num_computed
+        if keep and req.finish_reason != "error" and req.num_computed > 0 and (not overrun or self.manager.truncatable):
+            if overrun:
+                self.manager.truncate(req.id, req.num_computed)
+            self.kept[req.id] = req.all_ids[:req.num_computed]
+        else:
+            self.manager.free(req.id)
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
@@ -117,6 +167,9 @@ class Scheduler:
         ``fits_budget``: the caller has just seen that ``budget`` tokens fit the free pages."""
         total = req.num_tokens
         remaining = total - req.num_computed
+        if not fits_budget:
+            while not self.manager.fits(req.id, min(remaining, budget)) and self._evict_kept():
+                pass
         n = min(remaining, budget) if fits_budget else self._max_fit(req.id, min(remaining, budget))
         if n <= 0:
             return 0
@@ -134,6 +187,8 @@ class Scheduler:
                 if req not in self.running or not req.output or req.num_computed != req.num_tokens - 1:
                     continue
                 fits = self.manager.fits(req.id, 1)
+                while not fits and self._evict_kept():
+                    fits = self.manager.fits(req.id, 1)
                 while not fits:
                     victim = self.running[-1]
                     if victim is req:
@@ -160,14 +215,19 @@ class Scheduler:
                 if id(req) in planned or req.num_computed >= req.num_tokens:
                     continue
                 budget -= self._portion(req, budget, plan)
-            while self.waiting and budget > 0 and self.manager.free_slots > 0:
+            while self.waiting and budget > 0:
                 req = self.waiting[0]
                 if req in plan.preempted:
                     break                     # it just gave way; it comes back in a later step
-                self.manager.add(req.id)
+                resumed = req.id in self.manager          # a follow-up of a kept session: its slot and pages are there
+                if not resumed:
+                    if self.manager.free_slots == 0 and not self._evict_kept():
+                        break
+                    self.manager.add(req.id)
                 got = self._portion(req, budget, plan)
                 if got == 0:
                     self.manager.free(req.id)
+                    req.num_computed = 0      # what was kept is gone: the whole prompt again, later
                     break
                 self.waiting.popleft()
                 self.running.append(req)
@@ -204,7 +264,6 @@ class Scheduler:
                 req.push(tok, lp)
                 if req.finished or req.num_tokens >= self.max_model_len:
                     req.finish_reason = req.reason() if req.finished else "length"
-                    self.manager.free(req.id)
-                    self.running.remove(req)
+                    self.finish(req)
                     done.append(req)
         return done

@@ -245,3 +245,35 @@ def test_running_ahead_with_requests_that_cross_a_page_edge_together(tmp_path):
     assert eng.stats()["preemptions"] > 0
     eng.runner.manager.check()
     assert eng.runner.manager.pages_used() == [0]
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_a_kept_session_continues_in_a_second_turn(tmp_path, graph):
+    """The reference keeps a session's cache when a request ends, and the next request of the session runs only
+    what is new (rollout/engine.py:266-306; its check: rollout/utils/check_correctness.py:52-81, two turns).  Here
+    with ``keep``: turn 1 generates, turn 2 brings the whole conversation plus new tokens; its tokens equal the
+    plain implementation's on the whole context, and only the new tokens were run.  With captured graphs a stop
+    sequence is seen one step late, so a token too many is in the cache and has to be taken back before keeping."""
+    d = helpers.make_model_dir(tmp_path, "B")
+    p1 = helpers.random_ids(384, 23, 5)
+    more = helpers.random_ids(384, 11, 6)
+    free = _plain_greedy(d, [p1], 10)[0]
+    stop = [free[4:6]]
+    first = next(i for i in range(1, 10) if free[i - 1:i + 1] == stop[0])
+    eng = _engine(d, page_size=8, use_cuda_graph=graph)
+    t1 = eng.generate([p1], max_new_tokens=10, temperature=0.0, stop_ids=stop, keep=True, ids=["chat"])[0]
+    assert t1.output_ids == free[:first + 1] and t1.finish_reason == "stop"
+    cached = len(p1) + len(t1.output_ids) - 1
+    assert eng.runner.manager.length("chat") == cached and eng.stats()["kept_sessions"] == 1
+    p2 = p1 + t1.output_ids + more
+    want2 = _plain_greedy(d, [p2], 8)[0]
+    steps_before = eng.stats()["steps"]
+    t2 = eng.generate([p2], max_new_tokens=8, temperature=0.0, keep=True, ids=["chat"])[0]
+    assert t2.output_ids == want2
+    # the second turn's prompt went in as one portion of what was new: one step for it, then seven decode steps
+    assert eng.stats()["steps"] - steps_before == 8
+    assert eng.runner.manager.length("chat") == len(p2) + 7
+    assert eng.release("chat") and eng.runner.manager.pages_used() == [0] and eng.runner.manager.free_slots == 4
+    # without keep nothing stays
+    eng.generate([p1], max_new_tokens=3, temperature=0.0, ids=["other"])
+    assert eng.stats()["kept_sessions"] == 0 and eng.runner.manager.pages_used() == [0]

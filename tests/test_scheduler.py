@@ -152,3 +152,79 @@ def test_random_load_finishes_everything_and_leaks_nothing(seed):
         assert steps < 5000
     assert all(r.finish_reason == "length" and len(r.output) == r.max_new_tokens for r in reqs)
     assert m.pages_used() == [0, 0] and m.free_slots == 4
+
+
+def test_kept_session_resumes_behind_its_cache_and_is_released():
+    m, s = _sched(pages=16, page=4, max_reside=2, chunk=32)
+    a = Request("s", [1, 2, 3, 4, 5], max_new_tokens=3, keep=True)
+    s.add(a)
+    _run(s, m, tok=7)
+    assert a.output == [7, 7, 7] and list(s.kept) == ["s"]
+    assert s.kept["s"] == [1, 2, 3, 4, 5, 7, 7] and m.length("s") == 7        # the last sampled token was not fed
+    assert m.pages_used() == [2] and m.free_slots == 1
+    # the follow-up brings the whole conversation; only what is new runs
+    b = Request("s", [1, 2, 3, 4, 5, 7, 7, 7, 9, 9], max_new_tokens=2)
+    s.add(b)
+    p = s.schedule()
+    assert [(e.request.id, e.tokens, e.start, e.sample) for e in p.entries] == [("s", [7, 9, 9], 7, True)]
+    s.commit(p, {"s": (8, 0.0)})
+    _run(s, m, tok=8)
+    assert b.output == [8, 8] and not s.kept and m.pages_used() == [0] and m.free_slots == 2     # b kept nothing
+    # release of a kept session
+    c = Request("t", [1, 2, 3], max_new_tokens=1, keep=True)
+    s.add(c)
+    _run(s, m)
+    assert "t" in s.kept and s.release("t") and not s.kept and m.pages_used() == [0]
+    assert not s.release("t")
+    m.check()
+
+
+def test_follow_up_that_does_not_continue_the_kept_tokens_starts_from_nothing():
+    m, s = _sched(pages=16, page=4, chunk=32)
+    s.add(Request("s", [1, 2, 3, 4], max_new_tokens=2, keep=True))
+    _run(s, m, tok=7)
+    b = Request("s", [1, 2, 9, 4, 7, 5], max_new_tokens=1)
+    s.add(b)
+    assert "s" not in m and b.num_computed == 0
+    p = s.schedule()
+    assert [(e.tokens, e.start) for e in p.entries] == [([1, 2, 9, 4, 7, 5], 0)]
+    s.commit(p, {"s": (3, 0.0)})
+    m.check()
+
+
+def test_kept_sessions_give_way_before_running_requests_are_preempted():
+    m, s = _sched(pages=6, page=4, max_reside=2, chunk=32)
+    for name in ("k1", "k2"):
+        s.add(Request(name, list(range(7)), max_new_tokens=2, keep=True))
+    _run(s, m)
+    assert list(s.kept) == ["k1", "k2"] and m.pages_used() == [4] and m.free_slots == 0
+    # a new request needs a slot and more pages than are free: the session kept longest goes first
+    n = Request("n", list(range(11)), max_new_tokens=2)
+    s.add(n)
+    p = s.schedule()
+    assert [e.request.id for e in p.entries] == ["n"] and not p.preempted
+    assert list(s.kept) == ["k2"]
+    s.commit(p, {"n": (5, 0.0)})
+    _run(s, m, tok=5)
+    assert n.output == [5, 5]
+    # k2 is still there for its follow-up
+    f = Request("k2", list(range(7)) + [7, 7, 1], max_new_tokens=1)
+    s.add(f)
+    p = s.schedule()
+    assert p.entries[0].start == 8 and p.entries[0].tokens == [7, 1]
+    m.check()
+
+
+def test_truncate_gives_pages_back():
+    m = CacheManager([GroupSpec("full", 4, 8)], 2)
+    m.add("a")
+    m.append("a", 10)
+    assert m.pages_used() == [3]
+    m.truncate("a", 9)
+    assert m.length("a") == 9 and m.pages_used() == [3]
+    m.truncate("a", 4)
+    assert m.pages_used() == [1] and m.append("a", 1) == 4
+    m.truncatable = False
+    with pytest.raises(ValueError, match="nothing can be taken back"):
+        m.truncate("a", 2)
+    m.check()
