@@ -670,29 +670,73 @@ attn_decode_kernel(const bf16* __restrict__ q, int ld, const bf16* __restrict__ 
     }
 }
 
-__global__ void __launch_bounds__(128)
+// One CTA per (token, query head).  Every load is asked for before anything waits for one: the splits' (maximum,
+// sum) pairs by one thread each, the splits' outputs eight at a time by the thread of their column, so the kernel
+// takes about two trips to memory however many splits there are (a loop that loads, uses and loads again takes
+// one trip per few splits, three times over).
+constexpr int COMBINE_MAX_SPLITS = 64;
+constexpr int COMBINE_THREADS = 128;
+__global__ void __launch_bounds__(COMBINE_THREADS)
 attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     const int* __restrict__ dec_segs, const int* __restrict__ cu_q,
                     bf16* __restrict__ out, int Hq, int num_splits) {
+    __shared__ float s_w[COMBINE_MAX_SPLITS];
+    __shared__ float s_red[2][COMBINE_THREADS / 32];
     pdl_launch_dependents();
-    pdl_wait();
-    const int i = blockIdx.x, h = blockIdx.y;
-    const int tok_row = cu_q[dec_segs[i]];
+    const int i = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int tok_row = cu_q[dec_segs[i]];             // the step's tables: written before its first kernel
     const size_t base = ((size_t)i * Hq + h) * num_splits;
-    float mg = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) mg = fmaxf(mg, part_ml[(base + s) * 2]);
-    float lg = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-        const float ms = part_ml[(base + s) * 2];
-        lg += ms == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(ms - mg);
-    }
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.f;
-        for (int s = 0; s < num_splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            if (ms != -INFINITY) acc += part_o[(base + s) * D + d] * exp2f(ms - mg);
+    pdl_wait();
+    constexpr int COLS = (D + COMBINE_THREADS - 1) / COMBINE_THREADS;       // columns of a thread
+    constexpr int UNROLL = 8;
+    float po[COLS][UNROLL];
+    auto load_o = [&](int s0) {
+#pragma unroll
+        for (int c = 0; c < COLS; ++c) {
+            const int d = tid + c * COMBINE_THREADS;
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+                po[c][u] = (s0 + u < num_splits && d < D) ? part_o[(base + s0 + u) * D + d] : 0.f;
         }
-        out[(size_t)tok_row * Hq * D + (size_t)h * D + d] = __float2bfloat16_rn(acc / lg);
+    };
+    float2 ml = make_float2(-INFINITY, 0.f);
+    if (tid < num_splits) ml = *reinterpret_cast<const float2*>(part_ml + (base + tid) * 2);
+    load_o(0);
+    // the common maximum, every split's weight and the common sum
+    float mg = ml.x;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mg = fmaxf(mg, __shfl_xor_sync(0xffffffffu, mg, o));
+    if ((tid & 31) == 0) s_red[0][tid >> 5] = mg;
+    __syncthreads();
+    mg = s_red[0][0];
+#pragma unroll
+    for (int w = 1; w < COMBINE_THREADS / 32; ++w) mg = fmaxf(mg, s_red[0][w]);
+    const float wgt = ml.x == -INFINITY ? 0.f : exp2f(ml.x - mg);
+    if (tid < COMBINE_MAX_SPLITS) s_w[tid] = wgt;
+    float lg = ml.y * wgt;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, o);
+    if ((tid & 31) == 0) s_red[1][tid >> 5] = lg;
+    __syncthreads();
+    lg = 0.f;
+#pragma unroll
+    for (int w = 0; w < COMBINE_THREADS / 32; ++w) lg += s_red[1][w];       // in the order of the splits
+    float acc[COLS];
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) acc[c] = 0.f;
+    for (int s0 = 0; s0 < num_splits; s0 += UNROLL) {
+        if (s0 > 0) load_o(s0);
+#pragma unroll
+        for (int c = 0; c < COLS; ++c)
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+                if (s0 + u < num_splits) acc[c] += po[c][u] * s_w[s0 + u];
+    }
+    const float inv = 1.0f / lg;
+#pragma unroll
+    for (int c = 0; c < COLS; ++c) {
+        const int d = tid + c * COMBINE_THREADS;
+        if (d < D) out[(size_t)tok_row * Hq * D + (size_t)h * D + d] = __float2bfloat16_rn(acc[c] * inv);
     }
 }
 
@@ -735,7 +779,7 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
                   int bt_stride, int page_size, float* scratch, void* out, int Hq, int Hkv,
                   float scale, int window, int num_splits, const FusedRope* fused, cudaStream_t st) {
     if (n_dec <= 0) return 0;
-    if (num_splits < 1 || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
+    if (num_splits < 1 || num_splits > COMBINE_MAX_SPLITS || (num_splits > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
     const int G = Hq / Hkv, m_tiles = (G + 15) / 16;
     const size_t pipe = (size_t)DC_WARPS * DC_STAGES * 2 * DC_N * D * sizeof(bf16);
     const size_t merge = (size_t)DC_WARPS * 16 * (D + 2) * sizeof(float);
