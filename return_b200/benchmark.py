@@ -255,7 +255,8 @@ def kernel_attention_prefill(batch=1, ctx=2048, q_len=2048, heads=32, kv_heads=8
 def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> Dict[str, float]:
     """A bfloat16 matrix product alone: device time, weight bandwidth and TFLOP/s.
     ``impl`` 0: ``ops.linear`` (the engine's choice); 1: the tcgen05 kernel; 2: cuBLAS (``torch.mm``);
-    3: the tcgen05 weight-streaming kernel; 4: the mma.sync weight-streaming kernel."""
+    3: the tcgen05 weight-streaming kernel; 4: the mma.sync weight-streaming kernel; 5: the tcgen05 kernel on
+    256 x 256 tiles by pairs of CTAs."""
     from .ext import ops
     dev = torch.device("cuda:0")
     fns = []
@@ -271,10 +272,12 @@ def kernel_gemm(M=8, N=4096, K=4096, iters=10, warmup=3, out_f32=0, impl=0) -> D
             fns.append(lambda a=(x, w, out): ops.gemm_stream(*a))
         elif impl == 4:
             fns.append(lambda a=(x, w, out): ops.gemm_skinny(*a))
+        elif impl == 5:
+            fns.append(lambda a=(x, w, out): ops.gemm_tc5(*a, pair=True))
         else:
             fns.append(lambda a=(x, w, out): ops.linear(*a))
     ms = _time_kernels(fns, iters, warmup)
-    return {"kernel": ("linear", "gemm_tc5", "cublas", "gemm_stream", "gemm_skinny")[impl], "M": M, "N": N, "K": K, "ms": ms, "GBps": N * K * 2 / ms / 1e6,
+    return {"kernel": ("linear", "gemm_tc5", "cublas", "gemm_stream", "gemm_skinny", "gemm_tc5_pair")[impl], "M": M, "N": N, "K": K, "ms": ms, "GBps": N * K * 2 / ms / 1e6,
             "TFLOPs": 2.0 * M * N * K / ms / 1e9}
 
 
@@ -306,7 +309,8 @@ def kernel_elementwise(rows=2048, hidden=4096, intermediate=12288, iters=10, war
 
 def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[str, float]:
     """The gated feed-forward product out = silu(x Wg^T) * (x Wu^T) alone.  ``impl`` 0: the engine's
-    choice (``ops.gated_linear``); 1: the tcgen05 kernel with the SwiGLU epilogue; 2: cuBLAS + the SwiGLU kernel."""
+    choice (``ops.gated_linear``); 1: the tcgen05 kernel with the SwiGLU epilogue; 2: cuBLAS + the SwiGLU kernel;
+    3: the tcgen05 kernel by pairs of CTAs with the SwiGLU epilogue."""
     from .ext import ops
     dev = torch.device("cuda:0")
     fns = []
@@ -317,6 +321,8 @@ def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[st
         gu = torch.empty((M, 2 * I), dtype=torch.bfloat16, device=dev)
         if impl == 1:
             fns.append(lambda a=(x, w, out): ops.gemm_tc5(a[0], a[1], a[2], gated=True))
+        elif impl == 3:
+            fns.append(lambda a=(x, w, out): ops.gemm_tc5(a[0], a[1], a[2], gated=True, pair=True))
         elif impl == 2:
             def two(a=(x, w, out, gu)):
                 torch.mm(a[0], a[1].t(), out=a[3])
@@ -325,7 +331,7 @@ def kernel_gated(M=2048, I=12288, K=4096, iters=10, warmup=3, impl=0) -> Dict[st
         else:
             fns.append(lambda a=(x, w, out): ops.gated_linear(a[0], a[1], a[2], 8))
     ms = _time_kernels(fns, iters, warmup)
-    return {"kernel": ("gated_linear", "gemm_tc5_gated", "cublas+swiglu")[impl], "M": M, "I": I, "K": K, "ms": ms,
+    return {"kernel": ("gated_linear", "gemm_tc5_gated", "cublas+swiglu", "gemm_tc5_pair_gated")[impl], "M": M, "I": I, "K": K, "ms": ms,
             "TFLOPs": 4.0 * M * I * K / ms / 1e9}
 
 

@@ -15,6 +15,8 @@
 // TMEM and returns.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "tc5.cuh"
 #include "tma.cuh"
 
@@ -335,6 +337,211 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     if (warp == 1) tmem_dealloc(tacc, TMEM_COLS);
 }
 
+// ------------------------------------------------------------------------------------ the pair kernel
+// Two CTAs of a cluster, on neighbouring SMs, compute one 256 x 256 tile with the two-SM form of the MMA
+// (cta_group::2, M = 256): CTA r of the pair holds rows r*128.. of the tile's tokens and rows r*128.. of its
+// weights, so a k block costs each SM 32 KB of operands from L2 instead of the 48 KB a 128 x 256 tile of its
+// own would, and the tensor core of each SM reads the other half of the weights from its peer's shared memory.
+// The pair's even CTA (the leader) issues the MMAs; each CTA's accumulator half (its 128 rows x 256 columns,
+// two buffers) is in its own tensor memory and is drained by its own epilogue warps.
+//   producer thread (both CTAs): waits for its own "stage empty" barrier and asks for its two boxes with TMA;
+//       the bytes of both CTAs are counted on the leader's "stage full" barrier (cp.async.bulk.tensor with
+//       .cta_group::2 may signal a barrier of the peer), which the leader arms with the sum;
+//   MMA thread (leader): waits for "stage full", issues four MMAs, and commits with a multicast to the "stage
+//       empty" barriers of both CTAs; after the last k block it commits to "accumulator full" of both;
+//   epilogue warps (both CTAs): wait for "accumulator full", drain, and arrive on the leader's "accumulator
+//       empty" barrier (eight arrivals: four warps of each CTA).
+// Nothing is multicast by TMA.  Every mbarrier wait is bounded; the two cluster barriers (after set-up, before
+// the tensor memory is given back) are reached by every thread whatever the waits did.
+constexpr int PR_BN = 256;                // columns of the pair's tile
+constexpr int PR_HALF = PR_BN / 2;        // weight rows a CTA holds
+constexpr int PR_KPS = 2;                 // k blocks of 64 a stage: one wait and one commit of the issuing thread for both
+constexpr int PR_STAGES = 3;              // x 64 KB (measured at 2,048 x 24,576 x 4,096: 1.41 / 1.45 / 1.32 PFLOP/s with 1 / 2 / 3 k blocks a stage)
+constexpr unsigned PR_A_BYTES = BM * BK * 2, PR_B_BYTES = PR_HALF * BK * 2, PR_BLOCK_BYTES = PR_A_BYTES + PR_B_BYTES;
+constexpr unsigned PR_STAGE_BYTES = PR_KPS * PR_BLOCK_BYTES;
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's shared window, of the same variable in CTA `rank`
+__device__ __forceinline__ unsigned map_to_cta(unsigned smem_addr, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_in_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(unsigned smem_dst, const CUtensorMap* map, int x, int y, unsigned bar_in_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_dst), "l"(map), "r"(x), "r"(y), "r"(bar_in_cluster) : "memory");
+}
+__device__ __forceinline__ void mma_ss_pair(unsigned d_tmem, unsigned long long a_desc, unsigned long long b_desc,
+                                            unsigned idesc, bool accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((unsigned)accumulate) : "memory");
+}
+// one arrival on the barrier at this address in both CTAs of the pair, when the MMAs issued so far are done
+__device__ __forceinline__ void mma_commit_pair(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(unsigned slot_smem, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(unsigned taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+template <typename TOut, bool GATED>
+__global__ void __launch_bounds__(TC5_THREADS)
+tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                     TOut* __restrict__ out, int M, int N, int K, int ldo, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    __shared__ __align__(8) unsigned long long full_bar[PR_STAGES], empty_bar[PR_STAGES], acc_full[2], acc_empty[2];
+    __shared__ unsigned tmem_slot;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const unsigned rank = cluster_ctarank();                // 0: the leader
+    const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
+    constexpr unsigned TMEM_COLS = 2 * PR_BN;
+    const int nkb = (K + BK * PR_KPS - 1) / (BK * PR_KPS);  // stages a tile; k blocks past K are zero-filled by the copy
+    const int m_tiles = (M + 2 * BM - 1) / (2 * BM), n_tiles = (N + PR_BN - 1) / PR_BN, tiles = m_tiles * n_tiles;
+
+    if (warp == 1) tmem_alloc_pair(smem_u32(&tmem_slot), TMEM_COLS);
+    if (tid == 0) {
+        tma::prefetch_desc(&map_x);
+        tma::prefetch_desc(&map_w);
+#pragma unroll
+        for (int s = 0; s < PR_STAGES; ++s) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+#pragma unroll
+        for (int b = 0; b < 2; ++b) { mbar_init(smem_u32(&acc_full[b]), 1); mbar_init(smem_u32(&acc_empty[b]), 8); }
+        mbar_init_fence();
+    }
+    fence_before_sync();
+    cluster_sync_all();                                     // both CTAs' barriers exist before either is signalled
+    fence_after_sync();
+    pdl_wait();                                             // the tokens come from the kernel before
+    const unsigned tacc = tmem_slot;
+    bool ok = true;
+
+    if (warp == 0) {
+        if (lane == 0) {                                    // ---- producer (both CTAs)
+            int it = 0;
+            for (int tile = pair; tile < tiles; tile += pairs) {
+                const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM, n0 = (tile / m_tiles) * PR_BN + (int)rank * PR_HALF;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % PR_STAGES;
+                    if (it >= PR_STAGES) ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / PR_STAGES) - 1) & 1) && ok;
+                    const unsigned full_local = smem_u32(&full_bar[s]);
+                    if (rank == 0) mbar_arrive_expect_tx(full_local, 2 * PR_STAGE_BYTES);
+                    const unsigned full = map_to_cta(full_local, 0);
+                    const unsigned dst = smem_u32(base + (size_t)s * PR_STAGE_BYTES);
+#pragma unroll
+                    for (int j = 0; j < PR_KPS; ++j) {
+                        tma_load_2d_pair(dst + j * PR_BLOCK_BYTES, &map_x, (kb * PR_KPS + j) * BK, m0, full);
+                        tma_load_2d_pair(dst + j * PR_BLOCK_BYTES + PR_A_BYTES, &map_w, (kb * PR_KPS + j) * BK, n0, full);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {                       // ---- MMA issuer (the leader)
+            const unsigned idesc = instr_desc_bf16(2 * BM, PR_BN);
+            int it = 0, local = 0;
+            for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+                const int buf = local & 1;
+                if (local >= 2) ok = mbar_wait(smem_u32(&acc_empty[buf]), ((local >> 1) - 1) & 1) && ok;
+                fence_after_sync();
+                const unsigned d = tacc + buf * PR_BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % PR_STAGES;
+                    ok = mbar_wait(smem_u32(&full_bar[s]), (it / PR_STAGES) & 1) && ok;
+                    fence_after_sync();
+                    const unsigned a0 = smem_u32(base + (size_t)s * PR_STAGE_BYTES);
+#pragma unroll
+                    for (int j = 0; j < PR_KPS; ++j) {
+                        const unsigned a = a0 + j * PR_BLOCK_BYTES, b = a + PR_A_BYTES;
+#pragma unroll
+                        for (int k16 = 0; k16 < BK / 16; ++k16)
+                            mma_ss_pair(d, smem_desc_sw128(a, k16 * 32), smem_desc_sw128(b, k16 * 32), idesc, kb > 0 || j > 0 || k16 > 0);
+                    }
+                    mma_commit_pair(smem_u32(&empty_bar[s]));   // the stage is free in both CTAs once these MMAs have read it
+                }
+                mma_commit_pair(smem_u32(&acc_full[buf]));      // both halves of this tile's accumulator are complete
+            }
+        }
+    } else {                                                // ---- epilogue (both CTAs): TMEM lanes by warp % 4
+        const int q = warp & 3;
+        const unsigned acc_empty_leader0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+        const unsigned acc_empty_leader1 = map_to_cta(smem_u32(&acc_empty[1]), 0);
+        int local = 0;
+        for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+            const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM, n0 = (tile / m_tiles) * PR_BN;
+            const int buf = local & 1;
+            ok = mbar_wait(smem_u32(&acc_full[buf]), (local >> 1) & 1) && ok;
+            if (tile + pairs >= tiles) pdl_trigger_late();                 // the last tile of this CTA
+            fence_after_sync();
+            const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < PR_BN; c0 += 32) {
+                unsigned r[32];
+                tmem_ld32(tacc + ((unsigned)(q * 32) << 16) + buf * PR_BN + c0, r);
+                tmem_ld_wait();
+                if (m >= M || n0 + c0 >= N) continue;
+                if (GATED) {
+                    // columns come in blocks of 8 gate values and their 8 up values: 32 columns give 16 outputs
+                    TOut* dst = out + (size_t)m * ldo + ((n0 + c0) >> 1);
+                    const int valid = min(16, (N - n0 - c0) >> 1);
+                    float g[16];
+#pragma unroll
+                    for (int b = 0; b < 2; ++b)
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float gate = __uint_as_float(r[b * 16 + j]), up = __uint_as_float(r[b * 16 + 8 + j]);
+                            g[b * 8 + j] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                        }
+                    if (valid == 16 && sizeof(TOut) == 2 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(g[j], g[j + 1]), p1 = __floats2bfloat162_rn(g[j + 2], g[j + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(g[j + 4], g[j + 5]), p3 = __floats2bfloat162_rn(g[j + 6], g[j + 7]);
+                            v.x = *reinterpret_cast<unsigned*>(&p0); v.y = *reinterpret_cast<unsigned*>(&p1);
+                            v.z = *reinterpret_cast<unsigned*>(&p2); v.w = *reinterpret_cast<unsigned*>(&p3);
+                            *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(dst) + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (j < valid) dst[j] = from_f32<TOut>(g[j]);
+                    }
+                } else {
+                    store_row_chunk(out + (size_t)m * ldo + n0 + c0, r, min(32, N - n0 - c0));
+                }
+            }
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_in_cluster(buf ? acc_empty_leader1 : acc_empty_leader0);   // this warp has drained its quarter
+        }
+    }
+    if (!ok) atomicExch(status, 1);
+    __syncwarp();
+    fence_before_sync();
+    cluster_sync_all();                                     // neither CTA leaves, or gives its tensor memory back, while the other works
+    if (warp == 1) tmem_dealloc_pair(tacc, TMEM_COLS);
+}
+
 // ------------------------------------------------------------------------------------ host side
 template <int BN, int STAGES, int KPS, typename TOut, bool GATED>
 int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo, int* status,
@@ -359,6 +566,60 @@ int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int
     dim3 grid(tiles < num_sms ? tiles : num_sms);
     return rb_launch_pdl(tc5_gemm_kernel<BN, STAGES, KPS, TOut, GATED>, grid, dim3(TC5_THREADS), smem, st, mx, mw,
                          (TOut*)out, M, N, K, ldo, status);
+}
+
+template <typename TOut, bool GATED>
+int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo, int* status,
+                cudaStream_t st) {
+    CUtensorMap mx, mw;
+    if (!tma::make_map_bf16(&mx, x, M, K, ldx, BM) || !tma::make_map_bf16(&mw, w, N, K, ldw, PR_HALF)) return (int)cudaErrorInvalidValue;
+    const size_t smem = (size_t)PR_STAGES * PR_STAGE_BYTES + 1024;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    static std::mutex mu;
+    static bool configured[64] = {false};
+    static int num_sms[64] = {0};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!configured[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(tc5_gemm_pair_kernel<TOut, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            // pairs that the device holds at once (an SM whose neighbour is switched off takes none)
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3(2);
+            probe.blockDim = dim3(TC5_THREADS);
+            probe.dynamicSmemBytes = smem;
+            cudaLaunchAttribute pa[1];
+            pa[0].id = cudaLaunchAttributeClusterDimension;
+            pa[0].val.clusterDim.x = 2;
+            pa[0].val.clusterDim.y = 1;
+            pa[0].val.clusterDim.z = 1;
+            probe.attrs = pa;
+            probe.numAttrs = 1;
+            int clusters = 0;
+            e = cudaOccupancyMaxActiveClusters(&clusters, tc5_gemm_pair_kernel<TOut, GATED>, &probe);
+            if (e != cudaSuccess || clusters < 1) return e != cudaSuccess ? (int)e : (int)cudaErrorInvalidConfiguration;
+            num_sms[dev] = 2 * clusters;
+            configured[dev] = true;
+        }
+    }
+    const int tiles = ((N + PR_BN - 1) / PR_BN) * ((M + 2 * BM - 1) / (2 * BM));
+    const int pairs = tiles < num_sms[dev] / 2 ? tiles : num_sms[dev] / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(TC5_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = RB_PDL_MODE == 3 ? 1 : 2;
+    return (int)cudaLaunchKernelEx(&cfg, tc5_gemm_pair_kernel<TOut, GATED>, mx, mw, (TOut*)out, M, N, K, ldo, status);
 }
 
 }  // namespace
@@ -419,4 +680,17 @@ RB_EXPORT int rb_tc5_gemm_bmn(const void* x, const void* b, float* out, int bn, 
     if (bn == 256) RB_BMN(256)
 #undef RB_BMN
     return (int)cudaErrorInvalidValue;
+}
+
+// The same product by pairs of CTAs on 256 x 256 tiles (two-SM MMAs); same arguments as rb_tc5_gemm.
+RB_EXPORT int rb_tc5_gemm_pair(const void* x, const void* w, void* out, int out_f32, int gated, int M, int N, int K,
+                               int ldx, int ldw, int ldo, int* status, cudaStream_t st) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)x % 16) || ((uintptr_t)w % 16)) return (int)cudaErrorInvalidValue;
+    if (gated) {
+        if (out_f32 || N % 16) return (int)cudaErrorInvalidValue;
+        return launch_pair<bf16, true>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    }
+    if (out_f32) return launch_pair<float, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
+    return launch_pair<bf16, false>(x, w, out, M, N, K, ldx, ldw, ldo, status, st);
 }

@@ -38,21 +38,25 @@ def test_one_stage_twin(bn, M, N, K):
     assert (out.double() - want).abs().max() < 2e-3
 
 
+@pytest.mark.parametrize("pair", [False, True], ids=["one_cta", "cta_pair"])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (33, 40, 72), (300, 520, 1000), (2048, 1024, 4096),
-                                   (129, 257 * 8, 264)])
-def test_pipelined_product(M, N, K, out_dtype):
+                                   (129, 257 * 8, 264), (257, 256, 136), (1100, 1288, 328)])
+def test_pipelined_product(M, N, K, out_dtype, pair):
+    """One 128 x 256 tile a CTA, and 256 x 256 tiles by pairs of CTAs (two-SM MMAs): tails in every dimension, more
+    tiles than CTAs, fewer k blocks than stages."""
     ops = _ops()
     x, w, want = _case(M, N, K, M * 3 + N + K)
     out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    ops.gemm_tc5(x, w, out)
+    ops.gemm_tc5(x, w, out, pair=pair)
     assert _status_clear(ops) == 0, "a bounded wait inside the kernel gave up"
     tol = 2e-3 if out_dtype == torch.float32 else 3e-2
     assert (out.double() - want).abs().max() < tol
 
 
-@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (200, 104, 136), (512, 3072, 1024)])
-def test_pipelined_product_with_swiglu_epilogue(M, I, K):
+@pytest.mark.parametrize("pair", [False, True], ids=["one_cta", "cta_pair"])
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (200, 104, 136), (512, 3072, 1024), (1030, 1192, 520)])
+def test_pipelined_product_with_swiglu_epilogue(M, I, K, pair):
     ops = _ops()
     g = torch.Generator().manual_seed(M + I)
     x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
@@ -60,7 +64,7 @@ def test_pipelined_product_with_swiglu_epilogue(M, I, K):
     up = (torch.randn(I, K, generator=g) / K ** 0.5).bfloat16()
     woven = torch.stack([gate.view(-1, 8, K), up.view(-1, 8, K)], dim=1).reshape(2 * I, K).contiguous().to(DEV)
     out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.gemm_tc5(x, woven, out, gated=True)
+    ops.gemm_tc5(x, woven, out, gated=True, pair=pair)
     assert _status_clear(ops) == 0
     gg, uu = x.float().cpu() @ gate.float().T, x.float().cpu() @ up.float().T
     assert torch.allclose(out.float().cpu(), gg * torch.sigmoid(gg) * uu, atol=2e-2, rtol=3e-2)
@@ -124,3 +128,39 @@ def test_gemm_stream_gated(M, I, K):
     assert _status_clear(ops) == 0
     gg, uu = x.float().cpu() @ gate.float().T, x.float().cpu() @ up.float().T
     assert torch.allclose(out.float().cpu(), gg * torch.sigmoid(gg) * uu, atol=2e-2, rtol=3e-2)
+
+
+def test_the_pair_kernel_gives_the_same_bits_again_and_takes_a_view():
+    """A second call gives the same bits (the order of the k blocks is fixed); x may be a view with a row stride."""
+    ops = _ops()
+    M, N, K = 777, 1544, 392
+    x, w, want = _case(M, N, K, 11)
+    a = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    b = torch.full_like(a, float("nan"))
+    ops.gemm_tc5(x, w, a, pair=True)
+    ops.gemm_tc5(x, w, b, pair=True)
+    assert _status_clear(ops) == 0
+    assert torch.equal(a, b) and (a.double() - want).abs().max() < 3e-2
+    big = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    big[:, :K] = x
+    c = torch.empty_like(a)
+    ops.gemm_tc5(big[:, :K], w, c, pair=True)
+    assert _status_clear(ops) == 0 and torch.equal(c, a)
+
+
+def test_gated_linear_takes_the_pair_kernel_for_many_rows():
+    """``ops.gated_linear`` with the woven layout: the same numbers whichever kernel the row count selects."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    M, I, K = ops.PAIR_MIN_ROWS + 37, 520, 264
+    x = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    w = (torch.randn(2 * I, K, generator=g) / K ** 0.5).bfloat16().to(DEV)
+    many = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gated_linear(x, w, many, 8)
+    assert _status_clear(ops) == 0
+    few = torch.empty((100, I), dtype=torch.bfloat16, device=DEV)
+    ops.gated_linear(x[:100], w, few, 8)                       # cuBLAS and the SwiGLU kernel
+    assert torch.allclose(many[:100].float(), few.float(), atol=2e-2, rtol=3e-2)
+    r = (x.float() @ w.float().T).view(M, I // 8, 2, 8)
+    want = (torch.nn.functional.silu(r[:, :, 0]) * r[:, :, 1]).reshape(M, I)
+    assert torch.allclose(many.float(), want, atol=2e-2, rtol=3e-2)
