@@ -750,18 +750,11 @@ RB_EXPORT int rb_attn_prefill(const void* q, int ld, const void* kpool, const vo
                               int window, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
     const size_t smem = (size_t)(PF_M + 4 * PF_N) * D * sizeof(bf16) + BT_CAP * sizeof(int);
-    {
-        static std::mutex mu;
-        static bool configured[64] = {false};
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-        std::lock_guard<std::mutex> lock(mu);
-        if (!configured[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            configured[dev] = true;
-        }
-    }
+    static PerDevice configured;
+    const int cfg = configured.once([&](int) {
+        return cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    });
+    if (cfg != 0) return cfg;
     dim3 grid(n_tiles, Hq);
     return rb_launch_pdl(attn_prefill_kernel, grid, dim3(128), smem, st, (const bf16*)q, ld, (const bf16*)kpool,
                          (const bf16*)vpool, tiles, cu_q, seg_pos0, block_table, bt_stride, page_size, (bf16*)out,
@@ -784,20 +777,14 @@ int launch_decode(const void* q, int ld, const void* kpool, const void* vpool, c
     const size_t pipe = (size_t)DC_WARPS * DC_STAGES * 2 * DC_N * D * sizeof(bf16);
     const size_t merge = (size_t)DC_WARPS * 16 * (D + 2) * sizeof(float);
     const size_t smem = (size_t)16 * D * sizeof(bf16) + BT_CAP * sizeof(int) + (pipe > merge ? pipe : merge);
-    {
-        // the kernels' shared-memory limit is a setting per device: made once for each device that calls
-        static std::mutex mu;
-        static bool configured[64] = {false};
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-        std::lock_guard<std::mutex> lock(mu);
-        if (!configured[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            configured[dev] = true;
-        }
-    }
+    // the kernels' shared-memory limit is a setting per device: made once for each device that calls
+    static PerDevice configured;
+    const int cfg = configured.once([&](int) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return e;
+    });
+    if (cfg != 0) return cfg;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_dec * Hq * num_splits * D : nullptr;
     dim3 grid(n_dec, Hkv * m_tiles, num_splits);

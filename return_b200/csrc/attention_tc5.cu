@@ -548,12 +548,11 @@ RB_EXPORT int rb_attn_prefill_tc5(const void* q, int ld, const void* kpool, cons
                                   int n_split, void* scratch, int total_rows, int* status, cudaStream_t st) {
     if (n_tiles <= 0) return 0;
     if (n_tiles > 65535 || n_split < 1 || n_split > 64 || (n_split > 1 && scratch == nullptr)) return (int)cudaErrorInvalidValue;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static PerDevice configured;
+    const int rc = configured.once([](int) {
+        return cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    });
+    if (rc != 0) return rc;
     float* part_o = (float*)scratch;
     float* part_ml = part_o ? part_o + (size_t)n_split * total_rows * Hq * D : nullptr;
     dim3 grid(Hq, n_tiles, n_split);

@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #define RB_EXPORT extern "C" __attribute__((visibility("default")))
 
 // dtype codes shared with return_b200/ext/ops.py
@@ -16,6 +18,38 @@
 #define RB_BF16 1
 
 typedef __nv_bfloat16 bf16;
+
+// Host-side set-up that CUDA keeps per device (cudaFuncSetAttribute, a device's properties): a launcher holds one of
+// these as a static and runs its set-up the first time it is called with each device current, under a lock.
+// `amount` lets a set-up be run again when more is asked for than before (a larger shared-memory limit).
+struct PerDevice {
+    static constexpr int MAX_DEVICES = 64;
+    std::mutex mu;
+    long long have[MAX_DEVICES] = {0};
+    template <typename F>
+    int once(F set_up, long long amount = 1) {             // set_up(device) -> cudaError_t; returns 0 or the CUDA error
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return (int)e;
+        if (dev < 0 || dev >= MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lock(mu);
+        if (have[dev] >= amount) return 0;
+        e = set_up(dev);
+        if (e == cudaSuccess) have[dev] = amount;
+        return (int)e;
+    }
+};
+
+// Streaming multiprocessors of the current device (0 if it cannot be asked).
+static inline int rb_num_sms() {
+    static std::mutex mu;
+    static int sms[PerDevice::MAX_DEVICES] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PerDevice::MAX_DEVICES) return 0;
+    std::lock_guard<std::mutex> lock(mu);
+    if (sms[dev] == 0) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    return sms[dev];
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(bf16 x) { return __bfloat162float(x); }

@@ -232,17 +232,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut*
     }
 }
 
-int resident_ctas() {                                     // CTAs that fit the current GPU at once
-    static int of_device[64] = {0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-    if (of_device[dev] == 0) {
-        int sms = 0;
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        of_device[dev] = sms * SK_CTAS_PER_SM;
-    }
-    return of_device[dev];
-}
+int resident_ctas() { return rb_num_sms() * SK_CTAS_PER_SM; }      // CTAs that fit the current GPU at once
 
 int grid_for(int N) {
     const int groups = (N + SK_ROWS - 1) / SK_ROWS, resident = resident_ctas();

@@ -282,16 +282,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_cons
     if (warp == 1) tmem_dealloc(tacc, tmem_cols);
 }
 
-int num_sms() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    }
-    return n;
-}
-
 Plan make_plan(int N, int K, int grid, int mpad, bool gated) {
     Plan p;
     p.granule = gated ? 16 : 1;
@@ -321,7 +311,8 @@ Plan make_plan(int N, int K, int grid, int mpad, bool gated) {
 template <int MPAD, typename TOut, bool GATED>
 int launch_stream(const void* x, const void* w, void* out, int M, int N, int K, int ldx, int ldw, int ldo,
                   int* status, cudaStream_t st) {
-    const int sms = num_sms();
+    const int sms = rb_num_sms();
+    if (sms <= 0) return (int)cudaErrorInvalidDevice;
     const Plan plan = make_plan(N, K, sms, MPAD, GATED);
     CUtensorMap mw[3], mx;
     for (int i = 0; i < 3; ++i) {
@@ -333,13 +324,11 @@ int launch_stream(const void* x, const void* w, void* out, int M, int N, int K, 
     // the MMA reads 128 rows from a stage's base: room for that behind the last stage; then the sums of the parts
     const size_t red_bytes = plan.kq > 1 ? (size_t)LANES * MPAD * 4 : 0;
     const size_t smem = (size_t)plan.stages * (plan.w_bytes + plan.kq * MPAD * BK * 2) + LANES * BK * 2 + red_bytes + 1024;
-    static size_t configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<MPAD, TOut, GATED>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
+    static PerDevice configured;                           // the largest shared-memory size asked for so far, per device
+    const int rc = configured.once([&](int) {
+        return cudaFuncSetAttribute(gemm_stream_kernel<MPAD, TOut, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }, (long long)smem);
+    if (rc != 0) return rc;
     const int units = (N + plan.granule - 1) / plan.granule;
     dim3 grid(units < sms ? units : sms);
     return rb_launch_pdl(gemm_stream_kernel<MPAD, TOut, GATED>, grid, dim3(THREADS), smem, st, mw[0], mw[1], mw[2], mx,
@@ -372,6 +361,6 @@ RB_EXPORT int rb_gemm_stream(const void* x, const void* w, void* out, int out_f3
 // tallest chunk, parts of K side by side}.
 RB_EXPORT void rb_gemm_stream_plan(int M, int N, int K, int gated, int* out4) {
     const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-    const Plan p = make_plan(N, K, num_sms(), mpad, gated != 0);
+    const Plan p = make_plan(N, K, rb_num_sms(), mpad, gated != 0);
     out4[0] = (p.base + (p.extra ? 1 : 0)) * p.granule; out4[1] = p.nchunk; out4[2] = p.qmax * p.granule; out4[3] = p.kq;
 }

@@ -15,8 +15,6 @@
 // TMEM and returns.
 #include <cuda.h>
 
-#include <mutex>
-
 #include "tc5.cuh"
 #include "tma.cuh"
 
@@ -549,20 +547,14 @@ int launch_tc5(const void* x, const void* w, void* out, int M, int N, int K, int
     CUtensorMap mx, mw;
     if (!tma::make_map_bf16(&mx, x, M, K, ldx, BM) || !tma::make_map_bf16(&mw, w, N, K, ldw, BN)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)STAGES * KPS * (BM + BN) * BK * 2 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(tc5_gemm_kernel<BN, STAGES, KPS, TOut, GATED>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static PerDevice configured;
+    const int rc = configured.once([&](int) {
+        return cudaFuncSetAttribute(tc5_gemm_kernel<BN, STAGES, KPS, TOut, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    });
+    if (rc != 0) return rc;
     const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
-    static int num_sms = 0;
-    if (num_sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int num_sms = rb_num_sms();
+    if (num_sms <= 0) return (int)cudaErrorInvalidDevice;
     dim3 grid(tiles < num_sms ? tiles : num_sms);
     return rb_launch_pdl(tc5_gemm_kernel<BN, STAGES, KPS, TOut, GATED>, grid, dim3(TC5_THREADS), smem, st, mx, mw,
                          (TOut*)out, M, N, K, ldo, status);
@@ -574,37 +566,36 @@ int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, in
     CUtensorMap mx, mw;
     if (!tma::make_map_bf16(&mx, x, M, K, ldx, BM) || !tma::make_map_bf16(&mw, w, N, K, ldw, PR_HALF)) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)PR_STAGES * PR_STAGE_BYTES + 1024;
+    // pairs that the device holds at once (an SM whose neighbour is switched off takes none)
+    static PerDevice configured;
+    static int pairs_of_device[PerDevice::MAX_DEVICES] = {0};
+    const int rc = configured.once([&](int dev) {
+        cudaError_t e = cudaFuncSetAttribute(tc5_gemm_pair_kernel<TOut, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(2);
+        probe.blockDim = dim3(TC5_THREADS);
+        probe.dynamicSmemBytes = smem;
+        cudaLaunchAttribute pa[1];
+        pa[0].id = cudaLaunchAttributeClusterDimension;
+        pa[0].val.clusterDim.x = 2;
+        pa[0].val.clusterDim.y = 1;
+        pa[0].val.clusterDim.z = 1;
+        probe.attrs = pa;
+        probe.numAttrs = 1;
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, tc5_gemm_pair_kernel<TOut, GATED>, &probe);
+        if (e != cudaSuccess) return e;
+        if (clusters < 1) return cudaErrorInvalidConfiguration;
+        pairs_of_device[dev] = clusters;
+        return cudaSuccess;
+    });
+    if (rc != 0) return rc;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
-    static std::mutex mu;
-    static bool configured[64] = {false};
-    static int num_sms[64] = {0};
-    {
-        std::lock_guard<std::mutex> lock(mu);
-        if (!configured[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(tc5_gemm_pair_kernel<TOut, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-            // pairs that the device holds at once (an SM whose neighbour is switched off takes none)
-            cudaLaunchConfig_t probe = {};
-            probe.gridDim = dim3(2);
-            probe.blockDim = dim3(TC5_THREADS);
-            probe.dynamicSmemBytes = smem;
-            cudaLaunchAttribute pa[1];
-            pa[0].id = cudaLaunchAttributeClusterDimension;
-            pa[0].val.clusterDim.x = 2;
-            pa[0].val.clusterDim.y = 1;
-            pa[0].val.clusterDim.z = 1;
-            probe.attrs = pa;
-            probe.numAttrs = 1;
-            int clusters = 0;
-            e = cudaOccupancyMaxActiveClusters(&clusters, tc5_gemm_pair_kernel<TOut, GATED>, &probe);
-            if (e != cudaSuccess || clusters < 1) return e != cudaSuccess ? (int)e : (int)cudaErrorInvalidConfiguration;
-            num_sms[dev] = 2 * clusters;
-            configured[dev] = true;
-        }
-    }
+    cudaGetDevice(&dev);
+    const int resident = pairs_of_device[dev];
     const int tiles = ((N + PR_BN - 1) / PR_BN) * ((M + 2 * BM - 1) / (2 * BM));
-    const int pairs = tiles < num_sms[dev] / 2 ? tiles : num_sms[dev] / 2;
+    const int pairs = tiles < resident ? tiles : resident;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(TC5_THREADS);
