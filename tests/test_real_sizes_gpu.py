@@ -86,3 +86,49 @@ def test_mixed_trace_at_real_layer_sizes(real_model, dtype, graph):
             pos[e["id"]] = base + len(e["tokens"])
     assert rp.runner.manager.pages_used() == [0]
     print(f"real sizes {dtype} graph={graph}: worst error {worst:.3g}, logits' deviation {scale:.3g}")
+
+
+def test_long_portions_take_the_pair_kernel(real_model):
+    """Portions of 768 rows and more run the gated feed-forward product on the tcgen05 kernel by pairs of CTAs
+    (ops.PAIR_MIN_ROWS): a prompt of 1,100 tokens in one step, then 840 tokens of a second request beside a
+    decoded token of the first, against the plain implementation in bfloat16."""
+    from return_b200.engine.replay import TraceReplayer
+    from return_b200.ext import ops
+    assert ops.PAIR_MIN_ROWS <= 840
+    lens = {"p0": 1102, "p1": 850}
+    reqs = {rid: helpers.random_ids(REAL["vocab_size"], n, 700 + i) for i, (rid, n) in enumerate(lens.items())}
+    tail = lambda n, k=4: list(range(max(0, n - k), n))
+    steps = [
+        {"step": 0, "entries": [{"id": "p0", "tokens": reqs["p0"][:1100], "want": tail(1100) + [3, 500, 767, 768]}], "end": []},
+        {"step": 1, "entries": [{"id": "p0", "tokens": reqs["p0"][1100:1101], "want": [0]},
+                                {"id": "p1", "tokens": reqs["p1"][:840], "want": tail(840) + [0, 255, 256]}], "end": []},
+        {"step": 2, "entries": [{"id": "p0", "tokens": reqs["p0"][1101:1102], "want": [0]},
+                                {"id": "p1", "tokens": reqs["p1"][840:850], "want": tail(10)}], "end": ["p0", "p1"]},
+    ]
+    calls = []
+    real = ops.gemm_tc5
+
+    def spy(*a, **kw):
+        calls.append((a[0].shape[0], kw.get("pair", False), kw.get("gated", False)))
+        return real(*a, **kw)
+
+    rp = TraceReplayer(real_model, "bfloat16", helpers.pool_tokens(steps), page_size=16, max_reside=2, poison=True)
+    refs = {rid: helpers.plain_logits(real_model, ids) for rid, ids in reqs.items()}
+    tol = float(torch.cat(list(refs.values())).std()) / 12
+    ops.gemm_tc5 = spy
+    try:
+        pos = {}
+        for st in steps:
+            lg = rp.run_step(st).float().cpu()
+            r = 0
+            for e in st["entries"]:
+                base = pos.get(e["id"], 0)
+                for w in e["want"]:
+                    err = float((lg[r] - refs[e["id"]][base + w]).abs().max())
+                    assert err <= tol, f"step {st['step']} {e['id']} position {base + w}: error {err:.3g} (tolerance {tol:.3g})"
+                    r += 1
+                pos[e["id"]] = base + len(e["tokens"])
+    finally:
+        ops.gemm_tc5 = real
+    # two layers in each of the two long steps, none in the short one
+    assert sorted(calls) == [(841, True, True)] * 2 + [(1100, True, True)] * 2, calls
