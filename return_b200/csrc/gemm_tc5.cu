@@ -351,6 +351,20 @@ tc5_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
 //       empty" barrier (eight arrivals: four warps of each CTA).
 // Nothing is multicast by TMA.  Every mbarrier wait is bounded; the two cluster barriers (after set-up, before
 // the tensor memory is given back) are reached by every thread whatever the waits did.
+// The order of the tiles.  Tiles that run at the same time should share operands in L2: row tiles of one block of
+// weights run back to back (the row index fastest), but only PR_GROUP_ROWS row tiles of them; then the next block of
+// weights for the same rows, and the next group of rows only after the last block.  What is live at a time is then
+// a group's rows (16 x 256 tokens) and a few blocks of weights, whatever the number of tokens; with the row index
+// fastest over all rows, 32,768 tokens (268 MB) would be read again from HBM for every block of weights.
+constexpr int PR_GROUP_ROWS = 16;
+__device__ __forceinline__ void pair_tile_coords(int tile, int m_tiles, int n_tiles, int& mt, int& nt) {
+    const int per_group = PR_GROUP_ROWS * n_tiles;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int rows = min(PR_GROUP_ROWS, m_tiles - g * PR_GROUP_ROWS);     // the last group may be short
+    nt = r / rows;
+    mt = g * PR_GROUP_ROWS + (r - nt * rows);
+}
+
 constexpr int PR_BN = 256;                // columns of the pair's tile
 constexpr int PR_HALF = PR_BN / 2;        // weight rows a CTA holds
 constexpr int PR_KPS = 2;                 // k blocks of 64 a stage: one wait and one commit of the issuing thread for both
@@ -437,7 +451,9 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         if (lane == 0) {                                    // ---- producer (both CTAs)
             int it = 0;
             for (int tile = pair; tile < tiles; tile += pairs) {
-                const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM, n0 = (tile / m_tiles) * PR_BN + (int)rank * PR_HALF;
+                int mt, nt;
+                pair_tile_coords(tile, m_tiles, n_tiles, mt, nt);
+                const int m0 = mt * 2 * BM + (int)rank * BM, n0 = nt * PR_BN + (int)rank * PR_HALF;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % PR_STAGES;
                     if (it >= PR_STAGES) ok = mbar_wait(smem_u32(&empty_bar[s]), ((it / PR_STAGES) - 1) & 1) && ok;
@@ -485,7 +501,9 @@ tc5_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const unsigned acc_empty_leader1 = map_to_cta(smem_u32(&acc_empty[1]), 0);
         int local = 0;
         for (int tile = pair; tile < tiles; tile += pairs, ++local) {
-            const int m0 = (tile % m_tiles) * 2 * BM + (int)rank * BM, n0 = (tile / m_tiles) * PR_BN;
+            int mt, nt;
+            pair_tile_coords(tile, m_tiles, n_tiles, mt, nt);
+            const int m0 = mt * 2 * BM + (int)rank * BM, n0 = nt * PR_BN;
             const int buf = local & 1;
             ok = mbar_wait(smem_u32(&acc_full[buf]), (local >> 1) & 1) && ok;
             if (tile + pairs >= tiles) pdl_trigger_late();                 // the last tile of this CTA
