@@ -193,10 +193,349 @@ sample_kernel(const float* __restrict__ logits, int ld, int V,
     }
 }
 
+// ---------------------------------------------------------------- a row by a cluster of eight CTAs
+// The kernel above reads a row (600 KB at a vocabulary of 151,936) some seventy times with one CTA: 60 us a greedy
+// row, 2.5 ms with top-k and top-p.  Here a cluster of eight CTAs takes a row: each CTA reads an eighth of it once
+// into its shared memory, and every later pass runs there.  What the CTAs have to tell one another (maxima, sums,
+// histograms) each writes into all eight shared memories (st.shared::cluster) and a cluster barrier follows; the
+// values are then added in the order of the CTAs.
+// The cut-off values are found digit by digit, sixteen bins a pass (eight passes of four bits instead of thirty-two
+// of one), counts as integers and masses as fixed point (exp(x - max) * 2^32, added in 64 bits), so every sum is
+// exact and the result does not depend on the order of the additions.  Same meanings as above; the chosen token is the first,
+// in vocabulary order, at which the running mass of the kept tokens reaches u * (kept mass).
+constexpr int SC_CTAS = 8;
+constexpr int SC_THREADS = 512;                        // two CTAs share an SM
+constexpr int SC_WARPS = SC_THREADS / 32;
+constexpr float SC_MASS_ONE = 4294967296.0f;              // 2^32
+typedef unsigned long long u64;
+
+__device__ __forceinline__ unsigned sc_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void sc_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void sc_store(const void* local, unsigned rank, u64 v) {      // the same variable in CTA `rank`
+    unsigned a = (unsigned)__cvta_generic_to_shared(local), r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
+    asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(r), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned sc_mass(float xs, float mxs) {
+    return __float2uint_rz(fminf(expf(xs - mxs) * SC_MASS_ONE, 4294967040.0f));
+}
+// v[d] += m with v in registers: one case runs (the lanes of a warp mostly agree on the digit), not sixteen compares
+__device__ __forceinline__ void sc_bin_add(u64 (&v)[16], unsigned d, u64 m) {
+    switch (d) {
+        case 0: v[0] += m; break;   case 1: v[1] += m; break;   case 2: v[2] += m; break;   case 3: v[3] += m; break;
+        case 4: v[4] += m; break;   case 5: v[5] += m; break;   case 6: v[6] += m; break;   case 7: v[7] += m; break;
+        case 8: v[8] += m; break;   case 9: v[9] += m; break;   case 10: v[10] += m; break; case 11: v[11] += m; break;
+        case 12: v[12] += m; break; case 13: v[13] += m; break; case 14: v[14] += m; break; default: v[15] += m; break;
+    }
+}
+
+struct ScShared {
+    u64 warp_part[SC_WARPS][16];
+    u64 cta_tot[16];
+    u64 gath[2][SC_CTAS][16];          // what every CTA of the cluster said in this step (two steps in flight)
+    u64 warp_incl[SC_WARPS];
+    unsigned digit, pad;
+    u64 above;
+    int choice;
+};
+
+// Every thread brings 16 numbers; afterwards sh.gath[step & 1][r][b] holds CTA r's sums, for every r, in every CTA.
+__device__ __forceinline__ void sc_all_gather16(u64 (&v)[16], ScShared& sh, int step, unsigned rank, int n_used) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+    for (int b = 0; b < 16; ++b) {
+        if (b < n_used) {
+            u64 t = v[b];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+            if (lane == 0) sh.warp_part[warp][b] = t;
+        }
+    }
+    __syncthreads();
+    if (tid < n_used) {
+        u64 t = 0;
+        for (int w = 0; w < SC_WARPS; ++w) t += sh.warp_part[w][tid];
+        sh.cta_tot[tid] = t;
+    }
+    __syncthreads();
+    if (tid < n_used * SC_CTAS) {
+        const int r = tid / n_used, b = tid - r * n_used;
+        sc_store(&sh.gath[step & 1][rank][b], (unsigned)r, sh.cta_tot[b]);
+    }
+    sc_sync();
+}
+
+__global__ void __launch_bounds__(SC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, int per,
+                      const float* __restrict__ temperature, const int* __restrict__ top_k,
+                      const float* __restrict__ top_p, const float* __restrict__ uniform,
+                      int* __restrict__ token_out, float* __restrict__ logprob_out) {
+    extern __shared__ float sx[];                         // this CTA's part of the row
+    __shared__ ScShared sh;
+    __shared__ float fscratch[33];
+    __shared__ int iscratch[33];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned rank = sc_rank();
+    const int row = blockIdx.x / SC_CTAS;
+    const float* x = logits + (size_t)row * ld;
+    const int i0 = min(V, (int)rank * per), n = min(V, i0 + per) - i0;
+    const float temp = temperature ? temperature[row] : 0.f;
+    int step = 0;
+    u64 v16[16];
+    sc_sync();                                             // no CTA writes into another's shared memory before all have started
+
+    // ---- the part of the row, its maximum and the lowest index that holds it
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int j = tid; j < n; j += SC_THREADS) {
+        const float v = x[i0 + j];
+        sx[j] = v;
+        if (v > best) { best = v; best_i = i0 + j; }
+    }
+    const float mx_cta = block_max(best, fscratch);
+    int cand = (best == mx_cta) ? best_i : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) cand = min(cand, __shfl_xor_sync(0xffffffffu, cand, o));
+    __syncthreads();
+    if (lane == 0) iscratch[warp] = cand;
+    __syncthreads();
+    if (tid < 32) {
+        int c = tid < SC_WARPS ? iscratch[tid] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c = min(c, __shfl_xor_sync(0xffffffffu, c, o));
+        if (tid == 0) iscratch[32] = c;
+    }
+    __syncthreads();
+    if (tid < SC_CTAS) sc_store(&sh.gath[step & 1][rank][0], (unsigned)tid, ((u64)__float_as_uint(mx_cta) << 32) | (unsigned)iscratch[32]);
+    sc_sync();
+    float mx = -INFINITY;
+    int argmax = 0x7fffffff;
+    for (int r = 0; r < SC_CTAS; ++r) {
+        const u64 g = sh.gath[step & 1][r][0];
+        const float m = __uint_as_float((unsigned)(g >> 32));
+        const int a = (int)(unsigned)g;
+        if (m > mx || (m == mx && a < argmax)) { mx = m; argmax = a; }
+    }
+    if (argmax == 0x7fffffff) argmax = 0;                  // all -inf or NaN: token 0
+    ++step;
+    const bool greedy = !(temp > 0.f);
+    if (greedy && logprob_out == nullptr) {
+        if (rank == 0 && tid == 0) token_out[row] = argmax;
+        return;
+    }
+
+    // ---- sum of exp over the raw logits, for the log-probability
+    float se = 0.f;
+    for (int j = tid; j < n; j += SC_THREADS) se += expf(sx[j] - mx);
+    se = block_sum(se, fscratch);
+    if (tid < SC_CTAS) sc_store(&sh.gath[step & 1][rank][0], (unsigned)tid, (u64)__float_as_uint(se));
+    sc_sync();
+    float se_all = 0.f;
+    for (int r = 0; r < SC_CTAS; ++r) se_all += __uint_as_float((unsigned)sh.gath[step & 1][r][0]);
+    const float lse = mx + logf(se_all);
+    ++step;
+    if (greedy) {
+        if (rank == 0 && tid == 0) {
+            token_out[row] = argmax;
+            logprob_out[row] = x[argmax] - lse;
+        }
+        return;
+    }
+
+    const float mxs = mx / temp;
+    for (int j = tid; j < n; j += SC_THREADS) sx[j] = sx[j] / temp;
+    __syncthreads();
+    auto mass_at = [&](int j) -> u64 { return (u64)sc_mass(sx[j], mxs); };
+    const int k = top_k[row];
+    const float p_keep = top_p[row];
+    unsigned cut = 0u;                                     // tokens with key >= cut stay
+
+    if (k > 0 && k < V) {
+        // the k-th largest key, four bits a pass: among the keys that share the digits found so far, the bin in
+        // which the count from the top reaches k
+        unsigned prefix = 0u;
+        u64 above = 0;                                     // keys above every key that shares the prefix
+        for (int shift = 28; shift >= 0; shift -= 4) {
+            const unsigned hi_mask = shift == 28 ? 0u : (0xffffffffu << (shift + 4));
+#pragma unroll
+            for (int b = 0; b < 16; ++b) v16[b] = 0;
+            for (int j = tid; j < n; j += SC_THREADS) {
+                const unsigned key = ordered_key(sx[j]);
+                if ((key & hi_mask) == prefix) sc_bin_add(v16, (key >> shift) & 15u, 1ull);
+            }
+            sc_all_gather16(v16, sh, step, rank, 16);
+            if (tid < 16) {
+                u64 t = 0;
+                for (int r = 0; r < SC_CTAS; ++r) t += sh.gath[step & 1][r][tid];
+                sh.cta_tot[tid] = t;                       // now the sums over the whole row
+            }
+            __syncthreads();
+            if (tid == 0) {
+                u64 acc = above;
+                int d = 15;
+                for (; d > 0; --d) {
+                    const u64 t = sh.cta_tot[d];
+                    if (acc + t >= (u64)k) break;
+                    acc += t;
+                }
+                sh.digit = (unsigned)d;
+                sh.above = acc;
+            }
+            __syncthreads();
+            prefix |= sh.digit << shift;
+            above = sh.above;
+            ++step;
+            __syncthreads();
+        }
+        cut = prefix;
+    }
+    if (p_keep < 1.f) {
+        // kept mass so far, then the smallest c with mass{key > c, key >= cut} <= top_p * (that mass), four bits a pass
+#pragma unroll
+        for (int b = 0; b < 16; ++b) v16[b] = 0;
+        for (int j = tid; j < n; j += SC_THREADS)
+            if (ordered_key(sx[j]) >= cut) v16[0] += mass_at(j);
+        sc_all_gather16(v16, sh, step, rank, 1);
+        u64 z = 0;
+        for (int r = 0; r < SC_CTAS; ++r) z += sh.gath[step & 1][r][0];
+        ++step;
+        const u64 budget = (u64)((double)p_keep * (double)z);
+        unsigned prefix = 0u;
+        u64 above = 0;                                     // mass above every key that shares the prefix: never more than the budget
+        for (int shift = 28; shift >= 0; shift -= 4) {
+            const unsigned hi_mask = shift == 28 ? 0u : (0xffffffffu << (shift + 4));
+#pragma unroll
+            for (int b = 0; b < 16; ++b) v16[b] = 0;
+            for (int j = tid; j < n; j += SC_THREADS) {
+                const unsigned key = ordered_key(sx[j]);
+                if (key >= cut && (key & hi_mask) == prefix) sc_bin_add(v16, (key >> shift) & 15u, mass_at(j));
+            }
+            sc_all_gather16(v16, sh, step, rank, 16);
+            if (tid < 16) {
+                u64 t = 0;
+                for (int r = 0; r < SC_CTAS; ++r) t += sh.gath[step & 1][r][tid];
+                sh.cta_tot[tid] = t;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                // the lowest digit d for which the mass above it stays within the budget
+                u64 gt = above;
+                int d = 15;
+                for (;;) {
+                    const u64 t = sh.cta_tot[d];
+                    if (d == 0 || gt + t > budget) break;
+                    gt += t;
+                    --d;
+                }
+                sh.digit = (unsigned)d;
+                sh.above = gt;
+            }
+            __syncthreads();
+            prefix |= sh.digit << shift;
+            above = sh.above;
+            ++step;
+            __syncthreads();
+        }
+        cut = max(cut, prefix);
+    }
+
+    // ---- inverse CDF over the kept tokens in vocabulary order; a thread owns a run of its CTA's part
+    const int chunk = (n + SC_THREADS - 1) / SC_THREADS;
+    const int j0 = min(n, tid * chunk), j1 = min(n, j0 + chunk);
+    u64 own = 0;
+    int last_kept = -1;
+    for (int j = j0; j < j1; ++j)
+        if (ordered_key(sx[j]) >= cut) { own += mass_at(j); last_kept = j; }
+    u64 incl = own;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const u64 t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
+    if (lane == 31) sh.warp_incl[warp] = incl;
+    if (tid == 0) sh.choice = 0x7fffffff;
+    __syncthreads();
+    u64 before = 0, cta_total = 0;
+    for (int w = 0; w < SC_WARPS; ++w) {
+        if (w < warp) before += sh.warp_incl[w];
+        cta_total += sh.warp_incl[w];
+    }
+    incl += before;
+    if (tid < SC_CTAS) sc_store(&sh.gath[step & 1][rank][0], (unsigned)tid, cta_total);
+    sc_sync();
+    u64 total = 0, base = 0;
+    for (int r = 0; r < SC_CTAS; ++r) {
+        const u64 t = sh.gath[step & 1][r][0];
+        if (r < (int)rank) base += t;
+        total += t;
+    }
+    // u has 24 bits: u * total without leaving 64 bits; a target of zero would be met before the first token
+    const u64 u24 = (u64)(uniform[row] * 16777216.0f);
+    u64 target = (total >> 24) * u24 + (((total & 0xffffffull) * u24) >> 24);
+    if (target == 0) target = 1;
+    // the CTA in whose part the running mass reaches the target does the rest
+    if (!(base < target && base + cta_total >= target)) return;
+    if (last_kept >= 0 && base + incl >= target) atomicMin(&sh.choice, tid);
+    __syncthreads();
+    if (tid == sh.choice) {
+        u64 run = base + incl - own;
+        int tok = last_kept;
+        for (int j = j0; j < j1; ++j) {
+            if (ordered_key(sx[j]) >= cut) {
+                run += mass_at(j);
+                if (run >= target) { tok = j; break; }
+            }
+        }
+        token_out[row] = i0 + tok;
+        if (logprob_out) logprob_out[row] = x[i0 + tok] - lse;
+    }
+}
+
+// Rows of up to this many values go to the cluster kernel (an eighth of a row has to fit a CTA's shared memory).
+constexpr int SC_MAX_PART_BYTES = 200 * 1024;
+
+static int sample_cluster_part(int V) { return ((V + SC_CTAS - 1) / SC_CTAS + 3) & ~3; }     // values of a row a CTA holds
+static bool sample_cluster_fits(int V) { return (size_t)sample_cluster_part(V) * sizeof(float) <= (size_t)SC_MAX_PART_BYTES; }
+
+static int launch_sample_cluster(const float* logits, int ld, int n_rows, int V, const float* temperature,
+                                 const int* top_k, const float* top_p, const float* uniform, int* token_out,
+                                 float* logprob_out, cudaStream_t st) {
+    const int per = sample_cluster_part(V);
+    const size_t smem = (size_t)per * sizeof(float);
+    static PerDevice configured;                           // the largest shared-memory size asked for so far, per device
+    const int rc = configured.once([&](int) {
+        return cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }, (long long)smem + 1);
+    if (rc != 0) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_rows * SC_CTAS);
+    cfg.blockDim = dim3(SC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = SC_CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, ld, V, per, temperature, top_k, top_p, uniform,
+                                   token_out, logprob_out);
+}
+
+// one_cta != 0: the kernel with one CTA a row (any row length; the twin that the tests compare with).
 RB_EXPORT int rb_sample(const float* logits, int ld, int n_rows, int V, const float* temperature,
                         const int* top_k, const float* top_p, const float* uniform, int* token_out,
-                        float* logprob_out, cudaStream_t st) {
+                        float* logprob_out, int one_cta, cudaStream_t st) {
     if (n_rows <= 0) return 0;
+    if (!one_cta && sample_cluster_fits(V))
+        return launch_sample_cluster(logits, ld, n_rows, V, temperature, top_k, top_p, uniform, token_out, logprob_out, st);
     sample_kernel<<<n_rows, SAMPLE_THREADS, 0, st>>>(logits, ld, V, temperature, top_k, top_p, uniform,
                                                     token_out, logprob_out);
     return rb_launch_status();
@@ -233,6 +572,8 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
 
 RB_EXPORT int rb_argmax(const float* logits, int ld, int n_rows, int V, int* token_out, cudaStream_t st) {
     if (n_rows <= 0) return 0;
+    if (sample_cluster_fits(V))
+        return launch_sample_cluster(logits, ld, n_rows, V, nullptr, nullptr, nullptr, nullptr, token_out, nullptr, st);
     argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, st>>>(logits, ld, V, token_out);
     return rb_launch_status();
 }

@@ -91,7 +91,7 @@ def core() -> ctypes.CDLL:
         lib.rb_gemm_skinny_ctas.restype = c_int
         lib.rb_qk_norm_rope_write.argtypes = [P, I, P, P, I, F, F, P, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P]
         lib.rb_attention_simt.argtypes = [P, I, P, P, P, P, P, I, I, P, I, I, I, I, I, F, I, P]
-        lib.rb_sample.argtypes = [P, I, I, I, P, P, P, P, P, P, P]
+        lib.rb_sample.argtypes = [P, I, I, I, P, P, P, P, P, P, I, P]
         lib.rb_argmax.argtypes = [P, I, I, I, P, P]
         for name in ("rb_embedding", "rb_add_rmsnorm", "rb_rmsnorm_rows", "rb_swiglu", "rb_gemm_f32",
                      "rb_qk_norm_rope_write", "rb_attention_simt", "rb_sample", "rb_argmax"):
@@ -747,14 +747,16 @@ def paged_attention(qkv, k_pool, v_pool, batch, block_table, page_size, out, num
 
 # ------------------------------------------------------------------------------- sampling
 
-def sample(logits, temperature, top_k, top_p, uniform, tokens_out, logprobs_out=None) -> None:
-    """One token per row of float32 logits [n, V]; per-row temperature, top_k, top_p and uniform draw."""
+def sample(logits, temperature, top_k, top_p, uniform, tokens_out, logprobs_out=None, one_cta: bool = False) -> None:
+    """One token per row of float32 logits [n, V]; per-row temperature, top_k, top_p and uniform draw.
+    A cluster of eight CTAs takes a row (its parts in their shared memories); ``one_cta``: the kernel with one CTA
+    a row, which takes rows of any length and is what rows too long for eight shared memories fall back to."""
     n, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and uniform.dtype == torch.float32
     assert top_k.dtype == torch.int32 and tokens_out.dtype == torch.int32
     _check(core().rb_sample(_ptr(logits), logits.stride(0), n, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
-                            _ptr(uniform), _ptr(tokens_out), _ptr(logprobs_out), _stream()), "sample")
+                            _ptr(uniform), _ptr(tokens_out), _ptr(logprobs_out), 1 if one_cta else 0, _stream()), "sample")
 
 
 def argmax(logits, tokens_out) -> None:

@@ -612,6 +612,39 @@ def test_sample_matches_the_filtered_distribution(V):
         assert abs(float(lp[i]) - plain.logprob(logits[i], tok)) < 1e-3
 
 
+@pytest.mark.parametrize("V", [7, 50, 4099, 151936, 262144])
+def test_sample_by_a_cluster_and_by_one_cta_choose_the_same_tokens(V):
+    """The kernel that spreads a row over the shared memories of eight CTAs against its twin with one CTA a row:
+    greedy rows, temperature, top-k and top-p, with ties.  Masses are float32 sums in the one and exact fixed-point
+    sums in the other, so a draw that falls on the edge between two tokens may go either way: at most one row in
+    forty may differ, and then by a neighbour in the kept set."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(V)
+    n = 40
+    for trial in range(3):
+        logits = (2.5 * torch.randn(n, V, generator=g)).to(DEV)
+        if trial == 2:
+            logits[:, ::3] = logits[:, 1:2]                        # many equal values
+        temps = torch.tensor([0.8, 1.0, 1.3, 0.5, 0.0] * 8, device=DEV)
+        ks = torch.tensor([0, 0, 5, 40, 0, 1, 0, 3] * 5, dtype=torch.int32, device=DEV)
+        ps = torch.tensor([1.0, 0.9, 1.0, 0.7, 0.3, 1.0, 0.05, 0.95] * 5, device=DEV)
+        u = torch.rand(n, generator=g).to(DEV)
+        got = []
+        for one_cta in (True, False):
+            toks = torch.full((n,), -7, dtype=torch.int32, device=DEV)
+            lp = torch.full((n,), float("nan"), device=DEV)
+            ops.sample(logits, temps, ks, ps, u, toks, lp, one_cta=one_cta)
+            got.append((toks.cpu(), lp.cpu()))
+        same = got[0][0] == got[1][0]
+        assert int((~same).sum()) <= 1, (trial, got[0][0][~same], got[1][0][~same])
+        assert torch.allclose(got[0][1][same], got[1][1][same], atol=1e-5)
+        assert (got[1][0] >= 0).all() and (got[1][0] < V).all()
+        # again: the same bits
+        toks2 = torch.empty(n, dtype=torch.int32, device=DEV)
+        ops.sample(logits, temps, ks, ps, u, toks2, None)
+        assert torch.equal(toks2.cpu(), got[1][0])
+
+
 def test_sample_frequencies():
     ops = _ops()
     V, n = 12, 4000
