@@ -1,5 +1,7 @@
 // Sampling from float32 logits: greedy, temperature, top-k and top-p, with the log-probability
-// of the chosen token.  One thread block per row; rows carry their own parameters.
+// of the chosen token.  Rows carry their own parameters.  Two kernels with the same meanings: one CTA a row
+// (sample_kernel, any row length: the twin that tests compare with, and the fallback for very long rows) and a
+// cluster of eight CTAs a row (sample_cluster_kernel, further down: what the engine runs).
 //
 // Meaning of the options follows the reference's sampler (rollout/model.py:15-67):
 //   temperature <= 0        argmax of the raw logits;
