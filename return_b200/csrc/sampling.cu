@@ -478,7 +478,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, int per,
         total += t;
     }
     // u has 24 bits: u * total without leaving 64 bits; a target of zero would be met before the first token
-    const u64 u24 = (u64)(uniform[row] * 16777216.0f);
+    const u64 u24 = (u64)(fminf(fmaxf(uniform[row], 0.f), 0.99999994f) * 16777216.0f);
     u64 target = (total >> 24) * u24 + (((total & 0xffffffull) * u24) >> 24);
     if (target == 0) target = 1;
     // the CTA in whose part the running mass reaches the target does the rest
