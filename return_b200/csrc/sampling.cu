@@ -238,9 +238,8 @@ __device__ __forceinline__ void sc_bin_add(u64 (&v)[16], unsigned d, u64 m) {
 }
 
 struct ScShared {
-    u64 warp_part[SC_WARPS][16];
-    u64 cta_tot[16];
-    u64 gath[2][SC_CTAS][16];          // what every CTA of the cluster said in this step (two steps in flight)
+    u64 cta_tot[2][16];                // this CTA's sums of a step (two steps in flight; zero before a step adds to them)
+    u64 gath[2][SC_CTAS][16];          // what every CTA of the cluster said in this step
     u64 warp_incl[SC_WARPS];
     unsigned digit, pad;
     u64 above;
@@ -248,29 +247,42 @@ struct ScShared {
 };
 
 // Every thread brings 16 numbers; afterwards sh.gath[step & 1][r][b] holds CTA r's sums, for every r, in every CTA.
+// Most bins are empty in most warps (the values of a row share their leading digits, and late passes match few
+// values), so a warp adds up only the bins in which one of its lanes has something, and its first lane adds the
+// sum to the CTA's with an atomic in shared memory; integer sums, so the order does not matter.
 __device__ __forceinline__ void sc_all_gather16(u64 (&v)[16], ScShared& sh, int step, unsigned rank, int n_used) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, par = step & 1;
+    if (tid < 16) sh.cta_tot[par ^ 1][tid] = 0;            // for the step after this one: nobody reads or adds to it now
 #pragma unroll
     for (int b = 0; b < 16; ++b) {
-        if (b < n_used) {
+        if (b < n_used && __any_sync(0xffffffffu, v[b] != 0)) {
             u64 t = v[b];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-            if (lane == 0) sh.warp_part[warp][b] = t;
+            if (lane == 0) atomicAdd(&sh.cta_tot[par][b], t);
         }
-    }
-    __syncthreads();
-    if (tid < n_used) {
-        u64 t = 0;
-        for (int w = 0; w < SC_WARPS; ++w) t += sh.warp_part[w][tid];
-        sh.cta_tot[tid] = t;
     }
     __syncthreads();
     if (tid < n_used * SC_CTAS) {
         const int r = tid / n_used, b = tid - r * n_used;
-        sc_store(&sh.gath[step & 1][rank][b], (unsigned)r, sh.cta_tot[b]);
+        sc_store(&sh.gath[par][rank][b], (unsigned)r, sh.cta_tot[par][b]);
     }
     sc_sync();
+}
+
+// After a gather of 16 bins, in warp 0: lane l holds the row's sum of bin 15 - l (the bins from the top down), `incl`
+// the sum of the bins from the top down to its own.
+__device__ __forceinline__ void sc_bins_from_the_top(const ScShared& sh, int step, u64& own, u64& incl) {
+    const int lane = threadIdx.x & 31;
+    own = 0;
+    if (lane < 16)
+        for (int r = 0; r < SC_CTAS; ++r) own += sh.gath[step & 1][r][15 - lane];
+    incl = own;
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+        const u64 t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+    }
 }
 
 __global__ void __launch_bounds__(SC_THREADS)
@@ -290,6 +302,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, int per,
     const float temp = temperature ? temperature[row] : 0.f;
     int step = 0;
     u64 v16[16];
+    if (tid < 32) sh.cta_tot[tid >> 4][tid & 15] = 0;
     sc_sync();                                             // no CTA writes into another's shared memory before all have started
 
     // ---- the part of the row, its maximum and the lowest index that holds it
@@ -372,28 +385,19 @@ sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, int per,
                 if ((key & hi_mask) == prefix) sc_bin_add(v16, (key >> shift) & 15u, 1ull);
             }
             sc_all_gather16(v16, sh, step, rank, 16);
-            if (tid < 16) {
-                u64 t = 0;
-                for (int r = 0; r < SC_CTAS; ++r) t += sh.gath[step & 1][r][tid];
-                sh.cta_tot[tid] = t;                       // now the sums over the whole row
+            if (warp == 0) {
+                // from the top: the first bin at which the count reaches k (the lowest bin if none does)
+                u64 own, incl;
+                sc_bins_from_the_top(sh, step, own, incl);
+                const unsigned reached = __ballot_sync(0xffffffffu, lane < 16 && above + incl >= (u64)k) & 0xffffu;
+                const int l = reached ? __ffs(reached) - 1 : 15;
+                const u64 before = __shfl_sync(0xffffffffu, incl - own, l);
+                if (lane == 0) { sh.digit = (unsigned)(15 - l); sh.above = above + before; }
             }
-            __syncthreads();
-            if (tid == 0) {
-                u64 acc = above;
-                int d = 15;
-                for (; d > 0; --d) {
-                    const u64 t = sh.cta_tot[d];
-                    if (acc + t >= (u64)k) break;
-                    acc += t;
-                }
-                sh.digit = (unsigned)d;
-                sh.above = acc;
-            }
-            __syncthreads();
+            __syncthreads();                               // (the next write to these comes after the next gather's barrier)
             prefix |= sh.digit << shift;
             above = sh.above;
             ++step;
-            __syncthreads();
         }
         cut = prefix;
     }
@@ -419,30 +423,19 @@ sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, int per,
                 if (key >= cut && (key & hi_mask) == prefix) sc_bin_add(v16, (key >> shift) & 15u, mass_at(j));
             }
             sc_all_gather16(v16, sh, step, rank, 16);
-            if (tid < 16) {
-                u64 t = 0;
-                for (int r = 0; r < SC_CTAS; ++r) t += sh.gath[step & 1][r][tid];
-                sh.cta_tot[tid] = t;
-            }
-            __syncthreads();
-            if (tid == 0) {
-                // the lowest digit d for which the mass above it stays within the budget
-                u64 gt = above;
-                int d = 15;
-                for (;;) {
-                    const u64 t = sh.cta_tot[d];
-                    if (d == 0 || gt + t > budget) break;
-                    gt += t;
-                    --d;
-                }
-                sh.digit = (unsigned)d;
-                sh.above = gt;
+            if (warp == 0) {
+                // the lowest bin for which the mass above it stays within the budget (for the top bin it does)
+                u64 own, incl;
+                sc_bins_from_the_top(sh, step, own, incl);
+                const unsigned within = __ballot_sync(0xffffffffu, lane < 16 && above + (incl - own) <= budget) & 0xffffu;
+                const int l = within ? 31 - __clz(within) : 0;
+                const u64 before = __shfl_sync(0xffffffffu, incl - own, l);
+                if (lane == 0) { sh.digit = (unsigned)(15 - l); sh.above = above + before; }
             }
             __syncthreads();
             prefix |= sh.digit << shift;
             above = sh.above;
             ++step;
-            __syncthreads();
         }
         cut = max(cut, prefix);
     }
