@@ -164,3 +164,37 @@ def test_gated_linear_takes_the_pair_kernel_for_many_rows():
     r = (x.float() @ w.float().T).view(M, I // 8, 2, 8)
     want = (torch.nn.functional.silu(r[:, :, 0]) * r[:, :, 1]).reshape(M, I)
     assert torch.allclose(many.float(), want, atol=2e-2, rtol=3e-2)
+
+
+def test_cluster_kernels_replay_from_a_cuda_graph():
+    """The kernels that launch as clusters (the pair product, the sampler) captured into a CUDA graph and replayed
+    on new inputs in the same buffers."""
+    ops = _ops()
+    M, N, K, V = 800, 520, 264, 5000
+    x, w, _ = _case(M, N, K, 3)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    logits = torch.empty((6, V), device=DEV)
+    temp = torch.tensor([0.0, 1.0, 0.7, 1.2, 0.0, 0.9], device=DEV)
+    top_k = torch.tensor([0, 0, 20, 0, 0, 5], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.5, 1.0, 1.0], device=DEV)
+    u = torch.tensor([0.1, 0.5, 0.9, 0.3, 0.7, 0.2], device=DEV)
+    toks = torch.empty(6, dtype=torch.int32, device=DEV)
+    lps = torch.empty(6, device=DEV)
+    ops.gemm_tc5(x, w, out, pair=True)                       # compiled and configured before the capture
+    ops.sample(logits.normal_(), temp, top_k, top_p, u, toks, lps)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ops.gemm_tc5(x, w, out, pair=True)
+        ops.sample(logits, temp, top_k, top_p, u, toks, lps)
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    for _ in range(3):
+        x.copy_(torch.randn(M, K, generator=gen, device=DEV))
+        logits.copy_(3 * torch.randn(6, V, generator=gen, device=DEV))
+        g.replay()
+        torch.cuda.synchronize()
+        assert _status_clear(ops) == 0
+        assert (out.double() - x.double() @ w.double().T).abs().max() < 3e-2
+        want = torch.empty_like(toks)
+        ops.sample(logits, temp, top_k, top_p, u, want, None, one_cta=True)
+        assert torch.equal(toks, want)
