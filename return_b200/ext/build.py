@@ -145,8 +145,10 @@ def library_path(name: str, sources: Sequence[str], defines: Optional[Dict[str, 
             cmd = [find_nvcc()] + flags + ["-shared", "-o", tmp] + [os.path.join(CSRC, s) for s in sources]
             _run_with_heartbeat(cmd, what)
             os.replace(tmp, out)
-            for old in os.listdir(out_dir):          # builds of earlier sources under the same name are of no use now
-                if old.startswith(f"lib{name}-") and old.endswith(".so") and old != fname:
+            for old in os.listdir(out_dir):          # builds of earlier sources under the same name, and their lock files, are of no use now
+                stale_lib = old.startswith(f"lib{name}-") and old.endswith(".so") and old != fname
+                stale_lock = old.startswith(f".lib{name}-") and old.endswith(".so.lock") and old != f".{fname}.lock"
+                if stale_lib or stale_lock:
                     try:
                         os.remove(os.path.join(out_dir, old))
                     except OSError:
